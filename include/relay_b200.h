@@ -1,0 +1,269 @@
+/* relay_b200 — the C boundary of the B200 (sm_100a) implementation of relay's per-token
+ * compute path.
+ *
+ * Two groups of entry points:
+ *
+ *  1. The backend: everything relay's `relay::Backend` virtual interface offers
+ *     (engine/include/relay/backend.h:43-81) on an opaque handle, with plain pointers and
+ *     sizes, so that a thin C++ subclass (or a cgo / ctypes / Swift binding) turns each
+ *     virtual into one call. `make_cuda_backend` (backend.h:95-97) maps to rb200_create.
+ *
+ *  2. The operators: each hand-written kernel of the path on caller-owned DEVICE buffers,
+ *     for parity tests and measurements at the shapes the model-level path does not reach.
+ *
+ * Conventions (the reference C API's, engine/include/relay/c_api.h:5-6 and
+ * engine/src/c_api.cpp:31-46): functions that can fail return 0 or a valid pointer on
+ * success and -1 or NULL on failure; rb200_last_error() then says why, per thread.
+ * rb200_last_error_kind() classifies it the way the reference's exceptions do
+ * (engine/src/cuda_backend.cu:512-518, 546, 448).
+ *
+ * There is no CPU fallback behind any of these calls: without a CUDA device they fail.
+ */
+#ifndef RELAY_B200_H
+#define RELAY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- errors ------------------------------------------------------------------------ */
+
+enum {
+  RB200_OK = 0,
+  RB200_ERR_INVALID_ARGUMENT = 1, /* std::invalid_argument in the reference */
+  RB200_ERR_OUT_OF_RANGE = 2,     /* std::out_of_range (token id) */
+  RB200_ERR_RUNTIME = 3,          /* std::runtime_error (CUDA / NCCL) */
+  RB200_ERR_LOGIC = 4             /* std::logic_error (e.g. update of an int8 matrix refused) */
+};
+
+const char* rb200_last_error(void);
+int rb200_last_error_kind(void);
+/* Number of CUDA devices the library can see (0 without a driver); never fails. */
+int rb200_device_count(void);
+
+/* ---- model description ------------------------------------------------------------- */
+
+/* relay::ModelConfig (engine/include/relay/config.h:20-47), the fields the path reads. */
+typedef struct rb200_model_config {
+  int32_t hidden, intermediate, layers, heads, kv_heads, head_dim, vocab, max_position;
+  double rms_eps, rope_theta;
+  int32_t rope_scaling_type; /* 0: none, 1: "llama3" (config.h:12-18) */
+  double rope_factor, rope_low_freq_factor, rope_high_freq_factor, rope_original_max_position;
+  int32_t tie_embeddings, qkv_bias;
+} rb200_model_config;
+
+/* relay::LayerWeights / relay::HostWeights (engine/include/relay/weights.h:13-34):
+ * float32, row-major [out, in], q/k/v fused into wqkv and gate/up into w_gate_up. */
+typedef struct rb200_layer_weights {
+  const float* attn_norm; /* [hidden] */
+  const float* wqkv;      /* [q_dim + 2 kv_dim, hidden] */
+  const float* bqkv;      /* [q_dim + 2 kv_dim] or NULL */
+  const float* wo;        /* [hidden, q_dim] */
+  const float* mlp_norm;  /* [hidden] */
+  const float* w_gate_up; /* [2 intermediate, hidden]: gate rows, then up rows */
+  const float* w_down;    /* [hidden, intermediate] */
+} rb200_layer_weights;
+
+typedef struct rb200_weights {
+  const float* embed;      /* [vocab, hidden] */
+  const float* final_norm; /* [hidden] */
+  const float* lm_head;    /* [vocab, hidden], NULL when tied to embed */
+  const rb200_layer_weights* layers;
+} rb200_weights;
+
+/* relay::CudaOptions (backend.h:85-94). */
+enum {
+  RB200_INT8_WEIGHTS = 1,        /* CudaOptions::int8_weights: per-output-row int8 for the layer matrices */
+  RB200_REFERENCE_ATTENTION = 2, /* CudaOptions::reference_attention: the simple one-CTA-per-(token, head) kernel */
+  RB200_GPU_ARGMAX = 4           /* forward also leaves each logit row's greedy token on the device (rb200_forward_greedy) */
+};
+/* CudaOptions::from_env (engine/src/cuda_backend.cu:37-42): RELAY_CUDA_ATTENTION=m0, RELAY_CUDA_INT8=1. */
+uint32_t rb200_flags_from_env(void);
+
+/* The head_dim/2 inverse rotary frequencies with Llama-3 scaling applied
+ * (ModelConfig::rope_inv_freq, engine/src/config.cpp:79-109). Host only. */
+int rb200_rope_inv_freq(const rb200_model_config* cfg, float* out);
+
+/* Per-row symmetric int8 quantisation exactly as the reference's to_device_matrix
+ * (engine/src/cuda_backend.cu:282-304): scale = max|w| / 127 (1 for a zero row),
+ * q = lrintf(w / scale). Host only; w is [N, K] float32. */
+int rb200_quantize_rows_int8(const float* w, int N, int K, int8_t* q_out, float* scale_out);
+
+/* ---- the backend (relay::Backend) ---------------------------------------------------- */
+
+typedef struct rb200_backend rb200_backend;
+
+/* make_cuda_backend (backend.h:95-97; ctor engine/src/cuda_backend.cu:313-391).
+ * `weights` may be NULL: every tensor then starts as zeros and is filled through
+ * rb200_update_weight (which also takes device pointers), so a model too large for a
+ * float32 host copy can be built tensor by tensor. */
+rb200_backend* rb200_create(const rb200_model_config* cfg, const rb200_weights* weights, int num_blocks,
+                            int block_size, int device, int max_batch_tokens, int max_context, uint32_t flags);
+void rb200_destroy(rb200_backend* b);
+
+/* Backend::name(): "b200". */
+const char* rb200_name(const rb200_backend* b);
+int rb200_get_config(const rb200_backend* b, rb200_model_config* out);
+/* KVLayout (engine/include/relay/kv_cache.h:22-36): layers, kv_heads, head_dim, block_size, num_blocks. */
+int rb200_get_kv_layout(const rb200_backend* b, int32_t out[5]);
+
+/* LayerObserver::kv_written (backend.h:37-41): called on the calling thread right after
+ * layer `layer`'s K/V append is enqueued; pair with rb200_wait_kv_written. */
+typedef void (*rb200_layer_cb)(void* ctx, int layer);
+
+/* Backend::forward (backend.h:50-52; engine/src/cuda_backend.cu:504-603). The batch is
+ * relay::ForwardBatch flattened: chunk s has chunk_len[s] tokens (consecutive in `tokens`)
+ * starting at position start_pos[s], and table_len[s] block ids (consecutive in `tables`).
+ * want_logits may be NULL (all chunks want them). Writes [rows, vocab] float32 to
+ * logits_out (host memory; cap_floats is its capacity) and returns rows, or -1.
+ * Errors mirror the reference: "block table too short", "sequence longer than
+ * max_context", "batch has more tokens than max_batch_tokens" (invalid argument),
+ * "token id out of range" (out of range). An empty batch returns 0. */
+int rb200_forward(rb200_backend* b, int n_seqs, const int32_t* tokens, const int32_t* chunk_len,
+                  const int32_t* start_pos, const int32_t* table_len, const int32_t* tables,
+                  const uint8_t* want_logits, int all_logits, rb200_layer_cb cb, void* cb_ctx, float* logits_out,
+                  size_t cap_floats);
+
+/* The same forward pass, but instead of the logits it returns each logit row's greedy
+ * token (lowest id wins a tie: engine/src/sampler.cpp:17-22) and its logit, computed on
+ * the device, so that only 8 bytes per row cross to the host. Needs RB200_GPU_ARGMAX. */
+int rb200_forward_greedy(rb200_backend* b, int n_seqs, const int32_t* tokens, const int32_t* chunk_len,
+                         const int32_t* start_pos, const int32_t* table_len, const int32_t* tables,
+                         const uint8_t* want_logits, int all_logits, rb200_layer_cb cb, void* cb_ctx,
+                         int32_t* token_out, float* logit_out, size_t cap_rows);
+
+/* Backend::kv_block_bytes (engine/src/cuda_backend.cu:478): kv_heads * block_size * head_dim * 2. */
+size_t rb200_kv_block_bytes(const rb200_backend* b);
+/* Backend::read_kv_layer / write_kv_layer (backend.h:60-64; engine/src/cuda_backend.cu:630-664):
+ * `buf` is host memory holding all K blocks then all V blocks in the order given. n = 1
+ * with separate k/v pointers is read_kv_block / write_kv_block (backend.h:56-58). Safe to
+ * call from another thread while rb200_forward runs. */
+int rb200_read_kv_layer(rb200_backend* b, int layer, const int32_t* blocks, int n, void* k_out, void* v_out);
+int rb200_write_kv_layer(rb200_backend* b, int layer, const int32_t* blocks, int n, const void* k_in,
+                         const void* v_in);
+/* Backend::wait_kv_written (engine/src/cuda_backend.cu:502). */
+int rb200_wait_kv_written(rb200_backend* b, int layer);
+/* Backend::update_weight (backend.h:72-80; engine/src/cuda_backend.cu:429-477): `src` is
+ * n float32 values in relay's layout, in host memory or device memory of any GPU. Unlike
+ * the reference, an int8 backend requantises the matrix on the device instead of refusing. */
+int rb200_update_weight(rb200_backend* b, const char* name, const float* src, size_t n);
+
+/* ---- the prefill -> decode KV hop over NCCL ------------------------------------------ */
+/* Replaces the host-staged Layer payload of the transfer engine
+ * (engine/src/kv_transfer.cpp:107-128 sender, :289-297 receiver) on the GPU->GPU hop:
+ * gather kernel -> ncclSend on the sender, ncclRecv -> scatter kernel on the receiver,
+ * both on the backend's copy stream. Payload order is the wire format's: all K blocks,
+ * then all V blocks (engine/include/relay/kv_transfer.h:14-18). */
+
+#define RB200_NCCL_ID_BYTES 128
+/* Fills `id` (RB200_NCCL_ID_BYTES) on one rank; hand it to the others out of band. */
+int rb200_nccl_unique_id(void* id);
+/* Joins communicator of `nranks` as `rank`; collective across the ranks. */
+int rb200_nccl_init(rb200_backend* b, const void* id, int nranks, int rank);
+int rb200_nccl_finalize(rb200_backend* b);
+/* Enqueue one layer's blocks to / from `peer`; returns once enqueued on the copy stream. */
+int rb200_send_kv_layer(rb200_backend* b, int peer, int layer, const int32_t* blocks, int n);
+int rb200_recv_kv_layer(rb200_backend* b, int peer, int layer, const int32_t* blocks, int n);
+/* Waits for everything enqueued on the copy stream, at most timeout_ms (<= 0: no limit);
+ * on timeout the communicator is aborted and -1 returned. */
+int rb200_kv_hop_sync(rb200_backend* b, int timeout_ms);
+
+/* ---- operators on device buffers ----------------------------------------------------- */
+/* All pointers below are DEVICE pointers on the current device unless said otherwise;
+ * `stream` is a cudaStream_t (NULL: the default stream). Calls return once enqueued. */
+
+/* The batch's position metadata, engine/src/cuda_kernels.cuh:16-26 (TokenMeta): token t is
+ * at position pos[t] of sequence seq[t], whose block ids start at tables[table_off[seq]]. */
+typedef struct rb200_token_meta {
+  const int32_t* pos;
+  const int32_t* seq;
+  const int32_t* table_off;
+  const int32_t* tables;
+} rb200_token_meta;
+
+/* Geometry shared by the attention and KV operators. K and V pools are one layer's
+ * [num_blocks][kv_heads][block_size][head_dim] fp16 (engine/src/cuda_backend.cu:368-371). */
+typedef struct rb200_attn_shape {
+  int32_t heads, kv_heads, head_dim, block_size;
+  int32_t q_stride; /* floats between consecutive tokens' q rows (QKV in the model) */
+  int32_t o_stride; /* halves between consecutive tokens' output rows */
+} rb200_attn_shape;
+
+#define RB200_DECODE_SLICE 512 /* keys per split-context slice (engine/src/cuda_kernels.cuh:180-190) */
+
+/* Scratch the split decode needs for n_decode tokens whose longest context is max_ctx:
+ * per (token, head, slice) D + 2 floats. Returns bytes. */
+size_t rb200_decode_scratch_bytes(const rb200_attn_shape* s, int n_decode, int max_ctx);
+/* Split-context decode attention + LSE merge (replaces decode_attention_kernel and
+ * decode_combine_kernel, engine/src/cuda_kernels.cuh:223-362). q: fp32 rows of the batch
+ * (token t's head h at q + t*q_stride + h*D); decode_tokens[i] is the batch row of the
+ * i-th decode token, whose context is pos+1 keys; out: fp16 [T][o_stride]. */
+int rb200_decode_attention(const rb200_attn_shape* s, const float* q, const rb200_token_meta* m,
+                           const int32_t* decode_tokens, int n_decode, int max_ctx, const void* k_pool,
+                           const void* v_pool, void* scratch, size_t scratch_bytes, void* out, void* stream);
+
+/* Causal flash attention for chunks of several tokens over the paged cache (replaces
+ * flash_prefill_kernel, engine/src/cuda_kernels.cuh:51-178). tiles[i] = {first batch row,
+ * row count <= RB200_PREFILL_ROWS} as built by engine/src/cuda_backend.cu:533-545. */
+#define RB200_PREFILL_ROWS 64
+int rb200_prefill_attention(const rb200_attn_shape* s, const float* q, const rb200_token_meta* m,
+                            const int32_t* tiles, int n_tiles, const void* k_pool, const void* v_pool, void* out,
+                            void* stream);
+
+/* One CTA per (token, head) attention, any head_dim and group size (the role of the
+ * reference's M0 attention_kernel, engine/src/cuda_backend.cu:202-243). */
+int rb200_reference_attention(const rb200_attn_shape* s, const float* q, const rb200_token_meta* m, int n_tokens,
+                              const void* k_pool, const void* v_pool, void* out, void* stream);
+
+/* Weight-only int8 GEMV for 1..8 tokens (replaces gemv_int8_kernel,
+ * engine/src/cuda_kernels.cuh:378-430): y[T,N] = scale[n] * sum_k Wq[n,k] x[t,k] + beta*y.
+ * Wq int8 [N][ldw], x fp16 [T][ldx], y fp32 [T][N]; K, ldw, ldx multiples of 32.
+ * `scratch` (rb200_gemv_scratch_bytes) holds split-K partials and must be zero before its
+ * first use; the kernel leaves it zero again. */
+size_t rb200_gemv_scratch_bytes(int N, int K);
+int rb200_gemv_int8(const int8_t* wq, const float* scale, const void* x, float* y, int T, int K, int N, int ldw,
+                    int ldx, float beta, void* scratch, size_t scratch_bytes, void* stream);
+/* The same product for fp16 weights (the T <= 8 case of the reference's cublasGemmEx
+ * call, engine/src/cuda_backend.cu:724-730). */
+int rb200_gemv_f16(const void* w, const void* x, float* y, int T, int K, int N, int ldw, int ldx, float beta,
+                   void* scratch, size_t scratch_bytes, void* stream);
+
+/* y[T,N] = x[T,K] W[N,K]^T (+ beta*y) on tensor cores for any T: fp16 weights (replaces
+ * cublasGemmEx, engine/src/cuda_backend.cu:724-730) or int8 weights dequantised in the
+ * main loop (replaces dequant_int8_kernel + cuBLAS, engine/src/cuda_kernels.cuh:432-436,
+ * engine/src/cuda_backend.cu:719-721). Exactly one of w_f16 / w_i8 is non-NULL. */
+int rb200_gemm(const void* w_f16, const int8_t* w_i8, const float* scale, const void* x, float* y, int T, int K,
+               int N, int ldw, int ldx, float beta, void* stream);
+
+/* rmsnorm_kernel (engine/src/cuda_backend.cu:157-167): out[r] = w * x[rows ? rows[r] : r] * rsqrt(mean(x^2)+eps),
+ * fp32 -> fp16 rows of ld_out halves (columns H..ld_out-1 are written as zero). */
+int rb200_rmsnorm(const float* x, const int32_t* rows, const float* w, void* out, int R, int H, int ld_out,
+                  float eps, void* stream);
+/* embed_kernel (engine/src/cuda_backend.cu:150-154): x[t] = float(table[tokens[t]]). */
+int rb200_embed(const int32_t* tokens, const void* table, float* x, int T, int H, int ld_table, void* stream);
+/* qkv_post_kernel (engine/src/cuda_backend.cu:171-198): bias, RoPE on q and k in place,
+ * K/V append to the paged pools as fp16. bias may be NULL. */
+int rb200_qkv_post(float* qkv, const float* bias, const float* inv_freq, const rb200_token_meta* m, int T,
+                   void* k_pool, void* v_pool, int heads, int kv_heads, int head_dim, int block_size,
+                   void* stream);
+/* silu_mul_kernel (engine/src/cuda_backend.cu:245-253): act = silu(g) * u, fp32 [T][2I] -> fp16 [T][ld_act]. */
+int rb200_silu_mul(const float* gu, void* act, int T, int I, int ld_act, void* stream);
+/* f32_to_f16_kernel (engine/src/cuda_backend.cu:110-116): round to nearest even. */
+int rb200_f32_to_f16(const float* in, void* out, size_t n, void* stream);
+/* kv_gather_kernel / kv_scatter_kernel (engine/src/cuda_backend.cu:257-270): staging is
+ * [K of each block][V of each block]; block_bytes a multiple of 16. */
+int rb200_kv_gather(const void* k_pool, const void* v_pool, const int32_t* blocks, int n, size_t block_bytes,
+                    void* staging, void* stream);
+int rb200_kv_scatter(void* k_pool, void* v_pool, const int32_t* blocks, int n, size_t block_bytes,
+                     const void* staging, void* stream);
+/* Greedy token of each row of logits [R][V] (lowest id wins ties, engine/src/sampler.cpp:17-22). */
+int rb200_argmax_rows(const float* logits, int R, int V, int32_t* token_out, float* logit_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* RELAY_B200_H */
