@@ -1,0 +1,330 @@
+"""Benchmark of the per-token compute path: one decode step of a Llama-3-8B-shaped model.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step is one forward pass over a batch of single-token chunks: `--seqs` sequences (256)
+at context `--ctx` (4096) in the paged KV cache, fp16 weights (or `--int8`), random-init
+weights and N(0,1) cache contents of that architecture (no dataset is involved in this
+path; the reference's own benches draw random token ids). With N > 1 every rank is a
+full replica with its own 256 sequences (the path shards by sequence, no collective), so
+per-GPU work is fixed: weak scaling.
+
+Printed: ONE JSON line.
+  value      tokens/s of the whole job with the batch metadata already on the device and the
+             logits left there (CUDA events on the backend's stream, max over ranks)
+  e2e        the same through the reference-facing call (rb200_forward: host token / block
+             table arrays in, page-locked host logits out), wall clock around K calls
+  roofline   split-context decode attention, the dominant kernel: algorithmic bytes per
+             launch / its event-timed duration inside the same passes, against the measured
+             HBM copy bandwidth of MEASURED_PEAKS.json
+  cpu_baseline  relay's float32 CPU backend (oracle/_ref, else the C restatement) on a bounded
+             sample, on this box's host cores, rank 0 at N = 1 only
+`--impl reference` times only that CPU arm and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from relay_b200.types import ForwardBatch, HostWeights, ModelConfig, SeqChunk, flatten, tensor_shapes  # noqa: E402
+
+
+def llama3_8b(layers: int = 32, vocab: int = 128256, tie: bool = False) -> ModelConfig:
+    return ModelConfig(hidden=4096, intermediate=14336, layers=layers, heads=32, kv_heads=8, head_dim=128, vocab=vocab,
+                       max_position=8192, rms_eps=1e-5, rope_theta=500000.0, rope_scaling_type="llama3", rope_factor=8.0,
+                       rope_low_freq_factor=1.0, rope_high_freq_factor=4.0, rope_original_max_position=8192.0,
+                       tie_embeddings=tie)
+
+
+def decode_batch(seqs: int, ctx: int, bs: int, vocab: int, seed: int):
+    """`seqs` single-token chunks at position ctx-1; block tables are consecutive runs of a
+    seeded permutation of the pool."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    per = (ctx + bs - 1) // bs
+    perm = rng.permutation(seqs * per).astype(np.int32)
+    toks = rng.integers(0, vocab, seqs)
+    return ForwardBatch([SeqChunk([int(toks[i])], ctx - 1, perm[i * per:(i + 1) * per]) for i in range(seqs)])
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.12)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        mhz, mx, reasons = [], 0, set()
+        for r in self.rows:
+            try:
+                mhz.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def measured_peaks() -> tuple:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---- the CPU arm ---------------------------------------------------------------------------
+
+def cpu_arm(args, steps: int, warmup: int) -> dict:
+    """relay's CPU backend on a bounded sample of the decode workload: full widths and
+    vocabulary (tied head), `cpu_layers` layers, `cpu_seqs` sequences at the same context;
+    the full model's step time is extrapolated linearly in layers (stated in `sample`)."""
+    from oracle import oracle
+    L, S, ctx, bs = args.cpu_layers, args.cpu_seqs, args.ctx, 16
+    cfg = llama3_8b(layers=L, tie=True)
+    rng = np.random.Generator(np.random.PCG64(1))
+    tensors = {}
+    for name, shape in tensor_shapes(cfg).items():
+        if name.endswith("norm"):
+            tensors[name] = np.ones(shape, np.float32)
+        else:  # uniform with the std of N(0, 0.02): the values do not change the CPU's time
+            t = rng.random(shape, dtype=np.float32)
+            t -= 0.5
+            t *= 0.0693
+            tensors[name] = t
+    w = HostWeights(cfg, tensors)
+    per = (ctx + bs - 1) // bs
+    model = oracle.cpu_model(w, S * per, bs)
+    kind = "reference" if isinstance(model, oracle.RefModel) else "port"
+    n = model.kv_block_bytes() // 4
+    blk_k = (rng.random(n, dtype=np.float32) - 0.5).astype(np.float32)
+    for layer in range(L):
+        for b in range(S * per):
+            model.write_kv_block(layer, b, blk_k, blk_k)
+    batch = decode_batch(S, ctx, bs, cfg.vocab, 3)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        model.forward(batch)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    step = statistics.median(times)
+    # the head's share, timed alone, so that only the layers are scaled to the full depth
+    xr = rng.random((S, cfg.hidden), dtype=np.float32)
+    t0 = time.perf_counter()
+    oracle.matmul(xr, tensors["embed"])
+    head = min(time.perf_counter() - t0, step * 0.9)
+    full = (step - head) / L * args.layers + head
+    return {"value": S / full, "unit": "tok/s", "cores": os.cpu_count(), "kind": kind,
+            "sample": f"{S} sequences at context {ctx}, {L} of {args.layers} layers at full width and vocabulary: "
+                      f"{step * 1e3:.0f} ms per step measured ({head * 1e3:.0f} ms of it the LM head); layers scaled "
+                      f"linearly to {args.layers} -> {full * 1e3:.0f} ms per {S}-token step",
+            "ms_per_step_sample": step * 1e3}
+
+
+# ---- the GPU arm ---------------------------------------------------------------------------
+
+def gpu_arm(args) -> dict:
+    import torch
+    import torch.distributed as dist
+    from relay_b200 import _lib
+    from relay_b200.backend import Backend
+    from relay_b200.types import CudaOptions
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    cfg = llama3_8b(layers=args.layers)
+    bs, seqs, ctx = 16, args.seqs, args.ctx
+    per = (ctx + bs - 1) // bs
+    be = Backend(cfg, None, seqs * per, bs, device=local, max_batch_tokens=seqs, max_context=ctx,
+                 options=CudaOptions(int8_weights=args.int8))
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1000 + rank)
+    for name, shape in tensor_shapes(cfg).items():
+        t = torch.randn(shape, device="cuda", generator=gen) * 0.02
+        if name.endswith("norm"):
+            t += 1.0
+        be.update_weight(name, t.data_ptr(), t.numel())
+        del t
+    torch.cuda.empty_cache()
+    be.debug_fill_kv(77 + rank)
+
+    fb = flatten(decode_batch(seqs, ctx, bs, cfg.vocab, 5 + rank))
+    logits = torch.empty((seqs, cfg.vocab), dtype=torch.float32).pin_memory()
+    out = logits.numpy()
+    T = fb.n_tokens
+    T4, S4 = (T + 3) // 4 * 4, (fb.n_seqs + 3) // 4 * 4
+    h2d = (7 * T4 + S4 + fb.n_seqs * ((per + 3) // 4 * 4)) * 4
+    d2h = seqs * cfg.vocab * 4
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    L = _lib.lib()
+    for _ in range(args.warmup):
+        be.forward_flat(fb, out=out)
+
+    # e2e: the reference-facing call with host buffers, copies inside the timed region
+    barrier()
+    with ClockSampler(local) as clk_e2e:
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            be.forward_flat(fb, out=out)
+        barrier()
+        e2e_s = time.perf_counter() - t0
+    e2e_s = max_over_ranks(e2e_s)
+
+    # value: the same passes from device-resident metadata, timed with CUDA events
+    be.set_profiling(True)
+    be.take_profile()
+    barrier()
+    launches0 = L.rb200_kernel_launches()
+    with ClockSampler(local) as clk:
+        dev_ms = be.forward_replay(args.steps)
+        barrier()
+    launches = L.rb200_kernel_launches() - launches0
+    prof = be.take_profile()
+    be.set_profiling(False)
+    dev_ms = max_over_ranks(dev_ms)
+
+    ms_per_step = dev_ms / args.steps
+    value = seqs * world / (ms_per_step * 1e-3)
+    e2e_value = seqs * world / (e2e_s / args.steps)
+
+    # decode attention roofline: bytes the algorithm must move per launch (one layer, all sequences)
+    ctxs = [ctx] * seqs
+    attn_bytes = sum(ctxs) * (2 * cfg.kv_heads * cfg.head_dim * 2) + seqs * cfg.heads * cfg.head_dim * (4 + 2) + \
+        sum((c + bs - 1) // bs for c in ctxs) * 4
+    calls = max(int(prof["decode_attn_calls"]), 1)
+    attn_ms = prof["decode_attn_ms"] / calls
+    peak, peak_kind = measured_peaks()
+    achieved = attn_bytes / (attn_ms * 1e-3) / 1e9 if attn_ms > 0 else 0.0
+    weight_bytes = sum(int(np.prod(s)) for n, s in tensor_shapes(cfg).items() if n != "embed") * (1 if args.int8 else 2)
+    step_bytes = attn_bytes * cfg.layers + weight_bytes
+    line = {
+        "metric": "decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8w-f16" if args.int8 else "f16", "data": "synthetic",
+        "config": {"workload": f"llama3-8b-shape decode step: {seqs} sequences per GPU at context {ctx}, paged KV "
+                               f"(block 16), {cfg.layers} layers, {'int8' if args.int8 else 'fp16'} weights",
+                   "seqs_per_gpu": seqs, "context": ctx, "layers": cfg.layers, "parallelism": f"replicas x{world}",
+                   "l2": "per-step working set (KV + weights) is far larger than L2"},
+        "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_s / args.steps * 1e3},
+        "gpu_launches": int(launches),
+        "roofline": {"kernel": "decode_split_kernel<128> + decode_merge_kernel", "bound": "hbm", "achieved": achieved,
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if peak else None,
+                     "traffic": None, "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
+                     "launches_timed": calls,
+                     "share_of_step": prof["decode_attn_ms"] / prof["total_ms"] if prof["total_ms"] else None},
+        "step_roofline": {"algorithmic_bytes_per_step": step_bytes,
+                          "achieved_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9, "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak},
+        "clocks": clk.summary(), "clocks_e2e": clk_e2e.summary(),
+    }
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return {}
+    return line
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--seqs", type=int, default=256, help="sequences per GPU")
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--int8", action="store_true", help="weight-only int8 layer matrices")
+    ap.add_argument("--cpu-layers", type=int, default=2)
+    ap.add_argument("--cpu-seqs", type=int, default=8)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else max(args.warmup, 1)
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if args.gpus > 1 and "RANK" not in os.environ:
+        # not under a launcher: start one rank per GPU ourselves
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cpu = cpu_arm(args, args.steps, args.warmup)
+        line = {"impl": "reference", "metric": "decode_tok_per_s", "value": cpu["value"], "unit": "tok/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": cpu["ms_per_step_sample"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"llama3-8b-shape decode step: {args.seqs} sequences per GPU at context "
+                                       f"{args.ctx}, paged KV (block 16), {args.layers} layers, fp16 weights"},
+                "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": cpu["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
+
+    line = gpu_arm(args)
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            cpu = cpu_arm(args, 3, 1)
+            line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -151,6 +151,31 @@ int rb200_wait_kv_written(rb200_backend* b, int layer);
  * the reference, an int8 backend requantises the matrix on the device instead of refusing. */
 int rb200_update_weight(rb200_backend* b, const char* name, const float* src, size_t n);
 
+/* ---- measurement support (no counterpart in the reference: its benches time forward()
+ *      from the host, tools/relay_attention_bench.cpp:82-95) ------------------------------ */
+
+typedef struct rb200_profile {
+  double total_ms;        /* device time of the profiled forward passes, first to last kernel */
+  double decode_attn_ms;  /* of which split-context decode attention + merge */
+  double prefill_attn_ms; /* of which flash prefill attention */
+  uint64_t forwards, decode_attn_calls, prefill_attn_calls;
+} rb200_profile;
+
+/* While on, every forward pass brackets its attention launches with CUDA events on the
+ * backend's stream and adds their times to the profile. */
+int rb200_set_profiling(rb200_backend* b, int on);
+/* Returns the profile accumulated so far and clears it. */
+int rb200_get_profile(rb200_backend* b, rb200_profile* out);
+/* Enqueues the kernels of the latest rb200_forward `iters` times from the metadata already
+ * on the device (no host-to-device copy, logits stay on the device) and returns the device
+ * time of all of them in ms_out. Every pass recomputes the same values. */
+int rb200_forward_replay(rb200_backend* b, int iters, float* ms_out);
+/* Fills both KV pools with N(0,1) values rounded to fp16 from a counter-based generator:
+ * stands in for an untimed prefill when a benchmark needs a full cache. */
+int rb200_debug_fill_kv(rb200_backend* b, uint64_t seed);
+/* Kernels this library has launched in this process so far. */
+uint64_t rb200_kernel_launches(void);
+
 /* ---- the prefill -> decode KV hop over NCCL ------------------------------------------ */
 /* Replaces the host-staged Layer payload of the transfer engine
  * (engine/src/kv_transfer.cpp:107-128 sender, :289-297 receiver) on the GPU->GPU hop:

@@ -1,0 +1,214 @@
+"""Host-side mirror of `relay::Backend` (engine/include/relay/backend.h:43-81) over the C
+boundary: same methods, same argument meaning, same error behaviour (the reference's
+std::invalid_argument / std::out_of_range become ValueError / IndexError).
+
+    be = make_cuda_backend(weights, num_blocks, block_size, device, max_batch_tokens, max_context)
+    logits = be.forward(ForwardBatch([SeqChunk(tokens, start_pos, block_table)]))
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from . import _lib
+from .types import (CModelConfig, CudaOptions, FlatBatch, ForwardBatch, HostWeights, ModelConfig, flatten, i32, ptr)
+
+
+class KVLayout:
+    """relay::KVLayout (engine/include/relay/kv_cache.h:22-36)."""
+
+    def __init__(self, layers, kv_heads, head_dim, block_size, num_blocks):
+        self.layers, self.kv_heads, self.head_dim = layers, kv_heads, head_dim
+        self.block_size, self.num_blocks = block_size, num_blocks
+
+    def block_elems(self) -> int:
+        return self.kv_heads * self.block_size * self.head_dim
+
+    def offset(self, block: int, kv_head: int, slot: int) -> int:
+        return (block * self.kv_heads + kv_head) * self.block_size * self.head_dim + slot * self.head_dim
+
+    def blocks_for(self, tokens: int) -> int:
+        return (tokens + self.block_size - 1) // self.block_size
+
+
+class Backend:
+    def __init__(self, config: ModelConfig, weights: Optional[HostWeights], num_blocks: int, block_size: int,
+                 device: int = 0, max_batch_tokens: int = 1024, max_context: Optional[int] = None,
+                 options: Optional[CudaOptions] = None):
+        self._L = _lib.lib()
+        self._h = None
+        options = CudaOptions.from_env() if options is None else options
+        max_context = num_blocks * block_size if max_context is None else max_context
+        cc = config.to_c()
+        if weights is not None:
+            cw, keep = weights.to_c()
+            h = self._L.rb200_create(C.byref(cc), C.byref(cw), num_blocks, block_size, device, max_batch_tokens,
+                                     max_context, options.flags())
+            del keep
+        else:
+            h = self._L.rb200_create(C.byref(cc), None, num_blocks, block_size, device, max_batch_tokens, max_context,
+                                     options.flags())
+        if not h:
+            _lib.raise_last_error()
+        self._h = h
+        self._config = config
+        self._layout = KVLayout(config.layers, config.kv_heads, config.head_dim, block_size, num_blocks)
+        self.options = options
+
+    def close(self) -> None:
+        if self._h:
+            self._L.rb200_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- relay::Backend ---------------------------------------------------------------------
+    def config(self) -> ModelConfig:
+        return self._config
+
+    def kv_layout(self) -> KVLayout:
+        return self._layout
+
+    def name(self) -> str:
+        return self._L.rb200_name(self._h).decode()
+
+    def _cb(self, observer):
+        if observer is None:
+            return _lib.LAYER_CB(), None
+        fn = observer.kv_written if hasattr(observer, "kv_written") else observer
+        cb = _lib.LAYER_CB(lambda _ctx, layer: fn(layer))
+        return cb, cb
+
+    def forward_flat(self, fb: FlatBatch, observer=None, out: Optional[np.ndarray] = None) -> np.ndarray:
+        """forward() on an already flattened batch; `out` may be a caller-owned (for example
+        page-locked) float32 array of at least rows * vocab elements."""
+        V = self._config.vocab
+        rows = fb.n_rows
+        if out is None:
+            out = np.empty((max(rows, 1), V), np.float32)
+        cb, keep = self._cb(observer)
+        want = fb.want_logits.astype(np.uint8)
+        r = _lib.check(self._L.rb200_forward(
+            self._h, fb.n_seqs, ptr(fb.tokens), ptr(fb.chunk_len), ptr(fb.start_pos), ptr(fb.table_len), ptr(fb.tables),
+            ptr(want), int(fb.all_logits), cb, None, out.ctypes.data_as(C.c_void_p), out.size))
+        return out.reshape(-1)[: r * V].reshape(r, V)
+
+    def forward(self, batch: ForwardBatch, observer=None) -> np.ndarray:
+        """Backend::forward: [rows, vocab] float32, one row per chunk with want_logits (or per
+        token with all_logits). `observer.kv_written(layer)` is called as each layer's K/V
+        append is enqueued."""
+        return self.forward_flat(flatten(batch), observer)
+
+    def forward_greedy(self, batch: ForwardBatch, observer=None) -> Tuple[np.ndarray, np.ndarray]:
+        """The greedy token and its logit per logits row, reduced on the device."""
+        fb = flatten(batch)
+        rows = max(fb.n_rows, 1)
+        tok, val = np.empty(rows, np.int32), np.empty(rows, np.float32)
+        cb, keep = self._cb(observer)
+        want = fb.want_logits.astype(np.uint8)
+        r = _lib.check(self._L.rb200_forward_greedy(
+            self._h, fb.n_seqs, ptr(fb.tokens), ptr(fb.chunk_len), ptr(fb.start_pos), ptr(fb.table_len), ptr(fb.tables),
+            ptr(want), int(fb.all_logits), cb, None, ptr(tok), ptr(val), rows))
+        return tok[:r], val[:r]
+
+    def kv_block_bytes(self) -> int:
+        return self._L.rb200_kv_block_bytes(self._h)
+
+    def read_kv_block(self, layer: int, block: int) -> Tuple[np.ndarray, np.ndarray]:
+        bb = self.kv_block_bytes()
+        k, v = np.empty(bb, np.uint8), np.empty(bb, np.uint8)
+        _lib.check(self._L.rb200_read_kv_layer(self._h, layer, ptr(i32([block])), 1, ptr(k), ptr(v)))
+        return k, v
+
+    def write_kv_block(self, layer: int, block: int, k: np.ndarray, v: np.ndarray) -> None:
+        k, v = np.ascontiguousarray(k).view(np.uint8), np.ascontiguousarray(v).view(np.uint8)
+        if k.size != self.kv_block_bytes() or v.size != k.size:
+            raise ValueError("write_kv_block: wrong block size")
+        _lib.check(self._L.rb200_write_kv_layer(self._h, layer, ptr(i32([block])), 1, ptr(k), ptr(v)))
+
+    def read_kv_layer(self, layer: int, blocks: Sequence[int]) -> np.ndarray:
+        """All K blocks then all V blocks, in the order given (the transfer engine's payload)."""
+        b = i32(blocks)
+        bb = self.kv_block_bytes()
+        out = np.empty(2 * b.size * bb, np.uint8)
+        k = out.ctypes.data
+        _lib.check(self._L.rb200_read_kv_layer(self._h, layer, ptr(b), b.size, C.c_void_p(k), C.c_void_p(k + b.size * bb)))
+        return out
+
+    def write_kv_layer(self, layer: int, blocks: Sequence[int], data: np.ndarray) -> None:
+        b = i32(blocks)
+        bb = self.kv_block_bytes()
+        data = np.ascontiguousarray(data).view(np.uint8).ravel()
+        if data.size != 2 * b.size * bb:
+            raise ValueError("write_kv_layer: wrong payload size")
+        k = data.ctypes.data
+        _lib.check(self._L.rb200_write_kv_layer(self._h, layer, ptr(b), b.size, C.c_void_p(k), C.c_void_p(k + b.size * bb)))
+
+    def kv_host_ptr(self, layer: int, block: int, value: bool):
+        return None  # the cache is not in host memory (backend.h:66-68)
+
+    def wait_kv_written(self, layer: int) -> None:
+        _lib.check(self._L.rb200_wait_kv_written(self._h, layer))
+
+    def update_weight(self, name: str, src, n: Optional[int] = None) -> None:
+        """`src`: a float32 numpy array, or a raw address (host or any GPU) with `n` elements."""
+        if isinstance(src, np.ndarray):
+            a = np.ascontiguousarray(src, dtype=np.float32)
+            _lib.check(self._L.rb200_update_weight(self._h, name.encode(), ptr(a), a.size))
+        else:
+            _lib.check(self._L.rb200_update_weight(self._h, name.encode(), C.c_void_p(int(src)), int(n)))
+
+    # -- measurement support ------------------------------------------------------------------
+    def set_profiling(self, on: bool) -> None:
+        _lib.check(self._L.rb200_set_profiling(self._h, int(on)))
+
+    def take_profile(self) -> dict:
+        p = _lib.CProfile()
+        _lib.check(self._L.rb200_get_profile(self._h, C.byref(p)))
+        return {k: getattr(p, k) for k, _ in p._fields_}
+
+    def forward_replay(self, iters: int) -> float:
+        """Device milliseconds of `iters` re-runs of the last forward pass's kernels."""
+        ms = C.c_float(0)
+        _lib.check(self._L.rb200_forward_replay(self._h, iters, C.byref(ms)))
+        return ms.value
+
+    def debug_fill_kv(self, seed: int) -> None:
+        _lib.check(self._L.rb200_debug_fill_kv(self._h, seed))
+
+    # -- the NCCL KV hop ----------------------------------------------------------------------
+    @staticmethod
+    def nccl_unique_id() -> bytes:
+        buf = C.create_string_buffer(_lib.NCCL_ID_BYTES)
+        _lib.check(_lib.lib().rb200_nccl_unique_id(buf))
+        return buf.raw
+
+    def nccl_init(self, uid: bytes, nranks: int, rank: int) -> None:
+        _lib.check(self._L.rb200_nccl_init(self._h, C.c_char_p(uid), nranks, rank))
+
+    def nccl_finalize(self) -> None:
+        _lib.check(self._L.rb200_nccl_finalize(self._h))
+
+    def send_kv_layer(self, peer: int, layer: int, blocks: Sequence[int]) -> None:
+        b = i32(blocks)
+        _lib.check(self._L.rb200_send_kv_layer(self._h, peer, layer, ptr(b), b.size))
+
+    def recv_kv_layer(self, peer: int, layer: int, blocks: Sequence[int]) -> None:
+        b = i32(blocks)
+        _lib.check(self._L.rb200_recv_kv_layer(self._h, peer, layer, ptr(b), b.size))
+
+    def kv_hop_sync(self, timeout_ms: int = 0) -> None:
+        _lib.check(self._L.rb200_kv_hop_sync(self._h, timeout_ms))
+
+
+def make_cuda_backend(weights: HostWeights, num_blocks: int, block_size: int, device: int = 0,
+                      max_batch_tokens: int = 1024, max_context: Optional[int] = None,
+                      options: Optional[CudaOptions] = None) -> Backend:
+    """relay::make_cuda_backend (engine/include/relay/backend.h:95-97)."""
+    return Backend(weights.config, weights, num_blocks, block_size, device, max_batch_tokens, max_context, options)

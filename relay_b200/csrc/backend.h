@@ -1,0 +1,168 @@
+// The backend object behind the rb200_* handle: device weights, the paged KV pools, the
+// activation buffers and the two streams, with the same responsibilities and threading
+// rules as the reference's CudaBackend (engine/src/cuda_backend.cu:311-759): forward() is
+// called by one thread at a time; KV layer reads/writes may come from other threads at any
+// time and run on their own stream under copy_mu_.
+#pragma once
+
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "kernels.h"
+
+namespace rb200 {
+
+// Device memory with RAII; zero-filled on allocation when asked.
+struct DeviceBuf {
+  void* p = nullptr;
+  size_t bytes = 0;
+  DeviceBuf() = default;
+  explicit DeviceBuf(size_t n, bool zero = false);
+  ~DeviceBuf();
+  DeviceBuf(DeviceBuf&& o) noexcept : p(o.p), bytes(o.bytes) { o.p = nullptr; o.bytes = 0; }
+  DeviceBuf& operator=(DeviceBuf&& o) noexcept;
+  DeviceBuf(const DeviceBuf&) = delete;
+  DeviceBuf& operator=(const DeviceBuf&) = delete;
+  template <class T>
+  T* as() const { return static_cast<T*>(p); }
+  void ensure(size_t n);  // regrow (contents lost) when smaller than n
+};
+
+struct PinnedBuf {
+  void* p = nullptr;
+  size_t bytes = 0;
+  ~PinnedBuf();
+  void ensure(size_t n);
+  template <class T>
+  T* as() const { return static_cast<T*>(p); }
+};
+
+// A weight matrix [N][ld]: fp16, or int8 + per-row scale. Columns K..ld-1 are zero.
+struct Matrix {
+  int N = 0, K = 0, ld = 0;
+  bool int8 = false;
+  DeviceBuf data, scale;
+  WeightView view() const;
+};
+
+struct Layer {
+  DeviceBuf attn_norm, mlp_norm, bqkv;
+  Matrix wqkv, wo, w_gate_up, w_down;
+};
+
+// The NCCL communicator of the KV hop (an ncclComm_t, kept opaque here).
+struct NcclState {
+  void* comm = nullptr;
+  int nranks = 0, rank = -1;
+};
+
+class Backend {
+ public:
+  Backend(const rb200_model_config& cfg, const rb200_weights* w, int num_blocks, int block_size, int device,
+          int max_batch_tokens, int max_context, uint32_t flags);
+  ~Backend();
+
+  const rb200_model_config& config() const { return c_; }
+  int num_blocks() const { return num_blocks_; }
+  int block_size() const { return block_size_; }
+  size_t kv_block_bytes() const { return static_cast<size_t>(c_.kv_heads) * block_size_ * c_.head_dim * 2; }
+  long long layer_elems() const { return static_cast<long long>(c_.kv_heads) * block_size_ * c_.head_dim * num_blocks_; }
+
+  // Returns the number of logit rows. Exactly one of logits_out / token_out is used.
+  int forward(int n_seqs, const int32_t* tokens, const int32_t* chunk_len, const int32_t* start_pos,
+              const int32_t* table_len, const int32_t* tables, const uint8_t* want_logits, bool all_logits,
+              rb200_layer_cb cb, void* cb_ctx, float* logits_out, size_t cap_floats, int32_t* token_out,
+              float* logit_out, size_t cap_rows);
+
+  void read_kv_layer(int layer, const int32_t* blocks, int n, void* k_out, void* v_out);
+  void write_kv_layer(int layer, const int32_t* blocks, int n, const void* k_in, const void* v_in);
+  void wait_kv_written(int layer);
+  void update_weight(const std::string& name, const float* src, size_t n);
+
+  // measurement support
+  void set_profiling(bool on);
+  rb200_profile take_profile();
+  float replay(int iters);  // re-enqueues the last forward pass's kernels; returns device milliseconds
+  void debug_fill_kv(unsigned long long seed);
+
+  // kv_hop.cu
+  void nccl_init(const void* id, int nranks, int rank);
+  void nccl_finalize();
+  void send_kv_layer(int peer, int layer, const int32_t* blocks, int n);
+  void recv_kv_layer(int peer, int layer, const int32_t* blocks, int n);
+  void kv_hop_sync(int timeout_ms);
+  void nccl_finalize_noexcept() noexcept;
+
+ private:
+  void set_device() const;
+  void check_layer(int layer) const;
+  void check_blocks(const int32_t* blocks, int n) const;
+  void upload_matrix(Matrix& m, const float* src_any, int N, int K);
+  void upload_vector(DeviceBuf& dst, const float* src_any, size_t n);
+  Matrix make_matrix(int N, int K, bool int8);
+  // Feeds src (host, or device memory of any GPU) to apply(dev_ptr, first_row, rows) as
+  // float32 rows resident on this device, staging through stage_ when it is not local.
+  template <class F>
+  void for_row_chunks(const float* src, int rows, int cols, F&& apply);
+  void* staging_ids(const int32_t* blocks, int n);  // under copy_mu_: block ids on the device
+  void ensure_kv_staging(size_t n_blocks);
+
+  // What the last forward pass flattened: enough to enqueue its kernels again.
+  struct Plan {
+    int T = 0, R = 0, n_decode = 0, n_tiles = 0, max_ctx = 0;
+    size_t T4 = 0, S4 = 0;
+  };
+  // Event marks of one pass while profiling is on.
+  struct Prof {
+    bool on = false;
+    int first = 0, n = 0;
+  };
+  enum { kMarkStart, kMarkEnd, kMarkDecodeBegin, kMarkDecodeEnd, kMarkPrefillBegin, kMarkPrefillEnd };
+  void enqueue(const Plan& p, rb200_layer_cb cb, void* cb_ctx, bool argmax, Prof* prof);
+  Prof begin_profile();
+  void mark(Prof& p, int kind);
+  void end_profile(Prof& p);
+
+  Plan plan_;
+  bool profiling_ = false;
+  rb200_profile profile_{};
+  std::vector<cudaEvent_t> prof_events_;
+  std::vector<int> prof_kinds_;
+
+  rb200_model_config c_;
+  uint32_t flags_;
+  int device_, num_blocks_, block_size_, max_tokens_, max_context_;
+  int Hp_, Qp_, Ip_;  // hidden, q_dim and intermediate rounded up to the GEMM's k granularity
+  bool fast_attention_ = false;
+  cudaStream_t stream_ = nullptr, copy_stream_ = nullptr;
+  std::vector<cudaEvent_t> layer_done_;
+
+  Matrix embed_, lm_head_;
+  DeviceBuf final_norm_, inv_freq_;
+  std::vector<Layer> layers_;
+  DeviceBuf kc_, vc_;
+
+  DeviceBuf x_, xn_, qkv_, attn_, gu_, act_, logits_, argmax_tok_, argmax_val_;
+  DeviceBuf meta_dev_, decode_scratch_, gemv_scratch_, stage_;
+  PinnedBuf meta_host_, result_host_;
+
+  std::mutex copy_mu_;
+  DeviceBuf kv_staging_, kv_ids_;
+  PinnedBuf kv_pinned_;
+  // Block ids travel host -> device through a small ring of pinned slots, so that calls
+  // which only enqueue (the NCCL hop) can run ahead of the copy stream without a later
+  // call overwriting ids an earlier upload has not read yet.
+  struct IdSlot {
+    PinnedBuf buf;
+    cudaEvent_t uploaded = nullptr;
+    bool used = false;
+  };
+  std::vector<IdSlot> id_slots_;
+  int id_next_ = 0;
+
+  std::unique_ptr<NcclState> nccl_;
+};
+
+}  // namespace rb200

@@ -1,0 +1,463 @@
+// The linear layers: y[T,N] = x[T,K] W[N,K]^T (+ beta*y), W fp16 or weight-only int8 with
+// one fp32 scale per output row, x fp16, y fp32.
+//
+//  * gemv_kernel (T <= 8) — replaces gemv_int8_kernel (engine/src/cuda_kernels.cuh:378-430)
+//    and the small-T case of cublasGemmEx (engine/src/cuda_backend.cu:724-730). Bound by
+//    weight bandwidth: every weight byte is read from HBM exactly once, straight into
+//    registers with 16-byte loads (no shared-memory round trip), converted int8 -> fp16 with
+//    byte permutes, and multiplied on the tensor cores with the 8 tokens on the N axis of
+//    m16n8k16, so the arithmetic never competes with the load stream. The k order inside an
+//    instruction is permuted (legal for a dot product) so that a thread's 16 contiguous
+//    weight bytes feed four instructions. Small N is split along K across CTAs; the last
+//    CTA of a row block to finish adds the partials in a fixed order, so results are
+//    deterministic.
+//  * gemm_kernel (T > 8) — replaces dequant_int8_kernel + cuBLAS (engine/src/cuda_kernels.cuh:432-436,
+//    engine/src/cuda_backend.cu:719-721) and cublasGemmEx for fp16 weights: weights on the M
+//    axis, tokens on N, int8 dequantised on its way into shared memory (the fp16 copy of the
+//    matrix is never materialised in HBM), scale and residual applied in the epilogue.
+#include "kernels.h"
+
+namespace rb200 {
+
+namespace {
+
+// ---- int8 -> fp16 -----------------------------------------------------------------------
+
+// Four signed bytes -> two half2 (exact): flip the sign bit (v + 128 as an unsigned byte),
+// splice the byte under the exponent of 1024.0 (0x6400 | b = 1024 + b), subtract 1152.
+__device__ __forceinline__ void cvt_s8x4_f16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t u = w ^ 0x80808080u;
+  uint32_t a, b;
+  asm("prmt.b32 %0, %1, %2, 0x4140;" : "=r"(a) : "r"(u), "r"(0x64646464u));
+  asm("prmt.b32 %0, %1, %2, 0x4342;" : "=r"(b) : "r"(u), "r"(0x64646464u));
+  const __half2 bias = __half2half2(__ushort_as_half(0x6480));  // 1152.0
+  __half2 ha = __hsub2(*reinterpret_cast<__half2*>(&a), bias);
+  __half2 hb = __hsub2(*reinterpret_cast<__half2*>(&b), bias);
+  lo = *reinterpret_cast<uint32_t*>(&ha);
+  hi = *reinterpret_cast<uint32_t*>(&hb);
+}
+
+// ---- GEMV (T <= 8) -------------------------------------------------------------------------
+
+constexpr int kGemvWarps = 4;            // 16 output rows each
+constexpr int kGemvRows = kGemvWarps * 16;
+constexpr int kGemvMaxChunk = 2048;      // K values of x staged per CTA
+
+constexpr __host__ __device__ int gemv_x_pad(bool int8) { return int8 ? 8 : 32; }
+
+struct GemvPlan {
+  int row_blocks, splits, chunk;
+};
+
+GemvPlan plan_gemv(int N, int K) {
+  GemvPlan p;
+  p.row_blocks = div_up(N, kGemvRows);
+  const int want = std::max(div_up(2 * sm_count(), p.row_blocks), div_up(K, kGemvMaxChunk));
+  const int splits = std::max(1, std::min(want, K / 64));
+  p.chunk = round_up(div_up(K, splits), 64);
+  p.splits = div_up(K, p.chunk);
+  return p;
+}
+
+// Scratch: [row_blocks] arrival counters (padded to 256 B), then partials [splits][N][8] floats.
+size_t gemv_counter_bytes(int N) { return static_cast<size_t>(round_up(div_up(N, kGemvRows) * 4, 256)); }
+
+template <bool INT8>
+__global__ void __launch_bounds__(kGemvWarps * 32)
+gemv_kernel(const void* __restrict__ wv, const float* __restrict__ scale, const __half* __restrict__ x,
+            float* __restrict__ y, int T, int K, int N, int ldw, int ldx, float beta, int chunk, int splits,
+            unsigned* __restrict__ counters, float* __restrict__ partials) {
+  // x[8][chunk] halves, each row padded (16 bytes for int8 weights, 64 for fp16) so that the
+  // token rows a quarter-warp reads with 16-byte loads fall into different bank groups.
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ unsigned s_last;
+  const int xs_stride = chunk + gemv_x_pad(INT8);  // halves
+  __half* xs = reinterpret_cast<__half*>(smem_raw);
+
+  const int rb = blockIdx.x, split = blockIdx.y;
+  const int kb0 = split * chunk, kb1 = min(K, kb0 + chunk);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+
+  // stage x[:, kb0:kb1) (rows >= T are zero)
+  for (int idx = threadIdx.x; idx < 8 * (chunk / 8); idx += blockDim.x) {
+    const int t = idx / (chunk / 8), c = idx - t * (chunk / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < T && kb0 + c * 8 < kb1) v = *reinterpret_cast<const uint4*>(x + static_cast<long long>(t) * ldx + kb0 + c * 8);
+    *reinterpret_cast<uint4*>(xs + t * xs_stride + c * 8) = v;
+  }
+  __syncthreads();
+
+  const int row_a = min(rb * kGemvRows + warp * 16 + g, N - 1);      // clamped: extra rows are never stored
+  const int row_b = min(rb * kGemvRows + warp * 16 + g + 8, N - 1);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+
+  if constexpr (INT8) {
+    const int8_t* w = static_cast<const int8_t*>(wv);
+    const int8_t* wa = w + static_cast<long long>(row_a) * ldw + 16 * t4;
+    const int8_t* wb = w + static_cast<long long>(row_b) * ldw + 16 * t4;
+    const __half* xg = xs + g * xs_stride + 16 * t4;
+    constexpr int U = 4;  // 64-wide k blocks in flight per thread
+    int k = kb0;
+    for (; k + 64 * U <= kb1; k += 64 * U) {
+      uint4 ra[U], rbv[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        ra[u] = __ldcs(reinterpret_cast<const uint4*>(wa + k + 64 * u));
+        rbv[u] = __ldcs(reinterpret_cast<const uint4*>(wb + k + 64 * u));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint4 x0 = *reinterpret_cast<const uint4*>(xg + (k - kb0) + 64 * u);
+        const uint4 x1 = *reinterpret_cast<const uint4*>(xg + (k - kb0) + 64 * u + 8);
+        const uint32_t wa4[4] = {ra[u].x, ra[u].y, ra[u].z, ra[u].w}, wb4[4] = {rbv[u].x, rbv[u].y, rbv[u].z, rbv[u].w};
+        const uint32_t xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint32_t a[4];
+          cvt_s8x4_f16x4(wa4[i], a[0], a[2]);
+          cvt_s8x4_f16x4(wb4[i], a[1], a[3]);
+          mma_f16(acc, a, xb[2 * i], xb[2 * i + 1]);
+        }
+      }
+    }
+    for (; k < kb1; k += 64) {
+      const uint4 ra = __ldcs(reinterpret_cast<const uint4*>(wa + k));
+      const uint4 rbv = __ldcs(reinterpret_cast<const uint4*>(wb + k));
+      const uint4 x0 = *reinterpret_cast<const uint4*>(xg + (k - kb0));
+      const uint4 x1 = *reinterpret_cast<const uint4*>(xg + (k - kb0) + 8);
+      const uint32_t wa4[4] = {ra.x, ra.y, ra.z, ra.w}, wb4[4] = {rbv.x, rbv.y, rbv.z, rbv.w};
+      const uint32_t xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t a[4];
+        cvt_s8x4_f16x4(wa4[i], a[0], a[2]);
+        cvt_s8x4_f16x4(wb4[i], a[1], a[3]);
+        mma_f16(acc, a, xb[2 * i], xb[2 * i + 1]);
+      }
+    }
+  } else {
+    const __half* w = static_cast<const __half*>(wv);
+    const __half* wa = w + static_cast<long long>(row_a) * ldw + 8 * t4;
+    const __half* wb = w + static_cast<long long>(row_b) * ldw + 8 * t4;
+    const __half* xg = xs + g * xs_stride + 8 * t4;
+    constexpr int U = 4;  // 32-wide k blocks in flight per thread
+    int k = kb0;
+    for (; k + 32 * U <= kb1; k += 32 * U) {
+      uint4 ra[U], rbv[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        ra[u] = __ldcs(reinterpret_cast<const uint4*>(wa + k + 32 * u));
+        rbv[u] = __ldcs(reinterpret_cast<const uint4*>(wb + k + 32 * u));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(xg + (k - kb0) + 32 * u);
+        const uint32_t a0[4] = {ra[u].x, rbv[u].x, ra[u].y, rbv[u].y}, a1[4] = {ra[u].z, rbv[u].z, ra[u].w, rbv[u].w};
+        mma_f16(acc, a0, xv.x, xv.y);
+        mma_f16(acc, a1, xv.z, xv.w);
+      }
+    }
+    for (; k < kb1; k += 32) {
+      const uint4 ra = __ldcs(reinterpret_cast<const uint4*>(wa + k));
+      const uint4 rbv = __ldcs(reinterpret_cast<const uint4*>(wb + k));
+      const uint4 xv = *reinterpret_cast<const uint4*>(xg + (k - kb0));
+      const uint32_t a0[4] = {ra.x, rbv.x, ra.y, rbv.y}, a1[4] = {ra.z, rbv.z, ra.w, rbv.w};
+      mma_f16(acc, a0, xv.x, xv.y);
+      mma_f16(acc, a1, xv.z, xv.w);
+    }
+  }
+
+  // acc[0], acc[1]: row g, tokens 2*t4, 2*t4+1; acc[2], acc[3]: row g + 8.
+  const int n_a = rb * kGemvRows + warp * 16 + g, n_b = n_a + 8;
+  const int tok = 2 * t4;
+  auto finish = [&](int n, float v0, float v1) {
+    if (n >= N) return;
+    const float sc = INT8 ? scale[n] : 1.0f;
+    if (tok < T) {
+      float* d = y + static_cast<long long>(tok) * N + n;
+      *d = beta != 0.f ? v0 * sc + beta * *d : v0 * sc;
+    }
+    if (tok + 1 < T) {
+      float* d = y + static_cast<long long>(tok + 1) * N + n;
+      *d = beta != 0.f ? v1 * sc + beta * *d : v1 * sc;
+    }
+  };
+  if (splits == 1) {
+    finish(n_a, acc[0], acc[1]);
+    finish(n_b, acc[2], acc[3]);
+    return;
+  }
+  // Split K: park this CTA's partial sums, then the last CTA of the row block to arrive
+  // adds all of them in split order.
+  float* mine = partials + static_cast<long long>(split) * N * 8;
+  if (n_a < N) *reinterpret_cast<float2*>(mine + static_cast<long long>(n_a) * 8 + tok) = make_float2(acc[0], acc[1]);
+  if (n_b < N) *reinterpret_cast<float2*>(mine + static_cast<long long>(n_b) * 8 + tok) = make_float2(acc[2], acc[3]);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned seen = atomicAdd(&counters[rb], 1u);
+    s_last = seen == static_cast<unsigned>(splits - 1);
+    if (s_last) counters[rb] = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* p = partials + static_cast<long long>(s) * N * 8;
+    if (n_a < N) {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(p + static_cast<long long>(n_a) * 8 + tok));
+      s0 += v.x;
+      s1 += v.y;
+    }
+    if (n_b < N) {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(p + static_cast<long long>(n_b) * 8 + tok));
+      s2 += v.x;
+      s3 += v.y;
+    }
+  }
+  finish(n_a, s0, s1);
+  finish(n_b, s2, s3);
+}
+
+// ---- GEMM (T > 8) --------------------------------------------------------------------------
+
+constexpr int kBM = 128;  // weight rows per CTA
+constexpr int kBN = 64;   // tokens per CTA
+constexpr int kBK = 64;   // k per shared-memory tile (128-byte fp16 rows)
+
+template <bool INT8>
+__global__ void __launch_bounds__(256)
+gemm_kernel(const void* __restrict__ wv, const float* __restrict__ scale, const __half* __restrict__ x,
+            float* __restrict__ y, int T, int K, int N, int ldw, int ldx, float beta) {
+  // two stages of: A tile [kBM][kBK] fp16, B tile [kBN][kBK] fp16, both swizzled (8 chunks per row)
+  __shared__ __align__(128) __half sA[2][kBM * kBK];
+  __shared__ __align__(128) __half sB[2][kBN * kBK];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  const int wm = warp >> 1, wn = warp & 1;  // 4 x 2 warps, each 32 rows x 32 tokens
+  const int n0 = blockIdx.x * kBM, tok0 = blockIdx.y * kBN;
+
+  // Global -> register prefetch of one k tile; int8 weights are widened on the way to shared memory.
+  uint4 ra[INT8 ? 2 : 4];
+  uint4 rx[2];
+  auto fetch = [&](int kt) {
+    const int k0 = kt * kBK;
+    if constexpr (INT8) {
+      // 128 rows x 64 bytes: thread -> row tid/2, 32-byte half (tid & 1)
+      const int r = tid >> 1, h = tid & 1;
+      const int8_t* src = static_cast<const int8_t*>(wv) + static_cast<long long>(min(n0 + r, N - 1)) * ldw + k0 + h * 32;
+      ra[0] = *reinterpret_cast<const uint4*>(src);
+      ra[1] = *reinterpret_cast<const uint4*>(src + 16);
+    } else {
+      // 128 rows x 128 bytes: thread -> row tid/2, 64-byte half
+      const int r = tid >> 1, h = tid & 1;
+      const __half* src = static_cast<const __half*>(wv) + static_cast<long long>(min(n0 + r, N - 1)) * ldw + k0 + h * 32;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ra[i] = *reinterpret_cast<const uint4*>(src + i * 8);
+    }
+    // x: 64 tokens x 128 bytes: thread -> token tid/4, 32-byte quarter
+    const int r = tid >> 2, qd = tid & 3;
+    if (tok0 + r < T) {
+      const __half* src = x + static_cast<long long>(tok0 + r) * ldx + k0 + qd * 16;
+      rx[0] = *reinterpret_cast<const uint4*>(src);
+      rx[1] = *reinterpret_cast<const uint4*>(src + 8);
+    } else {
+      rx[0] = rx[1] = make_uint4(0, 0, 0, 0);
+    }
+  };
+  auto stash = [&](int stage) {
+    const int r = tid >> 1, h = tid & 1;
+    uint4* a = reinterpret_cast<uint4*>(sA[stage]);
+    if constexpr (INT8) {
+      const uint32_t w8[8] = {ra[0].x, ra[0].y, ra[0].z, ra[0].w, ra[1].x, ra[1].y, ra[1].z, ra[1].w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {  // 8 weights per 16-byte fp16 chunk
+        uint4 o;
+        cvt_s8x4_f16x4(w8[2 * c], o.x, o.y);
+        cvt_s8x4_f16x4(w8[2 * c + 1], o.z, o.w);
+        a[swz<8>(r, h * 4 + c)] = o;
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) a[swz<8>(r, h * 4 + c)] = ra[c];
+    }
+    const int rr = tid >> 2, qd = tid & 3;
+    uint4* b = reinterpret_cast<uint4*>(sB[stage]);
+    b[swz<8>(rr, qd * 2)] = rx[0];
+    b[swz<8>(rr, qd * 2 + 1)] = rx[1];
+  };
+
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+
+  const int nkt = K / kBK;
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  for (int kt = 0; kt < nkt; ++kt) {
+    const int stage = kt & 1;
+    if (kt + 1 < nkt) fetch(kt + 1);
+    const uint32_t a_base = smem_u32(sA[stage]), b_base = smem_u32(sB[stage]);
+#pragma unroll
+    for (int ks = 0; ks < kBK / 16; ++ks) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        // A fragment of rows wm*32 + i*16 ..: matrices (rows 0-7, k lo), (rows 8-15, k lo), (rows 0-7, k hi), (rows 8-15, k hi)
+        const int row = wm * 32 + i * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        ldmatrix_x4(af[i], a_base + swz<8>(row, 2 * ks + (lane >> 4)) * 16);
+      }
+#pragma unroll
+      for (int jp = 0; jp < 2; ++jp) {
+        uint32_t bf[4];
+        const int row = wn * 32 + jp * 16 + (lane & 7) + ((lane >> 4) << 3);
+        ldmatrix_x4(bf, b_base + swz<8>(row, 2 * ks + ((lane >> 3) & 1)) * 16);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          mma_f16(acc[i][2 * jp], af[i], bf[0], bf[1]);
+          mma_f16(acc[i][2 * jp + 1], af[i], bf[2], bf[3]);
+        }
+      }
+    }
+    if (kt + 1 < nkt) stash(stage ^ 1);
+    __syncthreads();
+  }
+
+  // epilogue: acc[i][j][0,1] = (row g, tokens 2*t4, +1), [2,3] = row g + 8
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+      const int n = n0 + wm * 32 + i * 16 + g + hrow * 8;
+      if (n >= N) continue;
+      const float sc = INT8 ? scale[n] : 1.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int tok = tok0 + wn * 32 + j * 8 + 2 * t4 + e;
+          if (tok >= T) continue;
+          float* d = y + static_cast<long long>(tok) * N + n;
+          const float v = acc[i][j][hrow * 2 + e] * sc;
+          *d = beta != 0.f ? v + beta * *d : v;
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+
+size_t gemv_scratch_bytes(int N, int K) {
+  const GemvPlan p = plan_gemv(N, K);
+  return gemv_counter_bytes(N) + (p.splits > 1 ? static_cast<size_t>(p.splits) * N * 8 * sizeof(float) : 0);
+}
+
+static void check_linear(const WeightView& W, int ldx, int T) {
+  RB_REQUIRE((W.f16 != nullptr) != (W.i8 != nullptr), "linear: exactly one of fp16 / int8 weights");
+  RB_REQUIRE(W.i8 == nullptr || W.scale != nullptr, "linear: int8 weights need row scales");
+  RB_REQUIRE(W.N > 0 && W.K > 0 && W.K % 64 == 0, "linear: K must be a positive multiple of 64 (pad with zeros)");
+  RB_REQUIRE(W.ld >= W.K && W.ld % 16 == 0 && ldx >= W.K && ldx % 8 == 0, "linear: row strides must be 16-byte aligned");
+  RB_REQUIRE(T >= 0, "linear: bad token count");
+}
+
+void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch,
+                 size_t scratch_bytes, cudaStream_t st) {
+  check_linear(W, ldx, T);
+  RB_REQUIRE(T <= 8, "gemv: at most 8 tokens");
+  if (T == 0) return;
+  const GemvPlan p = plan_gemv(W.N, W.K);
+  RB_REQUIRE(p.splits == 1 || (scratch != nullptr && scratch_bytes >= gemv_scratch_bytes(W.N, W.K)),
+             "gemv: scratch too small");
+  unsigned* counters = static_cast<unsigned*>(scratch);
+  float* partials = scratch ? reinterpret_cast<float*>(static_cast<char*>(scratch) + gemv_counter_bytes(W.N)) : nullptr;
+  const size_t smem = static_cast<size_t>(8) * (p.chunk + gemv_x_pad(W.i8 != nullptr)) * sizeof(__half);
+  dim3 grid(p.row_blocks, p.splits);
+  count_launch();
+  if (W.i8)
+    gemv_kernel<true><<<grid, kGemvWarps * 32, smem, st>>>(W.i8, W.scale, x, y, T, W.K, W.N, W.ld, ldx, beta, p.chunk,
+                                                           p.splits, counters, partials);
+  else
+    gemv_kernel<false><<<grid, kGemvWarps * 32, smem, st>>>(W.f16, nullptr, x, y, T, W.K, W.N, W.ld, ldx, beta, p.chunk,
+                                                            p.splits, counters, partials);
+}
+
+void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st) {
+  check_linear(W, ldx, T);
+  if (T == 0) return;
+  dim3 grid(div_up(W.N, kBM), div_up(T, kBN));
+  count_launch();
+  if (W.i8)
+    gemm_kernel<true><<<grid, 256, 0, st>>>(W.i8, W.scale, x, y, T, W.K, W.N, W.ld, ldx, beta);
+  else
+    gemm_kernel<false><<<grid, 256, 0, st>>>(W.f16, nullptr, x, y, T, W.K, W.N, W.ld, ldx, beta);
+}
+
+void launch_linear(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch,
+                   size_t scratch_bytes, cudaStream_t st) {
+  if (T <= 8) launch_gemv(W, x, ldx, y, T, beta, scratch, scratch_bytes, st);
+  else launch_gemm(W, x, ldx, y, T, beta, st);
+}
+
+}  // namespace rb200
+
+// ---- C boundary -----------------------------------------------------------------------
+
+using namespace rb200;
+
+extern "C" {
+
+size_t rb200_gemv_scratch_bytes(int N, int K) {
+  if (N <= 0 || K < 64) return 256;
+  return gemv_scratch_bytes(N, K);
+}
+
+int rb200_gemv_int8(const int8_t* wq, const float* scale, const void* x, float* y, int T, int K, int N, int ldw, int ldx,
+                    float beta, void* scratch, size_t scratch_bytes, void* stream) {
+  return guarded([&] {
+    WeightView W;
+    W.i8 = wq;
+    W.scale = scale;
+    W.N = N;
+    W.K = K;
+    W.ld = ldw;
+    launch_gemv(W, static_cast<const __half*>(x), ldx, y, T, beta, scratch, scratch_bytes, as_stream(stream));
+    RB_CUDA(cudaGetLastError());
+    return 0;
+  });
+}
+
+int rb200_gemv_f16(const void* w, const void* x, float* y, int T, int K, int N, int ldw, int ldx, float beta,
+                   void* scratch, size_t scratch_bytes, void* stream) {
+  return guarded([&] {
+    WeightView W;
+    W.f16 = static_cast<const __half*>(w);
+    W.N = N;
+    W.K = K;
+    W.ld = ldw;
+    launch_gemv(W, static_cast<const __half*>(x), ldx, y, T, beta, scratch, scratch_bytes, as_stream(stream));
+    RB_CUDA(cudaGetLastError());
+    return 0;
+  });
+}
+
+int rb200_gemm(const void* w_f16, const int8_t* w_i8, const float* scale, const void* x, float* y, int T, int K, int N,
+               int ldw, int ldx, float beta, void* stream) {
+  return guarded([&] {
+    WeightView W;
+    W.f16 = static_cast<const __half*>(w_f16);
+    W.i8 = w_i8;
+    W.scale = scale;
+    W.N = N;
+    W.K = K;
+    W.ld = ldw;
+    launch_gemm(W, static_cast<const __half*>(x), ldx, y, T, beta, as_stream(stream));
+    RB_CUDA(cudaGetLastError());
+    return 0;
+  });
+}
+
+}  // extern "C"

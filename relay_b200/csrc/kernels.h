@@ -1,0 +1,76 @@
+// Internal launch interface between the kernels (small_ops.cu, attention.cu, gemm.cu) and
+// the backend that sequences them (backend.cu). Everything here enqueues on a stream and
+// returns; callers check cudaGetLastError().
+#pragma once
+
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace rb200 {
+
+// Where each token of the flattened batch sits: position pos[t] of sequence seq[t], whose
+// block ids start at tables[table_off[seq[t]]] (engine/src/cuda_kernels.cuh:16-26).
+struct TokenMeta {
+  const int* pos;
+  const int* seq;
+  const int* table_off;
+  const int* tables;
+};
+
+struct AttnShape {
+  int heads, kv_heads, D, block_size;
+  int q_stride;  // floats between tokens' q rows
+  int o_stride;  // halves between tokens' output rows
+};
+
+constexpr int kDecodeSlice = RB200_DECODE_SLICE;  // keys per split-context CTA
+constexpr int kPrefillRows = RB200_PREFILL_ROWS;  // query rows per prefill tile
+
+// ---- small_ops.cu ----
+void launch_embed(const int* tokens, const __half* table, float* x, int T, int H, int ld_table, cudaStream_t st);
+void launch_rmsnorm(const float* x, const int* rows, const float* w, __half* out, int R, int H, int ld_out, float eps,
+                    cudaStream_t st);
+void launch_qkv_post(float* qkv, const float* bias, const float* inv_freq, const TokenMeta& m, int T, __half* kc,
+                     __half* vc, int heads, int kv_heads, int D, int block_size, cudaStream_t st);
+void launch_silu_mul(const float* gu, __half* act, int T, int I, int ld_act, cudaStream_t st);
+void launch_f32_to_f16(const float* in, __half* out, size_t n, cudaStream_t st);
+void launch_convert_rows_f16(const float* in, __half* out, int rows, int K, int ld, cudaStream_t st);
+void launch_quantize_rows_int8(const float* in, int8_t* out, float* scale, int rows, int K, int ld, cudaStream_t st);
+void launch_kv_gather(const void* k, const void* v, const int* blocks, int n, size_t block_bytes, void* staging,
+                      cudaStream_t st);
+void launch_kv_scatter(void* k, void* v, const int* blocks, int n, size_t block_bytes, const void* staging,
+                       cudaStream_t st);
+void launch_argmax_rows(const float* logits, int R, int V, int* token_out, float* logit_out, cudaStream_t st);
+
+// ---- attention.cu ----
+// True when the tensor-core decode / prefill kernels cover this head layout; otherwise the
+// backend routes every token through launch_reference_attention.
+bool fast_attention_supported(const AttnShape& s);
+size_t decode_scratch_bytes(const AttnShape& s, int n_decode, int max_ctx);
+void launch_decode_attention(const AttnShape& s, const float* q, const TokenMeta& m, const int* decode_tokens,
+                             int n_decode, int max_ctx, const __half* kc, const __half* vc, float* scratch,
+                             __half* out, cudaStream_t st);
+void launch_prefill_attention(const AttnShape& s, const float* q, const TokenMeta& m, const int2* tiles, int n_tiles,
+                              const __half* kc, const __half* vc, __half* out, cudaStream_t st);
+void launch_reference_attention(const AttnShape& s, const float* q, const TokenMeta& m, int T, const __half* kc,
+                                const __half* vc, __half* out, cudaStream_t st);
+
+// ---- gemm.cu ----
+// A weight matrix [N][ld] in device memory: fp16, or int8 with one fp32 scale per row.
+// ld >= K is the row stride in elements; columns K..ld-1 hold zeros.
+struct WeightView {
+  const __half* f16 = nullptr;
+  const int8_t* i8 = nullptr;
+  const float* scale = nullptr;
+  int N = 0, K = 0, ld = 0;
+};
+size_t gemv_scratch_bytes(int N, int K);
+// y[T,N] = x[T,K] W^T (+ beta*y); routes T <= 8 to the GEMV and larger T to the GEMM.
+void launch_linear(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch,
+                   size_t scratch_bytes, cudaStream_t st);
+void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch,
+                 size_t scratch_bytes, cudaStream_t st);
+void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st);
+
+}  // namespace rb200

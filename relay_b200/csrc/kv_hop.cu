@@ -1,0 +1,179 @@
+// The prefill -> decode KV hop over NVLink: one layer's blocks are gathered into a
+// contiguous [K of each block][V of each block] buffer and handed to ncclSend; the
+// receiver's ncclRecv lands in its staging buffer and a scatter kernel writes the pages
+// into its own block ids. This replaces, for GPU-to-GPU transfers inside one box, the
+// host-staged payload path of the reference's transfer engine (sender
+// engine/src/kv_transfer.cpp:107-128 -> read_kv_layer -> socket; receiver :289-297 ->
+// write_kv_layer); the framing, ordering and abort messages stay on the host connection,
+// which also fixes the order in which the two sides post their send and receive.
+//
+// NCCL is loaded at run time (dlopen) so that the library has no link-time dependency on
+// it and a process that already loaded NCCL (for example through torch) shares that copy.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <chrono>
+#include <cstring>
+#include <thread>
+
+#include "backend.h"
+
+namespace rb200 {
+
+namespace {
+
+struct NcclApi {
+  void* lib = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+  ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
+  ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+NcclApi& api() {
+  static NcclApi a;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    for (const char* name : {"libnccl.so.2", "libnccl.so"}) {
+      a.lib = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+      if (a.lib) break;
+    }
+    if (!a.lib) return;
+    auto sym = [&](const char* n) { return dlsym(a.lib, n); };
+    a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(sym("ncclGetUniqueId"));
+    a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(sym("ncclCommInitRank"));
+    a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(sym("ncclCommDestroy"));
+    a.CommAbort = reinterpret_cast<decltype(a.CommAbort)>(sym("ncclCommAbort"));
+    a.CommGetAsyncError = reinterpret_cast<decltype(a.CommGetAsyncError)>(sym("ncclCommGetAsyncError"));
+    a.Send = reinterpret_cast<decltype(a.Send)>(sym("ncclSend"));
+    a.Recv = reinterpret_cast<decltype(a.Recv)>(sym("ncclRecv"));
+    a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(sym("ncclGetErrorString"));
+  });
+  if (!a.lib || !a.GetUniqueId || !a.CommInitRank || !a.Send || !a.Recv || !a.CommDestroy || !a.CommAbort)
+    fail(RB200_ERR_RUNTIME, "NCCL is not available (libnccl.so.2 could not be loaded)");
+  return a;
+}
+
+void nccl_check(ncclResult_t r, const char* what) {
+  if (r != ncclSuccess && r != ncclInProgress) {
+    const NcclApi& a = api();
+    fail(RB200_ERR_RUNTIME, std::string("NCCL error in ") + what + ": " + (a.GetErrorString ? a.GetErrorString(r) : "?"));
+  }
+}
+
+}  // namespace
+
+static ncclComm_t comm_of(const NcclState& s) { return static_cast<ncclComm_t>(s.comm); }
+
+void Backend::nccl_init(const void* id, int nranks, int rank) {
+  set_device();
+  RB_REQUIRE(nranks >= 2 && rank >= 0 && rank < nranks, "nccl_init: bad rank");
+  RB_REQUIRE(!nccl_, "nccl_init: already initialised");
+  NcclApi& a = api();
+  ncclUniqueId uid;
+  static_assert(sizeof(uid) == RB200_NCCL_ID_BYTES, "NCCL unique id size");
+  std::memcpy(&uid, id, sizeof(uid));
+  auto st = std::make_unique<NcclState>();
+  ncclComm_t comm = nullptr;
+  nccl_check(a.CommInitRank(&comm, nranks, uid, rank), "ncclCommInitRank");
+  st->comm = comm;
+  st->nranks = nranks;
+  st->rank = rank;
+  nccl_ = std::move(st);
+}
+
+void Backend::nccl_finalize() {
+  if (!nccl_) return;
+  set_device();
+  RB_CUDA(cudaStreamSynchronize(copy_stream_));
+  nccl_check(api().CommDestroy(comm_of(*nccl_)), "ncclCommDestroy");
+  nccl_.reset();
+}
+
+void Backend::nccl_finalize_noexcept() noexcept {
+  try {
+    nccl_finalize();
+  } catch (...) {
+    nccl_.reset();
+  }
+}
+
+void Backend::send_kv_layer(int peer, int layer, const int32_t* blocks, int n) {
+  set_device();
+  RB_REQUIRE(nccl_ != nullptr, "send_kv_layer: call nccl_init first");
+  RB_REQUIRE(peer >= 0 && peer < nccl_->nranks && peer != nccl_->rank, "send_kv_layer: bad peer");
+  check_layer(layer);
+  check_blocks(blocks, n);
+  if (n == 0) return;
+  std::lock_guard<std::mutex> lock(copy_mu_);
+  const size_t bb = kv_block_bytes();
+  ensure_kv_staging(n);
+  const int* ids = static_cast<const int*>(staging_ids(blocks, n));
+  // The gather must see this layer's appends of the latest forward pass: order the copy
+  // stream behind the layer's event on the device instead of blocking the host.
+  RB_CUDA(cudaStreamWaitEvent(copy_stream_, layer_done_[layer], 0));
+  const size_t off = static_cast<size_t>(layer) * layer_elems();
+  launch_kv_gather(kc_.as<__half>() + off, vc_.as<__half>() + off, ids, n, bb, kv_staging_.p, copy_stream_);
+  RB_CUDA(cudaGetLastError());
+  nccl_check(api().Send(kv_staging_.p, 2 * static_cast<size_t>(n) * bb, ncclInt8, peer, comm_of(*nccl_), copy_stream_), "ncclSend");
+}
+
+void Backend::recv_kv_layer(int peer, int layer, const int32_t* blocks, int n) {
+  set_device();
+  RB_REQUIRE(nccl_ != nullptr, "recv_kv_layer: call nccl_init first");
+  RB_REQUIRE(peer >= 0 && peer < nccl_->nranks && peer != nccl_->rank, "recv_kv_layer: bad peer");
+  check_layer(layer);
+  check_blocks(blocks, n);
+  if (n == 0) return;
+  std::lock_guard<std::mutex> lock(copy_mu_);
+  const size_t bb = kv_block_bytes();
+  ensure_kv_staging(n);
+  const int* ids = static_cast<const int*>(staging_ids(blocks, n));
+  nccl_check(api().Recv(kv_staging_.p, 2 * static_cast<size_t>(n) * bb, ncclInt8, peer, comm_of(*nccl_), copy_stream_), "ncclRecv");
+  const size_t off = static_cast<size_t>(layer) * layer_elems();
+  launch_kv_scatter(kc_.as<__half>() + off, vc_.as<__half>() + off, ids, n, bb, kv_staging_.p, copy_stream_);
+  RB_CUDA(cudaGetLastError());
+}
+
+void Backend::kv_hop_sync(int timeout_ms) {
+  set_device();
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms > 0 ? timeout_ms : 0);
+  for (;;) {
+    const cudaError_t q = cudaStreamQuery(copy_stream_);
+    if (q == cudaSuccess) return;
+    if (q != cudaErrorNotReady) RB_CUDA(q);
+    if (nccl_ && api().CommGetAsyncError) {
+      ncclResult_t async = ncclSuccess;
+      api().CommGetAsyncError(comm_of(*nccl_), &async);
+      if (async != ncclSuccess && async != ncclInProgress) {
+        api().CommAbort(comm_of(*nccl_));
+        nccl_.reset();
+        fail(RB200_ERR_RUNTIME, "NCCL reported an asynchronous error; communicator aborted");
+      }
+    }
+    if (timeout_ms > 0 && std::chrono::steady_clock::now() > deadline) {
+      if (nccl_) {
+        api().CommAbort(comm_of(*nccl_));
+        nccl_.reset();
+      }
+      fail(RB200_ERR_RUNTIME, "kv_hop_sync: timed out; communicator aborted");
+    }
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
+
+}  // namespace rb200
+
+extern "C" int rb200_nccl_unique_id(void* id) {
+  return rb200::guarded([&] {
+    RB_REQUIRE(id != nullptr, "nccl_unique_id: null argument");
+    ncclUniqueId uid;
+    rb200::nccl_check(rb200::api().GetUniqueId(&uid), "ncclGetUniqueId");
+    std::memcpy(id, &uid, sizeof(uid));
+    return 0;
+  });
+}

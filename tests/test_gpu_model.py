@@ -1,0 +1,316 @@
+"""The whole forward pass on the GPU, through the host-side mirror of relay::Backend and the
+C boundary, against the CPU oracle and the committed golden vectors.
+
+Bars (the path's stated ones): logits within 2e-3 by the reference's own metric
+(max|a-b| / max|b| per row, tests/test_reference.cpp:50-57) with identical greedy argmax;
+KV pages and block-table moves bit-exact.
+"""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from oracle import oracle  # noqa: E402
+from relay_b200.types import CudaOptions, ForwardBatch, HostWeights, ModelConfig, SeqChunk  # noqa: E402
+from tests.helpers import FIXTURES, GOLDEN, argmax_lowest, load_fixture, rel_err_rows  # noqa: E402
+from tests.workloads import c1_inputs  # noqa: E402
+
+LOGIT_TOL = 2e-3
+
+
+@pytest.fixture(scope="module")
+def mk():
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device")
+    from relay_b200.backend import make_cuda_backend
+    return make_cuda_backend
+
+
+def test_c1_tiny_llama_matches_cpu_reference_logits_and_greedy_tokens(mk):
+    z = np.load(f"{GOLDEN}/c1_cpu_reference.npz")
+    w, prompt, table = c1_inputs()
+    be = mk(w, 64, 16)
+    assert be.name() == "b200"
+    lg = be.forward(ForwardBatch([SeqChunk(prompt.tolist(), 0, table.tolist())], all_logits=True))
+    assert lg.shape == z["prompt_logits"].shape
+    assert rel_err_rows(lg, z["prompt_logits"]) < LOGIT_TOL
+    tok = argmax_lowest(lg[-1])
+    for s in range(16):
+        assert tok == int(z["tokens"][s])
+        row = be.forward(ForwardBatch([SeqChunk([tok], 37 + s, table.tolist())]))[0]
+        assert rel_err_rows(row[None], z["step_logits"][s][None]) < LOGIT_TOL
+        tok = argmax_lowest(row)
+    # the page the CPU backend wrote, rounded to the cache's fp16: equal up to one fp16 step
+    k, v = be.read_kv_block(1, int(table[0]))
+    for got, want in ((k, z["layer1_block0_k"]), (v, z["layer1_block0_v"])):
+        g = got.view(np.float16).astype(np.float32)
+        assert np.abs(g - want).max() <= 2e-3 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("name", FIXTURES)
+def test_fixtures_match_transformers_golden_logits(mk, name):
+    # tests/test_reference.cpp:77-119 of the reference, at this path's 2e-3 instead of its 2e-2
+    w, gold = load_fixture(name)
+    be = mk(w, 64, 16)
+    prompt, table = gold["prompt"].tolist(), list(range(8))
+    lg = be.forward(ForwardBatch([SeqChunk(prompt, 0, table)], all_logits=True))
+    assert rel_err_rows(lg, gold["prompt_logits"]) < LOGIT_TOL
+    tok, toks = argmax_lowest(lg[-1]), []
+    for s in range(len(gold["generated"])):
+        toks.append(tok)
+        row = be.forward(ForwardBatch([SeqChunk([tok], len(prompt) + s, table)]))[0]
+        if s + 1 < len(gold["step_logits"]):
+            assert rel_err_rows(row[None], gold["step_logits"][s + 1][None]) < LOGIT_TOL
+        tok = argmax_lowest(row)
+    assert toks == gold["generated"].tolist()
+
+
+def synthetic(cfg: ModelConfig, seed: int, std=0.05):
+    return HostWeights.random(cfg, seed, std=std, norm_std=0.1)
+
+
+WIDE_CONFIGS = {
+    # head sizes the reference's fixtures do not reach (D = 64 and 128), still CPU-checkable
+    "d128_g4": ModelConfig(hidden=256, intermediate=320, layers=2, heads=4, kv_heads=1, head_dim=128, vocab=512),
+    "d64_g8": ModelConfig(hidden=256, intermediate=172, layers=2, heads=8, kv_heads=1, head_dim=64, vocab=300,
+                          rope_theta=500000.0, rope_scaling_type="llama3", rope_factor=8.0,
+                          rope_original_max_position=64.0),
+    "d32_mha_bias": ModelConfig(hidden=128, intermediate=200, layers=3, heads=4, kv_heads=4, head_dim=32, vocab=260,
+                                qkv_bias=True, tie_embeddings=True),
+}
+
+
+def schedule(cfg, rng, lens, chunk, steps, bs, first_block=0):
+    """Chunked prefill of several sequences per pass, then decode steps with a fresh prompt
+    riding along on odd steps (the shape of tests/test_attention.cpp:43-138)."""
+    seqs, nxt = [], first_block
+    for n in lens:
+        need = (n + steps + 1 + bs - 1) // bs
+        seqs.append(dict(tok=rng.integers(0, cfg.vocab, n + steps + 1).tolist(), n=n, table=list(range(nxt, nxt + need)), done=0))
+        nxt += need
+    passes = []
+    while any(s["done"] < s["n"] for s in seqs):
+        b = ForwardBatch()
+        for s in seqs:
+            k = min(s["n"] - s["done"], chunk)
+            if k > 0:
+                b.seqs.append(SeqChunk(s["tok"][s["done"]:s["done"] + k], s["done"], s["table"]))
+                s["done"] += k
+        passes.append(b)
+    for d in range(steps):
+        b = ForwardBatch()
+        for s in seqs:
+            b.seqs.append(SeqChunk([s["tok"][s["done"]]], s["done"], s["table"]))
+            s["done"] += 1
+        if d % 2 == 1:
+            b.seqs.append(SeqChunk(rng.integers(0, cfg.vocab, 40 + d).tolist(), 0, list(range(nxt, nxt + 4))))
+        passes.append(b)
+    return passes, nxt + 4
+
+
+@pytest.mark.parametrize("name", list(WIDE_CONFIGS))
+@pytest.mark.parametrize("bs", [16, 4])
+def test_mixed_prefill_and_decode_schedule_matches_cpu(mk, name, bs):
+    cfg = WIDE_CONFIGS[name]
+    w = synthetic(cfg, 5)
+    rng = np.random.Generator(np.random.PCG64(7))
+    passes, blocks = schedule(cfg, rng, [1, 17, 64, 200, 700], 192, 6, bs)
+    cpu = oracle.cpu_model(w, blocks, bs)
+    gpu = mk(w, blocks, bs, max_batch_tokens=2048)
+    worst, agree, total = 0.0, 0, 0
+    for b in passes:
+        a, g = cpu.forward(b), gpu.forward(b)
+        assert a.shape == g.shape
+        worst = max(worst, rel_err_rows(g, a))
+        agree += int((a.argmax(1) == g.argmax(1)).sum())
+        total += a.shape[0]
+    assert worst < LOGIT_TOL
+    assert agree == total
+
+
+def test_batched_equals_alone_and_chunked_equals_whole_on_gpu(mk):
+    # the invariances of tests/test_batching.cpp:75-120; on the GPU the GEMM tile a token
+    # lands in depends on the batch, so logits agree to rounding rather than bit for bit
+    w = synthetic(WIDE_CONFIGS["d64_g8"], 9)
+    rng = np.random.Generator(np.random.PCG64(3))
+    p1, p2 = rng.integers(0, 300, 90).tolist(), rng.integers(0, 300, 23).tolist()
+    t1, t2 = [5, 9, 2, 11, 30, 8], [7, 1]
+    alone = mk(w, 32, 16).forward(ForwardBatch([SeqChunk(p1, 0, t1)], all_logits=True))
+    both = mk(w, 32, 16).forward(ForwardBatch([SeqChunk(p2, 0, t2), SeqChunk(p1, 0, t1)], all_logits=True))
+    assert rel_err_rows(both[len(p2):], alone) < 5e-4
+    be = mk(w, 32, 16)
+    rows = [be.forward(ForwardBatch([SeqChunk(p1[i:i + 7], i, t1)], all_logits=True)) for i in range(0, 90, 7)]
+    assert rel_err_rows(np.concatenate(rows), alone) < 5e-4
+    assert np.array_equal(np.concatenate(rows).argmax(1), alone.argmax(1))
+
+
+def test_kv_blocks_moved_to_another_backend_decode_identically(mk):
+    # tests/test_kv_cache.cpp:67-102 of the reference: prefill on A, copy its blocks to B under
+    # different block ids, decode on both: same tokens; here also the same bits
+    w, prompt, _ = c1_inputs()
+    a, b = mk(w, 32, 16), mk(w, 32, 16)
+    ta, tb = [3, 17, 9], [20, 1, 30]
+    la = a.forward(ForwardBatch([SeqChunk(prompt.tolist(), 0, ta)]))
+    for layer in range(w.config.layers):
+        payload = a.read_kv_layer(layer, ta)
+        b.write_kv_layer(layer, tb, payload)
+        assert np.array_equal(b.read_kv_layer(layer, tb), payload)
+        k, v = a.read_kv_block(layer, ta[1])
+        k2, v2 = b.read_kv_block(layer, tb[1])
+        assert np.array_equal(k, k2) and np.array_equal(v, v2)
+    tok = argmax_lowest(la[0])
+    for s in range(6):
+        ra = a.forward(ForwardBatch([SeqChunk([tok], 37 + s, ta)]))[0]
+        rb = b.forward(ForwardBatch([SeqChunk([tok], 37 + s, tb)]))[0]
+        assert np.array_equal(ra, rb)
+        tok = argmax_lowest(ra)
+
+
+def test_kv_pages_match_cpu_pages_rounded_to_fp16(mk):
+    cfg = WIDE_CONFIGS["d128_g4"]
+    w = synthetic(cfg, 2)
+    rng = np.random.Generator(np.random.PCG64(1))
+    toks = rng.integers(0, cfg.vocab, 50).tolist()
+    table = [6, 2, 9, 0]
+    cpu, gpu = oracle.cpu_model(w, 12, 16), mk(w, 12, 16)
+    cpu.forward(ForwardBatch([SeqChunk(toks, 0, table)]))
+    gpu.forward(ForwardBatch([SeqChunk(toks, 0, table)]))
+    for layer in range(cfg.layers):
+        for blk in table:
+            kc, vc = cpu.read_kv_block(layer, blk)
+            kg, vg = gpu.read_kv_block(layer, blk)
+            for c, g in ((kc, kg), (vc, vg)):
+                g = g.view(np.float16).astype(np.float32)
+                assert np.abs(g - c).max() <= 2e-3 * np.abs(c).max()
+    # slots past the 50 tokens stay zero, as on the CPU
+    k, _ = gpu.read_kv_block(0, 0)
+    assert np.all(k.view(np.float16).reshape(cfg.kv_heads, 16, cfg.head_dim)[:, 2:, :] == 0)
+
+
+def test_layer_observer_fires_once_per_layer_in_order(mk):
+    # tests/test_transfer.cpp:220-233
+    w, prompt, table = c1_inputs()
+    be = mk(w, 64, 16)
+    seen = []
+    be.forward(ForwardBatch([SeqChunk(prompt.tolist(), 0, table.tolist())]), observer=seen.append)
+    assert seen == list(range(w.config.layers))
+    for l in seen:
+        be.wait_kv_written(l)
+
+
+def test_forward_rejects_what_the_reference_rejects(mk):
+    w, _, _ = c1_inputs()
+    be = mk(w, 16, 16, max_batch_tokens=32, max_context=64)
+    with pytest.raises(ValueError, match="block table too short"):
+        be.forward(ForwardBatch([SeqChunk(list(range(17)), 0, [3])]))
+    with pytest.raises(IndexError, match="token id out of range"):
+        be.forward(ForwardBatch([SeqChunk([256], 0, [3])]))
+    with pytest.raises(ValueError, match="max_context"):
+        be.forward(ForwardBatch([SeqChunk([1], 64, [0, 1, 2, 3, 4])]))
+    with pytest.raises(ValueError, match="max_batch_tokens"):
+        be.forward(ForwardBatch([SeqChunk([1] * 33, 0, [0, 1, 2])]))
+    with pytest.raises(ValueError, match="block id out of range"):
+        be.forward(ForwardBatch([SeqChunk([1], 0, [16])]))
+    assert be.forward(ForwardBatch([])).shape[0] == 0
+    assert be.forward(ForwardBatch([SeqChunk([1, 2], 0, [1], want_logits=False)])).shape[0] == 0
+    with pytest.raises(ValueError, match="no such layer"):
+        be.read_kv_layer(99, [0])
+    with pytest.raises(ValueError, match="wrong size"):
+        be.update_weight("final_norm", np.zeros(3, np.float32))
+    with pytest.raises(ValueError, match="no layers.9.wo"):
+        be.update_weight("layers.9.wo", np.zeros(3, np.float32))
+
+
+def test_reference_attention_option_agrees_with_the_fast_kernels(mk):
+    # tests/test_attention.cpp:179-198 (M1 against M0): same logits up to rounding
+    cfg = WIDE_CONFIGS["d64_g8"]
+    w = synthetic(cfg, 4)
+    rng = np.random.Generator(np.random.PCG64(5))
+    passes, blocks = schedule(cfg, rng, [1, 17, 200, 700], 192, 4, 16)
+    a = mk(w, blocks, 16, max_batch_tokens=2048, options=CudaOptions(reference_attention=True))
+    b = mk(w, blocks, 16, max_batch_tokens=2048, options=CudaOptions())
+    for p in passes:
+        la, lb = a.forward(p), b.forward(p)
+        assert rel_err_rows(lb, la) < LOGIT_TOL
+        assert np.array_equal(la.argmax(1), lb.argmax(1))
+
+
+def dequantised(w: HostWeights) -> HostWeights:
+    """The float32 model an int8 backend represents: layer matrices replaced by q * scale."""
+    out = dict(w.tensors)
+    for name, t in w.tensors.items():
+        if name.startswith("layers.") and t.ndim == 2:
+            q, s = oracle.quantize_rows_int8(t)
+            out[name] = (q.astype(np.float32) * s[:, None]).astype(np.float32)
+    return HostWeights(w.config, out)
+
+
+@pytest.mark.parametrize("name", ["c1", "d128_g4"])
+def test_int8_weights_match_cpu_on_the_dequantised_model(mk, name):
+    w = c1_inputs()[0] if name == "c1" else synthetic(WIDE_CONFIGS[name], 6)
+    cfg = w.config
+    rng = np.random.Generator(np.random.PCG64(8))
+    passes, blocks = schedule(cfg, rng, [5, 60, 130], 64, 5, 16)
+    cpu = oracle.cpu_model(dequantised(w), blocks, 16)
+    gpu = mk(w, blocks, 16, max_batch_tokens=1024, options=CudaOptions(int8_weights=True))
+    for p in passes:
+        a, g = cpu.forward(p), gpu.forward(p)
+        assert rel_err_rows(g, a) < LOGIT_TOL
+        assert np.array_equal(a.argmax(1), g.argmax(1))
+
+
+def test_update_weight_equals_construction_and_accepts_device_pointers(mk):
+    # tests/test_c_api.cpp (update_tensor == host write): a backend built empty and filled
+    # tensor by tensor, half of them from device memory, gives the same bits
+    w, prompt, table = c1_inputs()
+    from relay_b200.backend import Backend
+    batch = ForwardBatch([SeqChunk(prompt.tolist(), 0, table.tolist())], all_logits=True)
+    for opts in (CudaOptions(), CudaOptions(int8_weights=True)):
+        want = mk(w, 64, 16, options=opts).forward(batch)
+        be = Backend(w.config, None, 64, 16, options=opts)
+        keep = []
+        for i, (name, t) in enumerate(w.tensors.items()):
+            if i % 2:
+                d = torch.from_numpy(t).cuda()
+                keep.append(d)
+                be.update_weight(name, d.data_ptr(), d.numel())
+            else:
+                be.update_weight(name, t)
+        assert np.array_equal(be.forward(batch), want)
+
+
+def test_forward_greedy_equals_host_argmax(mk):
+    w, prompt, table = c1_inputs()
+    be = mk(w, 64, 16, options=CudaOptions(gpu_argmax=True))
+    b = ForwardBatch([SeqChunk(prompt.tolist(), 0, table.tolist())], all_logits=True)
+    lg = be.forward(b)
+    tok, val = be.forward_greedy(b)
+    assert tok.tolist() == [argmax_lowest(r) for r in lg]
+    assert np.array_equal(val, lg.max(1))
+
+
+def test_concurrent_kv_reads_while_forward_runs(mk):
+    # backend.h:60-64: read_kv_layer is safe from another thread during forward()
+    import threading
+    cfg = WIDE_CONFIGS["d64_g8"]
+    w = synthetic(cfg, 3)
+    be = mk(w, 64, 16, max_batch_tokens=1024)
+    rng = np.random.Generator(np.random.PCG64(4))
+    be.forward(ForwardBatch([SeqChunk(rng.integers(0, 300, 64).tolist(), 0, [0, 1, 2, 3])]))
+    snap = [be.read_kv_layer(l, [0, 1, 2, 3]) for l in range(cfg.layers)]
+    stop, bad = threading.Event(), []
+
+    def reader():
+        while not stop.is_set():
+            for l in range(cfg.layers):
+                if not np.array_equal(be.read_kv_layer(l, [0, 1, 2, 3]), snap[l]):
+                    bad.append(l)
+
+    th = threading.Thread(target=reader)
+    th.start()
+    for _ in range(20):  # forward passes on other blocks leave blocks 0-3 untouched
+        be.forward(ForwardBatch([SeqChunk(rng.integers(0, 300, 500).tolist(), 0, list(range(8, 48)))]))
+    stop.set()
+    th.join()
+    assert not bad
