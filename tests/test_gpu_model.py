@@ -85,6 +85,7 @@ def schedule(cfg, rng, lens, chunk, steps, bs, first_block=0):
     """Chunked prefill of several sequences per pass, then decode steps with a fresh prompt
     riding along on odd steps (the shape of tests/test_attention.cpp:43-138)."""
     seqs, nxt = [], first_block
+    extra = (40 + steps + bs - 1) // bs
     for n in lens:
         need = (n + steps + 1 + bs - 1) // bs
         seqs.append(dict(tok=rng.integers(0, cfg.vocab, n + steps + 1).tolist(), n=n, table=list(range(nxt, nxt + need)), done=0))
@@ -103,10 +104,10 @@ def schedule(cfg, rng, lens, chunk, steps, bs, first_block=0):
         for s in seqs:
             b.seqs.append(SeqChunk([s["tok"][s["done"]]], s["done"], s["table"]))
             s["done"] += 1
-        if d % 2 == 1:
-            b.seqs.append(SeqChunk(rng.integers(0, cfg.vocab, 40 + d).tolist(), 0, list(range(nxt, nxt + 4))))
+        if d % 2 == 1:  # a throwaway prompt in blocks of its own
+            b.seqs.append(SeqChunk(rng.integers(0, cfg.vocab, 40 + d).tolist(), 0, list(range(nxt, nxt + extra))))
         passes.append(b)
-    return passes, nxt + 4
+    return passes, nxt + extra
 
 
 @pytest.mark.parametrize("name", list(WIDE_CONFIGS))
@@ -130,18 +131,20 @@ def test_mixed_prefill_and_decode_schedule_matches_cpu(mk, name, bs):
 
 
 def test_batched_equals_alone_and_chunked_equals_whole_on_gpu(mk):
-    # the invariances of tests/test_batching.cpp:75-120; on the GPU the GEMM tile a token
-    # lands in depends on the batch, so logits agree to rounding rather than bit for bit
+    # the invariances of tests/test_batching.cpp:75-120; on the GPU a token's kernels depend on
+    # the batch (GEMV for up to 8 tokens, GEMM above; decode or prefill attention), each with
+    # its own fp16 rounding of P and of the activations, so logits agree to that rounding
+    # (about 2^-11 per rounding point) rather than bit for bit
     w = synthetic(WIDE_CONFIGS["d64_g8"], 9)
     rng = np.random.Generator(np.random.PCG64(3))
     p1, p2 = rng.integers(0, 300, 90).tolist(), rng.integers(0, 300, 23).tolist()
     t1, t2 = [5, 9, 2, 11, 30, 8], [7, 1]
     alone = mk(w, 32, 16).forward(ForwardBatch([SeqChunk(p1, 0, t1)], all_logits=True))
     both = mk(w, 32, 16).forward(ForwardBatch([SeqChunk(p2, 0, t2), SeqChunk(p1, 0, t1)], all_logits=True))
-    assert rel_err_rows(both[len(p2):], alone) < 5e-4
+    assert rel_err_rows(both[len(p2):], alone) < 1.5e-3
     be = mk(w, 32, 16)
     rows = [be.forward(ForwardBatch([SeqChunk(p1[i:i + 7], i, t1)], all_logits=True)) for i in range(0, 90, 7)]
-    assert rel_err_rows(np.concatenate(rows), alone) < 5e-4
+    assert rel_err_rows(np.concatenate(rows), alone) < 1.5e-3
     assert np.array_equal(np.concatenate(rows).argmax(1), alone.argmax(1))
 
 
