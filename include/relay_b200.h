@@ -263,6 +263,10 @@ int rb200_gemv_f16(const void* w, const void* x, float* y, int T, int K, int N, 
 int rb200_gemm(const void* w_f16, const int8_t* w_i8, const float* scale, const void* x, float* y, int T, int K,
                int N, int ldw, int ldx, float beta, void* stream);
 
+/* 0, or the code that a bounded pipeline wait inside the tensor-core GEMM left on the
+ * current device when it gave up (the launch then produced no valid output). */
+int rb200_gemm_status(void);
+
 /* rmsnorm_kernel (engine/src/cuda_backend.cu:157-167): out[r] = w * x[rows ? rows[r] : r] * rsqrt(mean(x^2)+eps),
  * fp32 -> fp16 rows of ld_out halves (columns H..ld_out-1 are written as zero). */
 int rb200_rmsnorm(const float* x, const int32_t* rows, const float* w, void* out, int R, int H, int ld_out,

@@ -75,6 +75,7 @@ SIGNATURES = {
     "rb200_gemv_int8": (I, [P, P, P, P, I, I, I, I, I, F, P, SZ, P]),
     "rb200_gemv_f16": (I, [P, P, P, I, I, I, I, I, F, P, SZ, P]),
     "rb200_gemm": (I, [P, P, P, P, P, I, I, I, I, I, F, P]),
+    "rb200_gemm_status": (I, []),
     "rb200_rmsnorm": (I, [P, P, P, P, I, I, I, F, P]),
     "rb200_embed": (I, [P, P, P, I, I, I, P]),
     "rb200_qkv_post": (I, [P, P, P, C.POINTER(CTokenMeta), I, P, P, I, I, I, I, P]),

@@ -404,6 +404,10 @@ int Backend::forward(int n_seqs, const int32_t* tokens, const int32_t* chunk_len
   RB_CUDA(cudaGetLastError());
   RB_CUDA(cudaStreamSynchronize(stream_));
   end_profile(prof);
+  if (T > 8 || R > 8) {  // the tensor-core GEMM ran: make sure none of its bounded waits gave up
+    const int code = umma_gemm_status();
+    if (code != 0) fail(RB200_ERR_RUNTIME, "tensor-core GEMM pipeline wait timed out (code " + std::to_string(code) + ")");
+  }
   return R;
 }
 

@@ -15,6 +15,8 @@
 //    engine/src/cuda_backend.cu:719-721) and cublasGemmEx for fp16 weights: weights on the M
 //    axis, tokens on N, int8 dequantised on its way into shared memory (the fp16 copy of the
 //    matrix is never materialised in HBM), scale and residual applied in the epilogue.
+#include <cstdlib>
+
 #include "kernels.h"
 
 namespace rb200 {
@@ -388,6 +390,17 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
 void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st) {
   check_linear(W, ldx, T);
   if (T == 0) return;
+  static const bool force_legacy = [] {
+    const char* e = std::getenv("RB200_GEMM");
+    return e && std::string(e) == "mma_sync";
+  }();
+  if (!force_legacy && umma_gemm_usable(W, x, ldx)) return launch_umma_gemm(W, x, ldx, y, T, beta, st);
+  launch_gemm_mma_sync(W, x, ldx, y, T, beta, st);
+}
+
+void launch_gemm_mma_sync(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st) {
+  check_linear(W, ldx, T);
+  if (T == 0) return;
   dim3 grid(div_up(W.N, kBM), div_up(T, kBN));
   count_launch();
   if (W.i8)
@@ -442,6 +455,15 @@ int rb200_gemv_f16(const void* w, const void* x, float* y, int T, int K, int N, 
     RB_CUDA(cudaGetLastError());
     return 0;
   });
+}
+
+int rb200_gemm_status(void) {
+  int v = -1;
+  const int rc = guarded([&] {
+    v = umma_gemm_status();
+    return 0;
+  });
+  return rc == 0 ? v : -1;
 }
 
 int rb200_gemm(const void* w_f16, const int8_t* w_i8, const float* scale, const void* x, float* y, int T, int K, int N,

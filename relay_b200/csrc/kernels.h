@@ -72,5 +72,14 @@ void launch_linear(const WeightView& W, const __half* x, int ldx, float* y, int 
 void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch,
                  size_t scratch_bytes, cudaStream_t st);
 void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st);
+// The same product with legacy mma.sync tiles (any alignment); launch_gemm prefers the
+// tcgen05 kernel of umma_gemm.cu and falls back to this one.
+void launch_gemm_mma_sync(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st);
+
+// ---- umma_gemm.cu ----
+bool umma_gemm_usable(const WeightView& W, const __half* x, int ldx);
+void launch_umma_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st);
+// 0, or the code a bounded pipeline wait of the tcgen05 GEMM left on the current device.
+int umma_gemm_status();
 
 }  // namespace rb200

@@ -1,0 +1,409 @@
+// Tensor-core GEMM for more than 8 tokens on Blackwell's fifth-generation tensor cores:
+//   y[T,N] = x[T,K] W[N,K]^T (+ beta*y),  W fp16 or int8 with a per-row scale.
+// Replaces the reference's cublasGemmEx call (engine/src/cuda_backend.cu:724-730) and its
+// dequantise-then-cuBLAS path for int8 (engine/src/cuda_kernels.cuh:432-436,
+// engine/src/cuda_backend.cu:719-721).
+//
+// Shape of one CTA: 128 weight rows (the M axis of tcgen05.mma, one TMEM lane per row) by BN
+// tokens (the N axis, one TMEM column per token), K in blocks of 64 halves = one 128-byte
+// swizzle atom. Six warps with fixed roles:
+//   warp 0   TMA producer: one elected lane streams the weight tile and the activation tile
+//            of each k block into a ring of shared-memory stages (cp.async.bulk.tensor,
+//            128-byte swizzle, completion on an mbarrier);
+//   warp 1   MMA issuer: one elected lane issues four tcgen05.mma (K = 16 each) per k block
+//            on shared-memory descriptors, accumulating in TMEM, and releases each stage
+//            with tcgen05.commit; it also owns the TMEM allocation;
+//   warps 2-5  epilogue: read the accumulator with tcgen05.ld (each warp its own quarter of
+//            the 128 lanes), apply the row scale and beta*y, store fp32 rows coalesced along
+//            N. With int8 weights the same four warps first act as the dequantiser of the
+//            main loop: the producer lands raw int8 rows in a staging buffer, they widen
+//            them to fp16 straight into the swizzled operand layout (fence.proxy.async),
+//            so the fp16 copy of the matrix exists only in shared memory.
+// Weight bytes are read from HBM once per token tile; activations come from L2.
+//
+// Every mbarrier wait is bounded: on exhaustion the kernel records a code in `status`,
+// stops issuing work, and still releases its TMEM before it returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "kernels.h"
+
+namespace rb200 {
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kBlockK = 64;        // halves per k block: one 128-byte swizzle atom
+constexpr int kUmmaThreads = 192;  // producer, MMA, 4 epilogue warps
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a pipeline wait gives up after 2 s
+
+// ---- PTX wrappers ----------------------------------------------------------------------
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for the phase with the given parity; false when the time limit runs out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  unsigned long long start = 0;
+  for (uint32_t i = 0;; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((i & 1023u) == 1023u) {
+      const unsigned long long now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > kWaitLimitNs) return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], fp16 inputs, fp32 accumulate.
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with
+// the 128-byte swizzle (what TMA's SWIZZLE_128B writes): start address / 16 in bits 0-13,
+// leading byte offset (unused for swizzled K-major; 1) in bits 16-29, stride between 8-row
+// groups (1024 bytes / 16) in bits 32-45, descriptor version 1 in bits 46-47, layout type 2
+// (SWIZZLE_128B) in bits 61-63.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::f16: fp32 accumulator (bits 4-5 = 1), fp16 A and B
+// (bits 7-9, 10-12 = 0), both K-major (bits 15, 16 = 0), N / 8 in bits 17-22, M / 16 in bits 24-28.
+__host__ __device__ constexpr uint32_t umma_idesc(int M, int N) {
+  return (1u << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+__device__ __forceinline__ void cvt_s8x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t u = w ^ 0x80808080u;
+  uint32_t a, b;
+  asm("prmt.b32 %0, %1, %2, 0x4140;" : "=r"(a) : "r"(u), "r"(0x64646464u));
+  asm("prmt.b32 %0, %1, %2, 0x4342;" : "=r"(b) : "r"(u), "r"(0x64646464u));
+  const __half2 bias = __half2half2(__ushort_as_half(0x6480));  // 1152.0
+  __half2 ha = __hsub2(*reinterpret_cast<__half2*>(&a), bias);
+  __half2 hb = __hsub2(*reinterpret_cast<__half2*>(&b), bias);
+  lo = *reinterpret_cast<uint32_t*>(&ha);
+  hi = *reinterpret_cast<uint32_t*>(&hb);
+}
+
+template <int BN, bool INT8>
+struct UmmaSmem {
+  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 5 : 6);
+  static constexpr int kABytes = kTileM * kBlockK * 2;            // fp16 operand tile
+  static constexpr int kBBytes = BN * kBlockK * 2;
+  static constexpr int kRawBytes = INT8 ? kTileM * kBlockK : 0;   // int8 staging tile
+  static constexpr int kStageBytes = kABytes + kBBytes + kRawBytes;
+  static constexpr int kBarBytes = 256;
+  static constexpr size_t kTotal = static_cast<size_t>(kStages) * kStageBytes + kBarBytes + 1024;  // + alignment slack
+};
+
+template <int BN, bool INT8>
+__global__ void __launch_bounds__(kUmmaThreads, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                 const float* __restrict__ scale, float* __restrict__ y, int T, int N, int K, float beta,
+                 int* __restrict__ status) {
+  using S = UmmaSmem<BN, INT8>;
+  constexpr int NS = S::kStages;
+  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;  // power of two >= 32
+  extern __shared__ unsigned char smem_dyn[];
+  // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern
+  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  const uint32_t sA = base;
+  const uint32_t sB = sA + NS * S::kABytes;
+  const uint32_t sRaw = sB + NS * S::kBBytes;
+  const uint32_t bars = sRaw + NS * S::kRawBytes;
+  const uint32_t full_bar = bars;              // NS x 8 bytes: TMA landed
+  const uint32_t empty_bar = bars + 8 * NS;    // NS x 8: MMA finished reading the stage
+  const uint32_t conv_bar = bars + 16 * NS;    // NS x 8: int8 tile widened (INT8 only)
+  const uint32_t accum_bar = bars + 24 * NS;   // accumulator complete
+  const uint32_t tmem_slot = bars + 24 * NS + 8;
+  unsigned char* gen_base = smem_dyn + (base - smem_u32(smem_dyn));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * kTileM, tok0 = blockIdx.y * BN;
+  const int nk = K / kBlockK;
+
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(empty_bar + 8 * s, 1);
+      mbar_init(conv_bar + 8 * s, 128);
+    }
+    mbar_init(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
+
+  bool ok = true;
+  if (warp == 0) {
+    // ---- TMA producer ----
+    if (elect_one()) {
+      for (int kb = 0; kb < nk && ok; ++kb) {
+        const int s = kb % NS;
+        ok = mbar_wait(empty_bar + 8 * s, ((kb / NS) & 1) ^ 1);
+        if (!ok) break;
+        mbar_expect_tx(full_bar + 8 * s, (INT8 ? S::kRawBytes : S::kABytes) + S::kBBytes);
+        if (INT8) tma_load_2d(sRaw + s * S::kRawBytes, &map_w, kb * kBlockK, m0, full_bar + 8 * s);
+        else tma_load_2d(sA + s * S::kABytes, &map_w, kb * kBlockK, m0, full_bar + 8 * s);
+        tma_load_2d(sB + s * S::kBBytes, &map_x, kb * kBlockK, tok0, full_bar + 8 * s);
+      }
+      if (!ok) atomicExch(status, 1);
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc(kTileM, BN);
+      for (int kb = 0; kb < nk && ok; ++kb) {
+        const int s = kb % NS;
+        ok = mbar_wait((INT8 ? conv_bar : full_bar) + 8 * s, (kb / NS) & 1);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t da = smem_desc_sw128(sA + s * S::kABytes);
+        const uint64_t db = smem_desc_sw128(sB + s * S::kBBytes);
+#pragma unroll
+        for (int k4 = 0; k4 < kBlockK / 16; ++k4)  // 16 halves = 32 bytes = 2 descriptor units per step
+          umma_f16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+        umma_commit(empty_bar + 8 * s);  // arrives once the MMAs above have read the stage
+      }
+      umma_commit(accum_bar);
+      if (!ok) atomicExch(status, 2);
+    }
+  } else {
+    // ---- int8 widening (main loop), then the epilogue ----
+    const int et = threadIdx.x - 64;  // 0..127: one weight row of the tile each
+    if constexpr (INT8) {
+      for (int kb = 0; kb < nk && ok; ++kb) {
+        const int s = kb % NS;
+        ok = mbar_wait(full_bar + 8 * s, (kb / NS) & 1);
+        if (!ok) break;
+        const uint4* raw = reinterpret_cast<const uint4*>(gen_base + (sRaw + s * S::kRawBytes - base)) + et * 4;
+        uint4* dst = reinterpret_cast<uint4*>(gen_base + (sA + s * S::kABytes - base));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {  // 16 int8 -> two 16-byte fp16 chunks
+          const uint4 r = raw[c];
+          uint4 o0, o1;
+          cvt_s8x4(r.x, o0.x, o0.y);
+          cvt_s8x4(r.y, o0.z, o0.w);
+          cvt_s8x4(r.z, o1.x, o1.y);
+          cvt_s8x4(r.w, o1.z, o1.w);
+          dst[et * 8 + ((2 * c) ^ (et & 7))] = o0;
+          dst[et * 8 + ((2 * c + 1) ^ (et & 7))] = o1;
+        }
+        fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+        mbar_arrive(conv_bar + 8 * s);
+      }
+      if (!ok) atomicExch(status, 3);
+    }
+    bool done = mbar_wait(accum_bar, 0);
+    if (!done) atomicExch(status, 4);
+    tc_fence_after();
+    if (done && ok) {
+      const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
+      const int n = m0 + quarter * 32 + lane;
+      const float sc = (INT8 && n < N) ? scale[n] : 1.0f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+        tmem_ld_wait();
+        if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int tok = tok0 + c0 + j;
+            if (tok < T) {
+              float* d = y + static_cast<long long>(tok) * N + n;
+              const float r = __uint_as_float(v[j]) * sc;
+              *d = beta != 0.f ? r + beta * *d : r;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+    else
+      cudaGetLastError();
+  });
+  if (!fn) fail(RB200_ERR_RUNTIME, "cuTensorMapEncodeTiled is not available from this driver");
+  return fn;
+}
+
+// A 2-D tensor map over a row-major [rows][ld] matrix of 1- or 2-byte elements, box = [box_rows][box_cols].
+CUtensorMap make_map(const void* ptr, int elem_bytes, long long rows, long long cols, long long ld, int box_rows,
+                     int box_cols, bool swizzle128) {
+  CUtensorMap m;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode_fn()(&m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                                 const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) fail(RB200_ERR_RUNTIME, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
+  return m;
+}
+
+int* status_word() {
+  // One word per device, allocated on first use and kept for the life of the process.
+  static int* words[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  RB_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  if (!words[dev]) {
+    RB_CUDA(cudaMalloc(&words[dev], sizeof(int)));
+    RB_CUDA(cudaMemset(words[dev], 0, sizeof(int)));
+  }
+  return words[dev];
+}
+
+template <int BN, bool INT8>
+void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st) {
+  using S = UmmaSmem<BN, INT8>;
+  static bool configured = false;
+  auto kernel = umma_gemm_kernel<BN, INT8>;
+  if (!configured) {
+    RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
+    configured = true;
+  }
+  const CUtensorMap mw = INT8 ? make_map(W.i8, 1, W.N, W.K, W.ld, kTileM, kBlockK, false)
+                              : make_map(W.f16, 2, W.N, W.K, W.ld, kTileM, kBlockK, true);
+  const CUtensorMap mx = make_map(x, 2, T, W.K, ldx, BN, kBlockK, true);
+  dim3 grid(div_up(W.N, kTileM), div_up(T, BN));
+  count_launch();
+  kernel<<<grid, kUmmaThreads, S::kTotal, st>>>(mw, mx, W.scale, y, T, W.N, W.K, beta, status_word());
+}
+
+template <bool INT8>
+void launch_umma_i(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st) {
+  if (T <= 32) launch_umma_t<32, INT8>(W, x, ldx, y, T, beta, st);
+  else if (T <= 64) launch_umma_t<64, INT8>(W, x, ldx, y, T, beta, st);
+  else if (T <= 128 || (T > 256 && T <= 384 && false)) launch_umma_t<128, INT8>(W, x, ldx, y, T, beta, st);
+  else launch_umma_t<256, INT8>(W, x, ldx, y, T, beta, st);
+}
+
+}  // namespace
+
+bool umma_gemm_usable(const WeightView& W, const __half* x, int ldx) {
+  // TMA wants 16-byte aligned bases and row strides
+  const uintptr_t wp = reinterpret_cast<uintptr_t>(W.i8 ? static_cast<const void*>(W.i8) : static_cast<const void*>(W.f16));
+  return (wp & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (static_cast<long long>(W.ld) * (W.i8 ? 1 : 2)) % 16 == 0 &&
+         (static_cast<long long>(ldx) * 2) % 16 == 0 && W.K % kBlockK == 0;
+}
+
+void launch_umma_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st) {
+  if (T == 0) return;
+  if (W.i8) launch_umma_i<true>(W, x, ldx, y, T, beta, st);
+  else launch_umma_i<false>(W, x, ldx, y, T, beta, st);
+}
+
+int umma_gemm_status() {
+  int v = 0;
+  RB_CUDA(cudaMemcpy(&v, status_word(), sizeof(int), cudaMemcpyDeviceToHost));
+  return v;
+}
+
+}  // namespace rb200

@@ -114,6 +114,10 @@ def gemm(w, x, y, beta=0.0, scale=None) -> torch.Tensor:
     return y
 
 
+def gemm_status() -> int:
+    return _lib.lib().rb200_gemm_status()
+
+
 def rmsnorm(x, w, out, eps, rows=None) -> torch.Tensor:
     R = out.shape[0]
     _lib.check(_lib.lib().rb200_rmsnorm(_p(x), _p(rows), _p(w), _p(out), R, x.shape[1], out.stride(0), eps, _stream()))
