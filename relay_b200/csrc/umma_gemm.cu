@@ -21,10 +21,17 @@
 //            so the fp16 copy of the matrix exists only in shared memory.
 // Weight bytes are read from HBM once per token tile; activations come from L2.
 //
+// Matrices with few 128-row tiles (the attention output and down projections have 32) would
+// leave most SMs idle, so K is split across a thread-block cluster: each CTA of the cluster
+// accumulates its k range in its own TMEM, parks the partial tile in its shared memory, and
+// after a cluster barrier every CTA adds one slice of the tile from all members' shared
+// memory over DSMEM in a fixed order (deterministic, no atomics, no global scratch).
+//
 // Every mbarrier wait is bounded: on exhaustion the kernel records a code in `status`,
 // stops issuing work, and still releases its TMEM before it returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "kernels.h"
@@ -115,6 +122,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t cta_rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta_rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(
@@ -193,7 +210,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * kTileM, tok0 = blockIdx.y * BN;
-  const int nk = K / kBlockK;
+  const int splits = gridDim.z, split = blockIdx.z;  // the cluster spans z: split == rank in the cluster
+  const int nk_all = K / kBlockK;
+  const int kb_begin = static_cast<int>(static_cast<long long>(nk_all) * split / splits);
+  const int nk = static_cast<int>(static_cast<long long>(nk_all) * (split + 1) / splits) - kb_begin;
 
   if (warp == 0 && lane == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -223,9 +243,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         ok = mbar_wait(empty_bar + 8 * s, ((kb / NS) & 1) ^ 1);
         if (!ok) break;
         mbar_expect_tx(full_bar + 8 * s, (INT8 ? S::kRawBytes : S::kABytes) + S::kBBytes);
-        if (INT8) tma_load_2d(sRaw + s * S::kRawBytes, &map_w, kb * kBlockK, m0, full_bar + 8 * s);
-        else tma_load_2d(sA + s * S::kABytes, &map_w, kb * kBlockK, m0, full_bar + 8 * s);
-        tma_load_2d(sB + s * S::kBBytes, &map_x, kb * kBlockK, tok0, full_bar + 8 * s);
+        const int kx = (kb_begin + kb) * kBlockK;
+        if (INT8) tma_load_2d(sRaw + s * S::kRawBytes, &map_w, kx, m0, full_bar + 8 * s);
+        else tma_load_2d(sA + s * S::kABytes, &map_w, kx, m0, full_bar + 8 * s);
+        tma_load_2d(sB + s * S::kBBytes, &map_x, kx, tok0, full_bar + 8 * s);
       }
       if (!ok) atomicExch(status, 1);
     }
@@ -277,28 +298,64 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     bool done = mbar_wait(accum_bar, 0);
     if (!done) atomicExch(status, 4);
     tc_fence_after();
-    if (done && ok) {
-      const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
-      const int n = m0 + quarter * 32 + lane;
-      const float sc = (INT8 && n < N) ? scale[n] : 1.0f;
+    const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
+    const int row = quarter * 32 + lane;
+    const int n = m0 + row;
+    const float sc = (INT8 && n < N) ? scale[n] : 1.0f;
+    if (splits == 1) {
+      if (done && ok) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+          tmem_ld_wait();
+          if (n < N) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int tok = tok0 + c0 + j;
+              if (tok < T) {
+                float* d = y + static_cast<long long>(tok) * N + n;
+                const float r = __uint_as_float(v[j]) * sc;
+                *d = beta != 0.f ? r + beta * *d : r;
+              }
+            }
+          }
+        }
+      }
+    } else {
+      // Park this CTA's partial tile as red[token][row] in the (now idle) operand stages.
+      float* red = reinterpret_cast<float*>(gen_base);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t v[32];
         tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
         tmem_ld_wait();
-        if (n < N) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int tok = tok0 + c0 + j;
-            if (tok < T) {
-              float* d = y + static_cast<long long>(tok) * N + n;
-              const float r = __uint_as_float(v[j]) * sc;
-              *d = beta != 0.f ? r + beta * *d : r;
-            }
-          }
+        for (int j = 0; j < 32; ++j) red[(c0 + j) * kTileM + row] = __uint_as_float(v[j]);
+      }
+    }
+  }
+  if (splits > 1) {
+    cluster_sync_all();  // every member's partial tile is in its shared memory
+    if (warp >= 2) {
+      const int row = (warp & 3) * 32 + lane;
+      const int n = m0 + row;
+      const float sc = (INT8 && n < N) ? scale[n] : 1.0f;
+      const int per = (BN + splits - 1) / splits;  // token columns this CTA finishes
+      const int c_begin = split * per, c_end = min(BN, c_begin + per);
+      for (int c = c_begin; c < c_end; ++c) {
+        const int tok = tok0 + c;
+        if (tok >= T) break;
+        float acc = 0.f;
+        for (int r = 0; r < splits; ++r) acc += ld_dsmem_f32(base + static_cast<uint32_t>(c * kTileM + row) * 4, r);
+        if (n < N) {
+          float* d = y + static_cast<long long>(tok) * N + n;
+          const float v = acc * sc;
+          *d = beta != 0.f ? v + beta * *d : v;
         }
       }
     }
+    cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
   }
   tc_fence_before();
   __syncthreads();
@@ -372,9 +429,32 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
   const CUtensorMap mw = INT8 ? make_map(W.i8, 1, W.N, W.K, W.ld, kTileM, kBlockK, false)
                               : make_map(W.f16, 2, W.N, W.K, W.ld, kTileM, kBlockK, true);
   const CUtensorMap mx = make_map(x, 2, T, W.K, ldx, BN, kBlockK, true);
-  dim3 grid(div_up(W.N, kTileM), div_up(T, BN));
+  // Split K across a cluster when the tiles alone would leave SMs idle.
+  const int tiles = div_up(W.N, kTileM) * div_up(T, BN), nk = W.K / kBlockK;
+  int splits = std::max(1, std::min({8, sm_count() / tiles, nk / 4}));
+  if (static_cast<size_t>(BN) * kTileM * 4 > static_cast<size_t>(S::kStages) * S::kStageBytes) splits = 1;
+  static const int forced = [] {
+    const char* e = std::getenv("RB200_GEMM_SPLITS");
+    return e ? std::atoi(e) : 0;
+  }();
+  if (forced > 0) splits = std::min({forced, 8, std::max(1, nk)});
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(div_up(W.N, kTileM), div_up(T, BN), splits);
+  cfg.blockDim = dim3(kUmmaThreads);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   count_launch();
-  kernel<<<grid, kUmmaThreads, S::kTotal, st>>>(mw, mx, W.scale, y, T, W.N, W.K, beta, status_word());
+  int* status = status_word();
+  const float* scale = W.scale;
+  const int N = W.N, K = W.K;
+  RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, mw, mx, scale, y, T, N, K, beta, status));
 }
 
 template <bool INT8>
