@@ -217,7 +217,8 @@ typedef struct rb200_attn_shape {
   int32_t o_stride; /* halves between consecutive tokens' output rows */
 } rb200_attn_shape;
 
-#define RB200_DECODE_SLICE 512 /* keys per split-context slice (engine/src/cuda_kernels.cuh:180-190) */
+#define RB200_DECODE_SLICE 512 /* keys per split-context slice (engine/src/cuda_kernels.cuh:180-190); slices grow in
+                                  multiples of it when a batch has enough (token, KV head) pairs to fill the GPU */
 
 /* Scratch the split decode needs for n_decode tokens whose longest context is max_ctx:
  * per (token, head, slice) D + 2 floats. Returns bytes. */

@@ -19,6 +19,8 @@
 //
 // Page addressing everywhere is KVLayout::offset (engine/include/relay/kv_cache.h:32-35):
 // key j of a sequence lives at ((table[j / bs] * kv_heads + kvh) * bs + j % bs) * D.
+#include <cstdlib>
+
 #include "kernels.h"
 
 namespace rb200 {
@@ -99,19 +101,19 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
 decode_split_kernel(const float* __restrict__ q, TokenMeta m, const int* __restrict__ decode_tokens,
                     const __half* __restrict__ kc, const __half* __restrict__ vc, float* __restrict__ part_o,
                     float* __restrict__ part_ml, __half* __restrict__ out, int heads, int kv_heads, int bs,
-                    int bs_shift, int q_stride, int o_stride, float scale_log2e, int max_parts) {
+                    int bs_shift, int q_stride, int o_stride, float scale_log2e, int max_parts, int slice) {
   constexpr int CH = D / 8;               // 16-byte chunks per K/V row
   constexpr int TILE_HALVES = 16 * D;     // one 16-key tile of K (or V)
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ int s_table[kDecodeSlice];   // block ids covering the slice (block_size 1 needs 512)
+  __shared__ int s_table[kDecodeSlice];   // block ids covering the slice: slice / block_size <= 512 entries
   __shared__ float s_m[kDecWarps][16], s_l[kDecWarps][16];
 
   const int di = blockIdx.x, kvh = blockIdx.y, part = blockIdx.z;
   const int tok = decode_tokens[di];
   const int ctx = m.pos[tok] + 1;
-  const int k0 = part * kDecodeSlice;
+  const int k0 = part * slice;
   if (k0 >= ctx) return;
-  const int k1 = min(ctx, k0 + kDecodeSlice);
+  const int k1 = min(ctx, k0 + slice);
   const int ntiles = (k1 - k0 + 15) >> 4;
   const int G = heads / kv_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -327,27 +329,54 @@ decode_split_kernel(const float* __restrict__ q, TokenMeta m, const int* __restr
 }
 
 // out = sum_p e^(m_p - M) O_p / sum_p e^(m_p - M) l_p over the slices the token's context
-// reaches (engine/src/cuda_kernels.cuh:341-362). One warp per (decode token, head).
+// reaches (engine/src/cuda_kernels.cuh:341-362). One warp per (decode token, head): lanes
+// first work across the slices (max and sum by warp reduction), then across the head
+// dimension, four values per lane, with each slice's weight broadcast by shuffle.
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int* __restrict__ decode_tokens, const int* __restrict__ pos,
                                     __half* __restrict__ out, int heads, int D, int o_stride, int max_parts,
-                                    int n_pairs) {
+                                    int n_pairs, int slice) {
   const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (pair >= n_pairs) return;
   const int lane = threadIdx.x & 31;
   const int di = pair / heads, h = pair - di * heads;
   const int tok = decode_tokens[di];
-  const int parts = (pos[tok] + 1 + kDecodeSlice - 1) / kDecodeSlice;
+  const int parts = (pos[tok] + slice) / slice;  // ceil((pos + 1) / slice)
   const long long base = static_cast<long long>(pair) * max_parts;
   float M = -INFINITY;
-  for (int p = 0; p < parts; ++p) M = fmaxf(M, part_ml[(base + p) * 2]);
+  for (int p0 = 0; p0 < parts; p0 += 32)
+    M = fmaxf(M, p0 + lane < parts ? part_ml[(base + p0 + lane) * 2] : -INFINITY);
+  M = warp_max(M);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
   float L = 0.f;
-  for (int p = 0; p < parts; ++p) L += __expf(part_ml[(base + p) * 2] - M) * part_ml[(base + p) * 2 + 1];
+  for (int p0 = 0; p0 < parts; p0 += 32) {
+    float w = 0.f, wl = 0.f;
+    if (p0 + lane < parts) {
+      const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + p0 + lane) * 2);
+      w = __expf(ml.x - M);
+      wl = w * ml.y;
+    }
+    L += wl;
+    const int np = min(32, parts - p0);
+    for (int d0 = lane * 4; d0 < D; d0 += 128) {  // D <= 128: a single trip
+      for (int p = 0; p < np; ++p) {
+        const float wp = __shfl_sync(0xffffffffu, w, p);
+        const float4 o = *reinterpret_cast<const float4*>(part_o + (base + p0 + p) * D + d0);
+        acc[0] += wp * o.x;
+        acc[1] += wp * o.y;
+        acc[2] += wp * o.z;
+        acc[3] += wp * o.w;
+      }
+    }
+    if (lane * 4 >= D)  // lanes past the head dimension still take part in the shuffles
+      for (int p = 0; p < np; ++p) (void)__shfl_sync(0xffffffffu, w, p);
+  }
+  L = warp_sum(L);
   const float inv = 1.0f / L;
-  for (int d = lane; d < D; d += 32) {
-    float acc = 0.f;
-    for (int p = 0; p < parts; ++p) acc += __expf(part_ml[(base + p) * 2] - M) * part_o[(base + p) * D + d];
-    out[static_cast<long long>(tok) * o_stride + h * D + d] = __float2half_rn(acc * inv);
+  if (lane * 4 < D) {
+    __half2* o = reinterpret_cast<__half2*>(out + static_cast<long long>(tok) * o_stride + h * D + lane * 4);
+    o[0] = __floats2half2_rn(acc[0] * inv, acc[1] * inv);
+    o[1] = __floats2half2_rn(acc[2] * inv, acc[3] * inv);
   }
 }
 
@@ -584,7 +613,7 @@ void raise_smem(K kernel, size_t bytes) {
 
 template <int D, bool CONTIG, bool WIDE>
 void launch_decode_t(const AttnShape& s, const float* q, const TokenMeta& m, const int* decode_tokens, int n_decode,
-                     int parts, const __half* kc, const __half* vc, float* part_o, float* part_ml, __half* out,
+                     int parts, int slice, const __half* kc, const __half* vc, float* part_o, float* part_ml, __half* out,
                      cudaStream_t st) {
   static bool configured = false;  // benign race: the call is idempotent
   auto kernel = decode_split_kernel<D, CONTIG, WIDE>;
@@ -597,18 +626,18 @@ void launch_decode_t(const AttnShape& s, const float* q, const TokenMeta& m, con
   count_launch();
   kernel<<<grid, kDecWarps * 32, decode_smem_bytes<D>(), st>>>(q, m, decode_tokens, kc, vc, part_o, part_ml, out, s.heads,
                                                                s.kv_heads, s.block_size, shift_of(s.block_size),
-                                                               s.q_stride, s.o_stride, scale_log2e, parts);
+                                                               s.q_stride, s.o_stride, scale_log2e, parts, slice);
 }
 
 template <int D>
 void launch_decode_d(const AttnShape& s, const float* q, const TokenMeta& m, const int* decode_tokens, int n_decode,
-                     int parts, const __half* kc, const __half* vc, float* part_o, float* part_ml, __half* out,
+                     int parts, int slice, const __half* kc, const __half* vc, float* part_o, float* part_ml, __half* out,
                      cudaStream_t st) {
   const bool contig = s.block_size % 16 == 0, wide = s.heads / s.kv_heads > 8;
-  if (contig && !wide) launch_decode_t<D, true, false>(s, q, m, decode_tokens, n_decode, parts, kc, vc, part_o, part_ml, out, st);
-  else if (contig) launch_decode_t<D, true, true>(s, q, m, decode_tokens, n_decode, parts, kc, vc, part_o, part_ml, out, st);
-  else if (!wide) launch_decode_t<D, false, false>(s, q, m, decode_tokens, n_decode, parts, kc, vc, part_o, part_ml, out, st);
-  else launch_decode_t<D, false, true>(s, q, m, decode_tokens, n_decode, parts, kc, vc, part_o, part_ml, out, st);
+  if (contig && !wide) launch_decode_t<D, true, false>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st);
+  else if (contig) launch_decode_t<D, true, true>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st);
+  else if (!wide) launch_decode_t<D, false, false>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st);
+  else launch_decode_t<D, false, true>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st);
 }
 
 template <int D>
@@ -646,22 +675,35 @@ void launch_decode_attention(const AttnShape& s, const float* q, const TokenMeta
                              int n_decode, int max_ctx, const __half* kc, const __half* vc, float* scratch,
                              __half* out, cudaStream_t st) {
   if (n_decode == 0) return;
-  const int parts = div_up(std::max(max_ctx, 1), kDecodeSlice);
+  // Slices are 512 keys when the batch alone would not fill the GPU; with many (token, KV
+  // head) pairs they grow (in steps of 512, up to 512 block-table entries) until a few waves
+  // of CTAs remain, which spares the partial results and, at one slice, the merge.
+  const long long pairs_kv = static_cast<long long>(n_decode) * s.kv_heads;
+  static const int waves = [] {
+    const char* e = std::getenv("RB200_DECODE_WAVES");
+    return e && std::atoi(e) > 0 ? std::atoi(e) : 8;
+  }();
+  const long long want_ctas = static_cast<long long>(waves) * sm_count();
+  const int want_parts = static_cast<int>(std::max<long long>(1, div_up(want_ctas, pairs_kv)));
+  int slice = round_up(std::max(1, div_up(std::max(max_ctx, 1), want_parts)), kDecodeSlice);
+  slice = static_cast<int>(std::min<long long>(slice, static_cast<long long>(kDecodeSlice) * s.block_size));
+  slice = std::max(kDecodeSlice, slice / kDecodeSlice * kDecodeSlice);
+  const int parts = div_up(std::max(max_ctx, 1), slice);
   RB_REQUIRE(parts <= 65535, "decode attention: context too long for one launch");
   float* part_o = scratch;
   float* part_ml = scratch + static_cast<size_t>(n_decode) * s.heads * parts * s.D;
   switch (s.D) {
-    case 16: launch_decode_d<16>(s, q, m, decode_tokens, n_decode, parts, kc, vc, part_o, part_ml, out, st); break;
-    case 32: launch_decode_d<32>(s, q, m, decode_tokens, n_decode, parts, kc, vc, part_o, part_ml, out, st); break;
-    case 64: launch_decode_d<64>(s, q, m, decode_tokens, n_decode, parts, kc, vc, part_o, part_ml, out, st); break;
-    case 128: launch_decode_d<128>(s, q, m, decode_tokens, n_decode, parts, kc, vc, part_o, part_ml, out, st); break;
+    case 16: launch_decode_d<16>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st); break;
+    case 32: launch_decode_d<32>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st); break;
+    case 64: launch_decode_d<64>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st); break;
+    case 128: launch_decode_d<128>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st); break;
     default: fail(RB200_ERR_INVALID_ARGUMENT, "decode attention: head_dim must be 16, 32, 64 or 128");
   }
   if (parts > 1) {
     const int pairs = n_decode * s.heads;
     count_launch();
     decode_merge_kernel<<<div_up(pairs, 4), 128, 0, st>>>(part_o, part_ml, decode_tokens, m.pos, out, s.heads, s.D,
-                                                          s.o_stride, parts, pairs);
+                                                          s.o_stride, parts, pairs, slice);
   }
 }
 

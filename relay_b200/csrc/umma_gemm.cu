@@ -310,14 +310,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
           tmem_ld_wait();
           if (n < N) {
+            float* d0 = y + static_cast<long long>(tok0 + c0) * N + n;
+            const int nt = min(32, T - tok0 - c0);  // valid token columns of this chunk
+            if (beta != 0.f) {
+              float old[32];  // all loads first, so that they are in flight together
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int tok = tok0 + c0 + j;
-              if (tok < T) {
-                float* d = y + static_cast<long long>(tok) * N + n;
-                const float r = __uint_as_float(v[j]) * sc;
-                *d = beta != 0.f ? r + beta * *d : r;
-              }
+              for (int j = 0; j < 32; ++j) old[j] = j < nt ? d0[static_cast<long long>(j) * N] : 0.f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < nt) d0[static_cast<long long>(j) * N] = __uint_as_float(v[j]) * sc + beta * old[j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < nt) d0[static_cast<long long>(j) * N] = __uint_as_float(v[j]) * sc;
             }
           }
         }
@@ -342,16 +347,35 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const int n = m0 + row;
       const float sc = (INT8 && n < N) ? scale[n] : 1.0f;
       const int per = (BN + splits - 1) / splits;  // token columns this CTA finishes
-      const int c_begin = split * per, c_end = min(BN, c_begin + per);
-      for (int c = c_begin; c < c_end; ++c) {
-        const int tok = tok0 + c;
-        if (tok >= T) break;
-        float acc = 0.f;
-        for (int r = 0; r < splits; ++r) acc += ld_dsmem_f32(base + static_cast<uint32_t>(c * kTileM + row) * 4, r);
+      const int c_begin = split * per, c_end = min(min(BN, c_begin + per), T - tok0);
+      uint32_t peer[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)  // fully unrolled so that peer[] stays in registers
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[r]) : "r"(base + static_cast<uint32_t>(row) * 4), "r"(r < splits ? r : 0));
+      for (int c = c_begin; c < c_end; c += 8) {
+        float acc[8], old[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          acc[j] = 0.f;
+          old[j] = (beta != 0.f && n < N && c + j < c_end) ? y[static_cast<long long>(tok0 + c + j) * N + n] : 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {  // members in rank order: the sum is the same on every run
+          if (r >= splits) break;
+          float part[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            part[j] = 0.f;
+            if (c + j < c_end)
+              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[j]) : "r"(peer[r] + static_cast<uint32_t>((c + j) * kTileM) * 4) : "memory");
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += part[j];
+        }
         if (n < N) {
-          float* d = y + static_cast<long long>(tok) * N + n;
-          const float v = acc * sc;
-          *d = beta != 0.f ? v + beta * *d : v;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (c + j < c_end) y[static_cast<long long>(tok0 + c + j) * N + n] = acc[j] * sc + beta * old[j];
         }
       }
     }
