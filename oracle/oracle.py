@@ -31,6 +31,9 @@ def build(reference: bool = True) -> None:
     ref_root = os.environ.get("RELAY_REFERENCE", "/root/reference")
     if reference and os.path.isdir(os.path.join(ref_root, "engine", "src")):
         subprocess.run(["make", "-s", "-j8", "-C", HERE, "ref", f"REF={ref_root}"], check=True)
+        if os.path.exists(os.path.join(os.path.dirname(HERE), "relay_b200", "librelay_b200.so")):
+            # relay's own test programs linked against the B200 backend (tests/test_gpu_reference_suite.py)
+            subprocess.run(["make", "-s", "-j8", "-C", HERE, "reftests", f"REF={ref_root}"], check=True)
 
 
 def lib() -> C.CDLL:
