@@ -106,11 +106,13 @@ class ClockSampler:
 
 
 def measured_peaks() -> tuple:
+    """(HBM GB/s, dense bf16 TFLOP/s burst, "measured" | "fallback")."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         with open(p) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
 
 
 # ---- the CPU arm ---------------------------------------------------------------------------
@@ -160,6 +162,117 @@ def cpu_arm(args, steps: int, warmup: int) -> dict:
                       f"{step * 1e3:.0f} ms per step measured ({head * 1e3:.0f} ms of it the LM head); layers scaled "
                       f"linearly to {args.layers} -> {full * 1e3:.0f} ms per {S}-token step",
             "ms_per_step_sample": step * 1e3}
+
+
+# ---- the other kernels of the metric, timed one at a time ----------------------------------
+
+def time_in_graph(fn, n_variants: int, iters: int = 20) -> float:
+    """Milliseconds per call of fn(i), i cycling over n_variants independent buffer sets
+    (together larger than L2), measured with CUDA events around a CUDA graph of `iters`
+    back-to-back launches so that host launch cost is not in the number."""
+    import torch
+    for i in range(min(n_variants, 3)):
+        fn(i)  # warm-up: first-use attribute calls happen outside the capture
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            for i in range(iters):
+                fn(i % n_variants)
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) / iters)
+    return best
+
+
+def op_suite(peak_gbs: float, peak_tflops: float) -> dict:
+    """Paged split-decode attention (32 sequences, contexts uniform in [1024, 4096], 32 q / 8 kv
+    heads, D 128), weight-only int8 GEMV / GEMM on the Llama-3-8B projection shapes, and flash
+    prefill (32 q / 4 kv heads, D 64, a 2048-token prompt as four 512-token chunks)."""
+    import torch
+    from relay_b200 import ops
+    from tests.workloads import c2_contexts
+    out = {}
+    dev = "cuda"
+    # -- decode attention --
+    heads, kvh, D, bs, nblk = 32, 8, 128, 16, 16384
+    ctxs = c2_contexts()
+    rng = np.random.Generator(np.random.PCG64(2))
+    perm = rng.permutation(nblk).astype(np.int32)
+    pos, seq, toff, tables, used = [], [], [], [], 0
+    for i, c in enumerate(ctxs):
+        nb = (c + bs - 1) // bs
+        while len(tables) % 4:
+            tables.append(0)
+        toff.append(len(tables))
+        tables += perm[used:used + nb].tolist()
+        used += nb
+        pos.append(c - 1)
+        seq.append(i)
+    meta = ops.TokenMeta.from_host(pos, seq, toff, tables)
+    shape = ops.attn_shape(heads, kvh, D, bs)
+    pools = [(torch.randn((nblk, kvh, bs, D), device=dev, dtype=torch.float16),
+              torch.randn((nblk, kvh, bs, D), device=dev, dtype=torch.float16)) for _ in range(2)]  # 2 x 1 GiB > L2
+    q = torch.randn((32, (heads + 2 * kvh) * D), device=dev)
+    o = torch.zeros((32, heads * D), device=dev, dtype=torch.float16)
+    toks = torch.arange(32, dtype=torch.int32, device=dev)
+    scratch = torch.empty(ops.decode_scratch_bytes(shape, 32, max(ctxs)), dtype=torch.uint8, device=dev)
+    ms = time_in_graph(lambda i: ops.decode_attention(shape, q, meta, toks, max(ctxs), pools[i][0], pools[i][1], o, scratch), 2)
+    nbytes = sum(ctxs) * (2 * kvh * D * 2) + 32 * heads * D * 6 + sum((c + bs - 1) // bs for c in ctxs) * 4
+    out["paged_decode_attention"] = {"workload": "32 seqs, ctx U[1024,4096], 32q/8kv heads, D128, block 16, 16384-block pool",
+                                     "us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / peak_gbs,
+                                     "algorithmic_bytes": nbytes}
+    del pools
+    # -- int8 GEMV / GEMM and the fp16 GEMV --
+    lin = {}
+    for (K, N) in ((4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)):
+        R = max(2, int(300e6 // (N * K)) + 1)
+        Ws = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev) for _ in range(R)]
+        sc = torch.rand(N, device=dev) * 0.019 + 0.001
+        scr = ops.gemv_scratch(N, K)
+        for T in (1, 8, 64):
+            x = torch.randn((T, K), device=dev).half()
+            y = torch.zeros((T, N), device=dev)
+            if T <= 8:
+                ms = time_in_graph(lambda i: ops.gemv_int8(Ws[i], sc, x, y, 0.0, scr), R)
+            else:
+                ms = time_in_graph(lambda i: ops.gemm(Ws[i], x, y, 0.0, sc), R)
+            b = N * K + 4 * N + 2 * T * K + 4 * T * N
+            lin[f"{K}->{N} T={T}"] = {"us": ms * 1e3, "gbs": b / ms / 1e6, "frac_of_measured_hbm": b / ms / 1e6 / peak_gbs}
+        del Ws
+    out["int8_linear"] = lin
+    # -- flash prefill --
+    heads, kvh, D, bs = 32, 4, 64, 16
+    nblk = 2048 // bs
+    kp = torch.randn((nblk, kvh, bs, D), device=dev, dtype=torch.float16)
+    vp = torch.randn((nblk, kvh, bs, D), device=dev, dtype=torch.float16)
+    table = torch.arange(nblk, dtype=torch.int32, device=dev)
+    chunks = []
+    for c in range(4):
+        p = torch.arange(512 * c, 512 * (c + 1), dtype=torch.int32, device=dev)
+        m = ops.TokenMeta(p, torch.zeros(512, dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev), table)
+        tiles = torch.tensor([[r, 64] for r in range(0, 512, 64)], dtype=torch.int32, device=dev).flatten()
+        chunks.append((m, tiles))
+    q = torch.randn((512, (heads + 2 * kvh) * D), device=dev)
+    o = torch.zeros((512, heads * D), device=dev, dtype=torch.float16)
+    shape = ops.attn_shape(heads, kvh, D, bs)
+
+    def prefill_all(_):
+        for m, tiles in chunks:
+            ops.prefill_attention(shape, q, m, tiles, kp, vp, o)
+    ms = time_in_graph(prefill_all, 1, iters=10)
+    flops = 4 * D * heads * sum(p + 1 for p in range(2048))
+    out["flash_prefill_attention"] = {"workload": "2048-token prompt as 4 x 512 chunks, 32q/4kv heads, D64, causal", "us": ms * 1e3,
+                                      "tflops": flops / ms / 1e9, "frac_of_measured_bf16": flops / ms / 1e9 / peak_tflops,
+                                      "tok_per_s": 2048 / (ms * 1e-3)}
+    return out
 
 
 # ---- the GPU arm ---------------------------------------------------------------------------
@@ -250,7 +363,7 @@ def gpu_arm(args) -> dict:
         sum((c + bs - 1) // bs for c in ctxs) * 4
     calls = max(int(prof["decode_attn_calls"]), 1)
     attn_ms = prof["decode_attn_ms"] / calls
-    peak, peak_kind = measured_peaks()
+    peak, peak_tf, peak_kind = measured_peaks()
     achieved = attn_bytes / (attn_ms * 1e-3) / 1e9 if attn_ms > 0 else 0.0
     weight_bytes = sum(int(np.prod(s)) for n, s in tensor_shapes(cfg).items() if n != "embed") * (1 if args.int8 else 2)
     step_bytes = attn_bytes * cfg.layers + weight_bytes
@@ -274,6 +387,10 @@ def gpu_arm(args) -> dict:
                           "achieved_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9, "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak},
         "clocks": clk.summary(), "clocks_e2e": clk_e2e.summary(),
     }
+    if world == 1 and not args.no_ops:
+        del be
+        torch.cuda.empty_cache()
+        line["ops"] = op_suite(peak, peak_tf)
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:
@@ -294,6 +411,7 @@ def main() -> None:
     ap.add_argument("--cpu-layers", type=int, default=2)
     ap.add_argument("--cpu-seqs", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ops", action="store_true", help="skip the single-kernel measurements")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else max(args.warmup, 1)
 
