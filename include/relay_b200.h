@@ -231,6 +231,26 @@ int rb200_decode_attention(const rb200_attn_shape* s, const float* q, const rb20
                            const int32_t* decode_tokens, int n_decode, int max_ctx, const void* k_pool,
                            const void* v_pool, void* scratch, size_t scratch_bytes, void* out, void* stream);
 
+/* No counterpart in the reference. The same split-context decode attention for callers
+ * that cannot allocate device memory where they need it: a serving process that has
+ * already handed every free byte of the GPU to its KV pool (a cudaMalloc there fails), or
+ * a latency-critical loop that must not hit the device-wide stall of cudaMalloc/cudaFree.
+ * The partial results live in a fixed RB200_STATIC_DECODE_SCRATCH_BYTES array inside the
+ * library image (each GPU that loads the library carries it until the process exits);
+ * inputs and outputs are still the caller's. This call allocates nothing, on the host side
+ * or the device side. Limits and rules:
+ *  - a batch whose partials (rb200_decode_scratch_bytes) exceed the array is rejected with
+ *    an invalid-argument error naming both sizes;
+ *  - the first call on each device looks up the array's device address; make that first
+ *    call before starting any stream capture on that device;
+ *  - all calls share the one array, which keeps whatever the previous call left (nothing
+ *    in it needs clearing: each call overwrites what it later reads); two calls that overlap
+ *    on the GPU, e.g. on different streams, race on it and must be serialised by the caller. */
+#define RB200_STATIC_DECODE_SCRATCH_BYTES (8u << 20)
+int rb200_decode_attention_static(const rb200_attn_shape* s, const float* q, const rb200_token_meta* m,
+                                  const int32_t* decode_tokens, int n_decode, int max_ctx, const void* k_pool,
+                                  const void* v_pool, void* out, void* stream);
+
 /* Causal flash attention for chunks of several tokens over the paged cache (replaces
  * flash_prefill_kernel, engine/src/cuda_kernels.cuh:51-178). tiles[i] = {first batch row,
  * row count <= RB200_PREFILL_ROWS} as built by engine/src/cuda_backend.cu:533-545. */

@@ -17,6 +17,7 @@ ERR_INVALID_ARGUMENT, ERR_OUT_OF_RANGE, ERR_RUNTIME, ERR_LOGIC = 1, 2, 3, 4
 DECODE_SLICE = 512
 PREFILL_ROWS = 64
 NCCL_ID_BYTES = 128
+STATIC_DECODE_SCRATCH_BYTES = 8 << 20
 
 LAYER_CB = C.CFUNCTYPE(None, C.c_void_p, C.c_int)
 
@@ -69,6 +70,7 @@ SIGNATURES = {
     "rb200_kv_hop_sync": (I, [P, I]),
     "rb200_decode_scratch_bytes": (SZ, [C.POINTER(CAttnShape), I, I]),
     "rb200_decode_attention": (I, [C.POINTER(CAttnShape), P, C.POINTER(CTokenMeta), P, I, I, P, P, P, SZ, P, P]),
+    "rb200_decode_attention_static": (I, [C.POINTER(CAttnShape), P, C.POINTER(CTokenMeta), P, I, I, P, P, P, P]),
     "rb200_prefill_attention": (I, [C.POINTER(CAttnShape), P, C.POINTER(CTokenMeta), P, I, P, P, P, P]),
     "rb200_reference_attention": (I, [C.POINTER(CAttnShape), P, C.POINTER(CTokenMeta), I, P, P, P, P]),
     "rb200_gemv_scratch_bytes": (SZ, [I, I]),

@@ -20,6 +20,7 @@
 // Page addressing everywhere is KVLayout::offset (engine/include/relay/kv_cache.h:32-35):
 // key j of a sequence lives at ((table[j / bs] * kv_heads + kvh) * bs + j % bs) * D.
 #include <cstdlib>
+#include <mutex>
 
 #include "kernels.h"
 
@@ -731,6 +732,39 @@ void launch_reference_attention(const AttnShape& s, const float* q, const TokenM
 
 }  // namespace rb200
 
+// ---- decode attention for callers that cannot allocate -----------------------------------
+//
+// The split-context kernel parks one partial result per (token, head, slice) in global
+// memory before the merge. rb200_decode_attention takes that scratch from its caller; the
+// entry point below keeps it in a fixed array that is part of the loaded library image, so a
+// caller needs no device allocation of its own at the moment it wants attention. Every GPU
+// that loads the library holds these bytes until the process exits, hence the small cap.
+namespace rb200 {
+namespace {
+
+static __device__ __align__(256) unsigned char g_static_decode_scratch[RB200_STATIC_DECODE_SCRATCH_BYTES];
+
+// Device address of the array on the current device. In host code the array's name only
+// stands for the symbol; the address a kernel can use comes from cudaGetSymbolAddress, asked
+// once per device with that device current.
+float* static_decode_scratch() {
+  static void* addr[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  RB_CUDA(cudaGetDevice(&dev));
+  RB_REQUIRE(dev >= 0 && dev < 64, "decode attention: device index out of range");
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    RB_CUDA(cudaGetSymbolAddress(&p, g_static_decode_scratch));
+    addr[dev] = p;
+  }
+  return static_cast<float*>(addr[dev]);
+}
+
+}  // namespace
+}  // namespace rb200
+
 // ---- C boundary -----------------------------------------------------------------------
 
 using namespace rb200;
@@ -765,6 +799,30 @@ int rb200_decode_attention(const rb200_attn_shape* s, const float* q, const rb20
     launch_decode_attention(sh, q, meta_of(m), decode_tokens, n_decode, max_ctx, static_cast<const __half*>(k_pool),
                             static_cast<const __half*>(v_pool), static_cast<float*>(scratch), static_cast<__half*>(out),
                             as_stream(stream));
+    RB_CUDA(cudaGetLastError());
+    return 0;
+  });
+}
+
+int rb200_decode_attention_static(const rb200_attn_shape* s, const float* q, const rb200_token_meta* m,
+                                  const int32_t* decode_tokens, int n_decode, int max_ctx, const void* k_pool,
+                                  const void* v_pool, void* out, void* stream) {
+  return guarded([&] {
+    const AttnShape sh = shape_of(s);
+    check_shape(sh);
+    RB_REQUIRE(fast_attention_supported(sh), "decode attention: head_dim must be 16/32/64/128 and heads/kv_heads <= 16");
+    RB_REQUIRE(n_decode >= 0 && max_ctx >= 1, "decode attention: bad batch");
+    const size_t need = decode_scratch_bytes(sh, n_decode, max_ctx);
+    if (need > static_cast<size_t>(RB200_STATIC_DECODE_SCRATCH_BYTES))
+      fail(RB200_ERR_INVALID_ARGUMENT, "decode attention (static scratch): this batch needs " + std::to_string(need) +
+                                           " bytes of partial results, the built-in buffer holds " +
+                                           std::to_string(static_cast<size_t>(RB200_STATIC_DECODE_SCRATCH_BYTES)) +
+                                           "; use rb200_decode_attention with caller-owned scratch");
+    // The first call on a device looks the buffer's address up (no allocation). Nothing in the
+    // buffer has to start at zero: every slice's partial is written before the merge reads it.
+    float* scratch = static_decode_scratch();
+    launch_decode_attention(sh, q, meta_of(m), decode_tokens, n_decode, max_ctx, static_cast<const __half*>(k_pool),
+                            static_cast<const __half*>(v_pool), scratch, static_cast<__half*>(out), as_stream(stream));
     RB_CUDA(cudaGetLastError());
     return 0;
   });

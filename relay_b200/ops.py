@@ -67,6 +67,18 @@ def decode_attention(shape: CAttnShape, q: torch.Tensor, meta: TokenMeta, decode
     return out
 
 
+def decode_attention_static(shape: CAttnShape, q, meta: TokenMeta, decode_tokens, max_ctx: int, k_pool, v_pool,
+                            out) -> torch.Tensor:
+    """decode_attention without caller scratch: the partial results go to the fixed buffer
+    inside the library (at most _lib.STATIC_DECODE_SCRATCH_BYTES; larger batches raise
+    ValueError). Allocates nothing; calls sharing a GPU must not overlap."""
+    m = meta.c()
+    _lib.check(_lib.lib().rb200_decode_attention_static(C.byref(shape), _p(q), C.byref(m), _p(decode_tokens),
+                                                        decode_tokens.numel(), max_ctx, _p(k_pool), _p(v_pool), _p(out),
+                                                        _stream()))
+    return out
+
+
 def prefill_attention(shape: CAttnShape, q, meta: TokenMeta, tiles: torch.Tensor, k_pool, v_pool, out) -> torch.Tensor:
     m = meta.c()
     _lib.check(_lib.lib().rb200_prefill_attention(C.byref(shape), _p(q), C.byref(m), _p(tiles), tiles.numel() // 2,

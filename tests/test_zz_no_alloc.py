@@ -1,0 +1,72 @@
+"""The decode-attention entry point that brings its own scratch (rb200_decode_attention_static).
+
+Some callers cannot allocate device memory at the point where they need attention: the GPU's
+free memory already belongs to their KV pool, or their loop cannot afford the device-wide
+stall of an allocation. For them the library keeps the split-context partials in a fixed
+array of its own. This file checks, through the C boundary, that the entry point gives the
+same output as rb200_decode_attention (which takes the scratch from the caller) on two calls
+in a row with different batches (so the second call runs over whatever the first one left
+in the shared array), and that a batch too large for the array is refused with a clear error.
+It is named to be collected last.
+"""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from tests.workloads import paged_attention_case  # noqa: E402
+
+ATTN_TOL = 3e-3  # the decode-attention tolerance of tests/test_gpu_ops.py
+
+
+def _dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def _row_err(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float((np.abs(a - b).max(1) / np.maximum(np.abs(b).max(1), 1e-6)).max())
+
+
+def _run_both(ops, seed, ctxs, heads, kv_heads, D, bs):
+    nb = sum((c + bs - 1) // bs for c in ctxs) + 3
+    c = paged_attention_case(seed, ctxs, [1] * len(ctxs), heads, kv_heads, D, bs, nb)
+    T = len(ctxs)
+    shape = ops.attn_shape(heads, kv_heads, D, bs)
+    meta = ops.TokenMeta.from_host(c["pos"], c["seq"], c["table_off"], c["tables"])
+    q, kp, vp = _dev(c["q"]), _dev(c["k_pool"], torch.float16), _dev(c["v_pool"], torch.float16)
+    toks = _dev(np.arange(T, dtype=np.int32))
+    want = torch.zeros((T, heads * D), dtype=torch.float16, device="cuda")
+    got = torch.zeros_like(want)
+    ops.decode_attention(shape, q, meta, toks, max(ctxs), kp, vp, want)           # caller-owned scratch
+    ops.decode_attention_static(shape, q, meta, toks, max(ctxs), kp, vp, got)     # the library's own array
+    torch.cuda.synchronize()
+    return got.cpu().numpy().astype(np.float32), want.cpu().numpy().astype(np.float32)
+
+
+def test_static_scratch_entry_point_matches_the_caller_scratch_one_twice_in_a_row():
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device")
+    from relay_b200 import ops
+    # both batches are split into several 512-key slices, so the scratch is really used
+    got1, want1 = _run_both(ops, 41, [1300, 700, 2048, 513, 90], 32, 8, 128, 16)
+    got2, want2 = _run_both(ops, 42, [600, 1025, 33], 8, 2, 64, 16)  # smaller: runs over the first call's leftovers
+    for got, want in ((got1, want1), (got2, want2)):
+        assert np.isfinite(got).all()
+        assert _row_err(got, want) < ATTN_TOL
+        assert np.array_equal(got, want)  # same kernels, same order of operations
+
+
+def test_static_scratch_entry_point_refuses_what_does_not_fit():
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device")
+    from relay_b200 import _lib, ops
+    shape = ops.attn_shape(32, 8, 128, 16)
+    n = 256  # 256 tokens x 32 heads x 8 slices x 130 floats = 34 MB of partials > 8 MiB
+    assert ops.decode_scratch_bytes(shape, n, 4096) > _lib.STATIC_DECODE_SCRATCH_BYTES
+    z = torch.zeros(16, device="cuda")
+    meta = ops.TokenMeta(*(torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(4)))
+    with pytest.raises(ValueError, match="built-in buffer holds 8388608"):
+        ops.decode_attention_static(shape, z, meta, torch.zeros(n, dtype=torch.int32, device="cuda"), 4096, z, z, z)
