@@ -1,0 +1,146 @@
+"""Two GPUs of one box: the prefill -> decode KV hop over NCCL, and sequence-sharded replicas.
+
+Rank 0 prefills a prompt and streams every layer's blocks to rank 1 from inside the forward
+pass (the layer callback enqueues gather -> ncclSend on the copy stream, ordered behind the
+layer's event), rank 1 receives them into different block ids and decodes; the result must
+equal, bit for bit, rank 0 decoding on its own cache (the reference's
+"disaggregated == colocated", tests/test_transfer.cpp:236-330, with NVLink in place of the
+socket). Skipped on boxes with one GPU.
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _hop_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    from relay_b200.backend import Backend, make_cuda_backend
+    from relay_b200.parallel import broadcast_bytes
+    from relay_b200.types import ForwardBatch, SeqChunk
+    from tests.test_gpu_model import WIDE_CONFIGS, synthetic
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.cuda.set_device(rank)
+        cfg = WIDE_CONFIGS["d128_g4"]
+        w = synthetic(cfg, 12)
+        be = make_cuda_backend(w, 64, 16, device=rank, max_batch_tokens=512)
+        uid = Backend.nccl_unique_id() if rank == 0 else b""
+        uid = broadcast_bytes(uid, 128, src=0)
+        be.nccl_init(uid, world, rank)
+        rng = np.random.Generator(np.random.PCG64(21))
+        prompt = rng.integers(0, cfg.vocab, 300).tolist()
+        src_blocks = list(range(3, 3 + 19))          # the prefill side's block ids
+        dst_blocks = list(range(40, 40 + 19))[::-1]  # the decode side's own, different ids
+        if rank == 0:
+            first = be.forward(ForwardBatch([SeqChunk(prompt, 0, src_blocks + [30])]),
+                               observer=lambda layer: be.send_kv_layer(1, layer, src_blocks))
+            be.kv_hop_sync(20000)
+            tok = int(np.argmax(first[0]))
+            dist.broadcast_object_list([tok], src=0)
+            table = src_blocks + [30]
+        else:
+            for layer in range(cfg.layers):
+                be.recv_kv_layer(0, layer, dst_blocks)
+            be.kv_hop_sync(20000)
+            box = [None]
+            dist.broadcast_object_list(box, src=0)
+            tok = box[0]
+            table = dst_blocks + [33]
+        toks, rows = [], []
+        for s in range(6):
+            row = be.forward(ForwardBatch([SeqChunk([tok], 300 + s, table)]))[0]
+            rows.append(row)
+            tok = int(np.argmax(row))
+            toks.append(tok)
+        pages = [be.read_kv_layer(l, table[:19]) for l in range(cfg.layers)]
+        be.nccl_finalize()
+        q.put((rank, toks, np.stack(rows), [p.tobytes() for p in pages]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_kv_hop_over_nccl_equals_colocated_decode():
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_hop_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(2):
+        rank, toks, rows, pages = q.get(timeout=300)
+        got[rank] = (toks, rows, pages)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert got[0][0] == got[1][0]                    # same greedy tokens
+    assert np.array_equal(got[0][1], got[1][1])      # same logits, bit for bit
+    assert got[0][2] == got[1][2]                    # the pages that crossed NVLink are byte-identical
+
+
+def _replica_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+    from relay_b200.backend import make_cuda_backend
+    from relay_b200.parallel import gather_in_order, shard_range
+    from relay_b200.types import ForwardBatch, SeqChunk
+    from tests.workloads import c1_inputs
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.cuda.set_device(rank)
+        w, _, _ = c1_inputs()
+        be = make_cuda_backend(w, 64, 16, device=rank)
+        rng = np.random.Generator(np.random.PCG64(5))
+        prompts = [rng.integers(0, 256, int(n)).tolist() for n in rng.integers(5, 40, 7)]
+        b, e = shard_range(len(prompts), world, rank)
+        mine = []
+        for i in range(b, e):  # each rank serves its own sequences in its own pool, no collective
+            lg = be.forward(ForwardBatch([SeqChunk(prompts[i], 0, [2 * (i - b), 2 * (i - b) + 1, 20 + i])]))
+            mine.append(int(np.argmax(lg[0])))
+        q.put((rank, gather_in_order(mine, len(prompts))))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_sharded_replicas_equal_one_gpu():
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from relay_b200.backend import make_cuda_backend
+    from relay_b200.types import ForwardBatch, SeqChunk
+    from tests.workloads import c1_inputs
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_replica_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    w, _, _ = c1_inputs()
+    be = make_cuda_backend(w, 64, 16)
+    rng = np.random.Generator(np.random.PCG64(5))
+    prompts = [rng.integers(0, 256, int(n)).tolist() for n in rng.integers(5, 40, 7)]
+    want = [int(np.argmax(be.forward(ForwardBatch([SeqChunk(p, 0, [0, 1, 2])]))[0])) for p in prompts]
+    assert got[0][1] == want and got[1][1] == want
