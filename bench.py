@@ -412,6 +412,7 @@ def main() -> None:
     ap.add_argument("--cpu-seqs", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ops", action="store_true", help="skip the single-kernel measurements")
+    ap.add_argument("--ops-only", action="store_true", help="only the single-kernel measurements (prints their JSON)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else max(args.warmup, 1)
 
@@ -421,6 +422,11 @@ def main() -> None:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.abspath(__file__)] + sys.argv[1:]
         sys.exit(subprocess.call(cmd))
+
+    if args.ops_only:
+        peak, peak_tf, _ = measured_peaks()
+        print(json.dumps(op_suite(peak, peak_tf)), flush=True)
+        return
 
     if args.impl == "reference":
         if rank != 0:

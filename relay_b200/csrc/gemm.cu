@@ -1,16 +1,19 @@
 // The linear layers: y[T,N] = x[T,K] W[N,K]^T (+ beta*y), W fp16 or weight-only int8 with
 // one fp32 scale per output row, x fp16, y fp32.
 //
-//  * gemv_kernel (T <= 8) — replaces gemv_int8_kernel (engine/src/cuda_kernels.cuh:378-430)
-//    and the small-T case of cublasGemmEx (engine/src/cuda_backend.cu:724-730). Bound by
-//    weight bandwidth: every weight byte is read from HBM exactly once, straight into
-//    registers with 16-byte loads (no shared-memory round trip), converted int8 -> fp16 with
-//    byte permutes, and multiplied on the tensor cores with the 8 tokens on the N axis of
-//    m16n8k16, so the arithmetic never competes with the load stream. The k order inside an
-//    instruction is permuted (legal for a dot product) so that a thread's 16 contiguous
-//    weight bytes feed four instructions. Small N is split along K across CTAs; the last
-//    CTA of a row block to finish adds the partials in a fixed order, so results are
-//    deterministic.
+//  * gemv_kernel (T <= 8) — replaces gemv_int8_kernel (engine/src/cuda_kernels.cuh:378-430).
+//    Bound by weight bandwidth: every weight byte is read from HBM exactly once, straight
+//    into registers with 256-bit loads (the four lanes of a quad cover a whole 128-byte line
+//    of a row), int8 spliced under an fp16 exponent with two byte permutes (the constant
+//    bias this leaves, 1152 * sum of the activations, is removed once per output), and
+//    multiplied on the tensor cores with the 8 tokens on the N axis of m16n8k16, so the
+//    arithmetic never competes with the load stream. The k order inside an instruction is
+//    permuted (legal for a dot product) so that a lane's 32 contiguous weight bytes feed
+//    eight instructions. Small N is split along K across CTAs; the last CTA of a row block to
+//    finish adds the partials in a fixed order, so results are deterministic.
+//    fp16 weights with up to 8 tokens go to the tcgen05 kernel of umma_gemm.cu (a 16-token
+//    tile): TMA streams them faster than per-lane loads do. This kernel keeps an fp16
+//    instantiation for operands TMA cannot address.
 //  * gemm_kernel (T > 8) — replaces dequant_int8_kernel + cuBLAS (engine/src/cuda_kernels.cuh:432-436,
 //    engine/src/cuda_backend.cu:719-721) and cublasGemmEx for fp16 weights: weights on the M
 //    axis, tokens on N, int8 dequantised on its way into shared memory (the fp16 copy of the
@@ -39,13 +42,36 @@ __device__ __forceinline__ void cvt_s8x4_f16x4(uint32_t w, uint32_t& lo, uint32_
   hi = *reinterpret_cast<uint32_t*>(&hb);
 }
 
+// 32 bytes per lane in one instruction (sm_100 has 256-bit global loads), streaming cache
+// policy; lanes past the end of the k range get zeros.
+__device__ __forceinline__ void ld_global_256(uint32_t (&r)[8], const void* p, bool valid) {
+  if (valid) {
+    asm volatile("ld.global.cs.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "l"(p));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r[i] = 0u;
+  }
+}
+
+// Four signed bytes -> two half2 holding w + 1152 (exact, 1024..1279): the byte, with its
+// sign bit flipped, spliced under the exponent of 1024.0. Two instructions cheaper per call
+// than cvt_s8x4_f16x4; the caller removes the bias once per output (1152 * sum of x).
+__device__ __forceinline__ void cvt_s8x4_biased(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t u = w ^ 0x80808080u;
+  asm("prmt.b32 %0, %1, %2, 0x4140;" : "=r"(lo) : "r"(u), "r"(0x64646464u));
+  asm("prmt.b32 %0, %1, %2, 0x4342;" : "=r"(hi) : "r"(u), "r"(0x64646464u));
+}
+
 // ---- GEMV (T <= 8) -------------------------------------------------------------------------
 
 constexpr int kGemvWarps = 4;            // 16 output rows each
 constexpr int kGemvRows = kGemvWarps * 16;
-constexpr int kGemvMaxChunk = 2048;      // K values of x staged per CTA
+constexpr int kGemvMaxChunk = 1024;      // K values of x staged per CTA
 
 constexpr __host__ __device__ int gemv_x_pad(bool int8) { return int8 ? 8 : 32; }
+__host__ __device__ inline int round_up_dev(int a, int b) { return (a + b - 1) / b * b; }
 
 struct GemvPlan {
   int row_blocks, splits, chunk;
@@ -54,8 +80,11 @@ struct GemvPlan {
 GemvPlan plan_gemv(int N, int K) {
   GemvPlan p;
   p.row_blocks = div_up(N, kGemvRows);
-  const int want = std::max(div_up(2 * sm_count(), p.row_blocks), div_up(K, kGemvMaxChunk));
-  const int splits = std::max(1, std::min(want, K / 64));
+  // about four resident CTAs per SM in total; k ranges of at most kGemvMaxChunk, shorter
+  // (down to 256) only when the rows alone cannot occupy the GPU
+  const int slots = 4 * sm_count();
+  const int want = std::max(div_up(slots, p.row_blocks), div_up(K, kGemvMaxChunk));
+  const int splits = std::max(1, std::min(want, std::max(1, K / 256)));
   p.chunk = round_up(div_up(K, splits), 64);
   p.splits = div_up(K, p.chunk);
   return p;
@@ -64,111 +93,14 @@ GemvPlan plan_gemv(int N, int K) {
 // Scratch: [row_blocks] arrival counters (padded to 256 B), then partials [splits][N][8] floats.
 size_t gemv_counter_bytes(int N) { return static_cast<size_t>(round_up(div_up(N, kGemvRows) * 4, 256)); }
 
+// What every GEMV variant does with a warp's accumulator (m16n8: acc[0], acc[1] = row g,
+// tokens 2*t4 and 2*t4+1; acc[2], acc[3] = row g + 8): scale, add beta*y and store, or, when
+// K is split, park the partial sums and let the last CTA of the row block add them in order.
 template <bool INT8>
-__global__ void __launch_bounds__(kGemvWarps * 32)
-gemv_kernel(const void* __restrict__ wv, const float* __restrict__ scale, const __half* __restrict__ x,
-            float* __restrict__ y, int T, int K, int N, int ldw, int ldx, float beta, int chunk, int splits,
-            unsigned* __restrict__ counters, float* __restrict__ partials) {
-  // x[8][chunk] halves, each row padded (16 bytes for int8 weights, 64 for fp16) so that the
-  // token rows a quarter-warp reads with 16-byte loads fall into different bank groups.
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ unsigned s_last;
-  const int xs_stride = chunk + gemv_x_pad(INT8);  // halves
-  __half* xs = reinterpret_cast<__half*>(smem_raw);
-
-  const int rb = blockIdx.x, split = blockIdx.y;
-  const int kb0 = split * chunk, kb1 = min(K, kb0 + chunk);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
-
-  // stage x[:, kb0:kb1) (rows >= T are zero)
-  for (int idx = threadIdx.x; idx < 8 * (chunk / 8); idx += blockDim.x) {
-    const int t = idx / (chunk / 8), c = idx - t * (chunk / 8);
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (t < T && kb0 + c * 8 < kb1) v = *reinterpret_cast<const uint4*>(x + static_cast<long long>(t) * ldx + kb0 + c * 8);
-    *reinterpret_cast<uint4*>(xs + t * xs_stride + c * 8) = v;
-  }
-  __syncthreads();
-
-  const int row_a = min(rb * kGemvRows + warp * 16 + g, N - 1);      // clamped: extra rows are never stored
-  const int row_b = min(rb * kGemvRows + warp * 16 + g + 8, N - 1);
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-
-  if constexpr (INT8) {
-    const int8_t* w = static_cast<const int8_t*>(wv);
-    const int8_t* wa = w + static_cast<long long>(row_a) * ldw + 16 * t4;
-    const int8_t* wb = w + static_cast<long long>(row_b) * ldw + 16 * t4;
-    const __half* xg = xs + g * xs_stride + 16 * t4;
-    constexpr int U = 4;  // 64-wide k blocks in flight per thread
-    int k = kb0;
-    for (; k + 64 * U <= kb1; k += 64 * U) {
-      uint4 ra[U], rbv[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        ra[u] = __ldcs(reinterpret_cast<const uint4*>(wa + k + 64 * u));
-        rbv[u] = __ldcs(reinterpret_cast<const uint4*>(wb + k + 64 * u));
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const uint4 x0 = *reinterpret_cast<const uint4*>(xg + (k - kb0) + 64 * u);
-        const uint4 x1 = *reinterpret_cast<const uint4*>(xg + (k - kb0) + 64 * u + 8);
-        const uint32_t wa4[4] = {ra[u].x, ra[u].y, ra[u].z, ra[u].w}, wb4[4] = {rbv[u].x, rbv[u].y, rbv[u].z, rbv[u].w};
-        const uint32_t xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t a[4];
-          cvt_s8x4_f16x4(wa4[i], a[0], a[2]);
-          cvt_s8x4_f16x4(wb4[i], a[1], a[3]);
-          mma_f16(acc, a, xb[2 * i], xb[2 * i + 1]);
-        }
-      }
-    }
-    for (; k < kb1; k += 64) {
-      const uint4 ra = __ldcs(reinterpret_cast<const uint4*>(wa + k));
-      const uint4 rbv = __ldcs(reinterpret_cast<const uint4*>(wb + k));
-      const uint4 x0 = *reinterpret_cast<const uint4*>(xg + (k - kb0));
-      const uint4 x1 = *reinterpret_cast<const uint4*>(xg + (k - kb0) + 8);
-      const uint32_t wa4[4] = {ra.x, ra.y, ra.z, ra.w}, wb4[4] = {rbv.x, rbv.y, rbv.z, rbv.w};
-      const uint32_t xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t a[4];
-        cvt_s8x4_f16x4(wa4[i], a[0], a[2]);
-        cvt_s8x4_f16x4(wb4[i], a[1], a[3]);
-        mma_f16(acc, a, xb[2 * i], xb[2 * i + 1]);
-      }
-    }
-  } else {
-    const __half* w = static_cast<const __half*>(wv);
-    const __half* wa = w + static_cast<long long>(row_a) * ldw + 8 * t4;
-    const __half* wb = w + static_cast<long long>(row_b) * ldw + 8 * t4;
-    const __half* xg = xs + g * xs_stride + 8 * t4;
-    constexpr int U = 4;  // 32-wide k blocks in flight per thread
-    int k = kb0;
-    for (; k + 32 * U <= kb1; k += 32 * U) {
-      uint4 ra[U], rbv[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        ra[u] = __ldcs(reinterpret_cast<const uint4*>(wa + k + 32 * u));
-        rbv[u] = __ldcs(reinterpret_cast<const uint4*>(wb + k + 32 * u));
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const uint4 xv = *reinterpret_cast<const uint4*>(xg + (k - kb0) + 32 * u);
-        const uint32_t a0[4] = {ra[u].x, rbv[u].x, ra[u].y, rbv[u].y}, a1[4] = {ra[u].z, rbv[u].z, ra[u].w, rbv[u].w};
-        mma_f16(acc, a0, xv.x, xv.y);
-        mma_f16(acc, a1, xv.z, xv.w);
-      }
-    }
-    for (; k < kb1; k += 32) {
-      const uint4 ra = __ldcs(reinterpret_cast<const uint4*>(wa + k));
-      const uint4 rbv = __ldcs(reinterpret_cast<const uint4*>(wb + k));
-      const uint4 xv = *reinterpret_cast<const uint4*>(xg + (k - kb0));
-      const uint32_t a0[4] = {ra.x, rbv.x, ra.y, rbv.y}, a1[4] = {ra.z, rbv.z, ra.w, rbv.w};
-      mma_f16(acc, a0, xv.x, xv.y);
-      mma_f16(acc, a1, xv.z, xv.w);
-    }
-  }
-
+__device__ __forceinline__ void gemv_finish(const float (&acc)[4], int rb, int split, int splits, int warp, int g, int t4,
+                                            int T, int N, const float* __restrict__ scale, float* __restrict__ y,
+                                            float beta, unsigned* __restrict__ counters, float* __restrict__ partials,
+                                            unsigned* s_last) {
   // acc[0], acc[1]: row g, tokens 2*t4, 2*t4+1; acc[2], acc[3]: row g + 8.
   const int n_a = rb * kGemvRows + warp * 16 + g, n_b = n_a + 8;
   const int tok = 2 * t4;
@@ -198,11 +130,11 @@ gemv_kernel(const void* __restrict__ wv, const float* __restrict__ scale, const 
   __syncthreads();
   if (threadIdx.x == 0) {
     const unsigned seen = atomicAdd(&counters[rb], 1u);
-    s_last = seen == static_cast<unsigned>(splits - 1);
-    if (s_last) counters[rb] = 0;  // ready for the next launch
+    *s_last = seen == static_cast<unsigned>(splits - 1);
+    if (*s_last) counters[rb] = 0;  // ready for the next launch
   }
   __syncthreads();
-  if (!s_last) return;
+  if (!*s_last) return;
   __threadfence();
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
   for (int s = 0; s < splits; ++s) {
@@ -220,6 +152,130 @@ gemv_kernel(const void* __restrict__ wv, const float* __restrict__ scale, const 
   }
   finish(n_a, s0, s1);
   finish(n_b, s2, s3);
+}
+
+template <bool INT8>
+__global__ void __launch_bounds__(kGemvWarps * 32)
+gemv_kernel(const void* __restrict__ wv, const float* __restrict__ scale, const __half* __restrict__ x,
+            float* __restrict__ y, int T, int K, int N, int ldw, int ldx, float beta, int chunk, int splits,
+            unsigned* __restrict__ counters, float* __restrict__ partials) {
+  // x[8][chunk] halves, each row padded (16 bytes for int8 weights, 64 for fp16) so that the
+  // token rows a quarter-warp reads with 16-byte loads fall into different bank groups.
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ unsigned s_last;
+  __shared__ float s_xsum[8];  // int8 only: sum of each token's activations over this CTA's k range
+  const int xs_stride = round_up_dev(chunk, 128) + gemv_x_pad(INT8);  // halves
+  __half* xs = reinterpret_cast<__half*>(smem_raw);
+
+  const int rb = blockIdx.x, split = blockIdx.y;
+  const int kb0 = split * chunk, kb1 = min(K, kb0 + chunk);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  constexpr int KB = INT8 ? 128 : 64;  // k values per block: each lane of a quad loads 32 bytes, a full 128-byte line per row
+  constexpr int U = 4;                 // 32-byte loads in flight per thread and row
+
+  const int row_a = min(rb * kGemvRows + warp * 16 + g, N - 1);      // clamped: extra rows are never stored
+  const int row_b = min(rb * kGemvRows + warp * 16 + g + 8, N - 1);
+  const size_t esz = INT8 ? 1 : 2;
+  const unsigned char* wa = static_cast<const unsigned char*>(wv) + (static_cast<size_t>(row_a) * ldw + kb0) * esz + 32 * t4;
+  const unsigned char* wb = static_cast<const unsigned char*>(wv) + (static_cast<size_t>(row_b) * ldw + kb0) * esz + 32 * t4;
+  const int span = (kb1 - kb0) * static_cast<int>(esz);  // bytes of one row this CTA covers (a multiple of 64)
+  const int nblk = (span + 127) / 128;
+
+  // Start the weight stream before anything else: the first U blocks are in flight while the
+  // activations are staged.
+  uint32_t ra[U][8], rbv[U][8];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    if (u < nblk) {
+      ld_global_256(ra[u], wa + u * 128, u * 128 + 32 * t4 < span);
+      ld_global_256(rbv[u], wb + u * 128, u * 128 + 32 * t4 < span);
+    }
+  }
+
+  // stage x[:, kb0:kb1) (rows >= T and the tail of the last block are zero)
+  const int xcols = round_up_dev(kb1 - kb0, 128);
+  float xsum = 0.f;  // this thread's share of its token's sum (idx -> token is fixed per warp pass below)
+  if (threadIdx.x < 8) s_xsum[threadIdx.x] = 0.f;
+  __syncthreads();
+  for (int t = warp; t < 8; t += kGemvWarps) {  // a warp stages whole token rows, so it can sum them too
+    xsum = 0.f;
+    for (int c = lane; c < xcols / 8; c += 32) {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (t < T && kb0 + c * 8 < kb1) v = *reinterpret_cast<const uint4*>(x + static_cast<long long>(t) * ldx + kb0 + c * 8);
+      *reinterpret_cast<uint4*>(xs + t * xs_stride + c * 8) = v;
+      if constexpr (INT8) {
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __half22float2(h[i]);
+          xsum += f.x + f.y;
+        }
+      }
+    }
+    if constexpr (INT8) {
+      xsum = warp_sum(xsum);
+      if (lane == 0) s_xsum[t] = xsum;
+    }
+  }
+  __syncthreads();
+
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const __half* xg = xs + g * xs_stride + (INT8 ? 32 : 16) * t4;
+  for (int b0 = 0; b0 < nblk; b0 += U) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int b = b0 + u;
+      if (b < nblk) {
+        uint32_t wra[8], wrb[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          wra[i] = ra[u][i];
+          wrb[i] = rbv[u][i];
+        }
+        if (b + U < nblk) {  // refill this slot at once: U loads stay in flight
+          ld_global_256(ra[u], wa + (b + U) * 128, (b + U) * 128 + 32 * t4 < span);
+          ld_global_256(rbv[u], wb + (b + U) * 128, (b + U) * 128 + 32 * t4 < span);
+        }
+        if constexpr (INT8) {
+          uint32_t xb[16];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xg + b * KB + 8 * c);
+            xb[4 * c] = xv.x;
+            xb[4 * c + 1] = xv.y;
+            xb[4 * c + 2] = xv.z;
+            xb[4 * c + 3] = xv.w;
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {  // four consecutive k per instruction and lane
+            uint32_t a[4];
+            cvt_s8x4_biased(wra[i], a[0], a[2]);
+            cvt_s8x4_biased(wrb[i], a[1], a[3]);
+            mma_f16(acc, a, xb[2 * i], xb[2 * i + 1]);
+          }
+        } else {
+          const uint4 x0 = *reinterpret_cast<const uint4*>(xg + b * KB);
+          const uint4 x1 = *reinterpret_cast<const uint4*>(xg + b * KB + 8);
+          const uint32_t xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t a[4] = {wra[2 * i], wrb[2 * i], wra[2 * i + 1], wrb[2 * i + 1]};
+            mma_f16(acc, a, xb[2 * i], xb[2 * i + 1]);
+          }
+        }
+      }
+    }
+  }
+  if constexpr (INT8) {
+    // The multiplicand fed to the tensor core was w + 1152 (see cvt_s8x4_biased): take the
+    // surplus 1152 * sum_k x[t][k] back out, in fp32, per token.
+    const float c0 = 1152.0f * s_xsum[2 * t4], c1 = 1152.0f * s_xsum[2 * t4 + 1];
+    acc[0] -= c0;
+    acc[1] -= c1;
+    acc[2] -= c0;
+    acc[3] -= c1;
+  }
+  gemv_finish<INT8>(acc, rb, split, splits, warp, g, t4, T, N, scale, y, beta, counters, partials, &s_last);
 }
 
 // ---- GEMM (T > 8) --------------------------------------------------------------------------
@@ -354,8 +410,16 @@ gemm_kernel(const void* __restrict__ wv, const float* __restrict__ scale, const 
 }  // namespace
 
 size_t gemv_scratch_bytes(int N, int K) {
-  const GemvPlan p = plan_gemv(N, K);
-  return gemv_counter_bytes(N) + (p.splits > 1 ? static_cast<size_t>(p.splits) * N * 8 * sizeof(float) : 0);
+  const int splits = plan_gemv(N, K).splits;
+  return gemv_counter_bytes(N) + (splits > 1 ? static_cast<size_t>(splits) * N * 8 * sizeof(float) : 0);
+}
+
+static bool gemm_forced_legacy() {
+  static const bool v = [] {
+    const char* e = std::getenv("RB200_GEMM");
+    return e && std::string(e) == "mma_sync";
+  }();
+  return v;
 }
 
 static void check_linear(const WeightView& W, int ldx, int T) {
@@ -371,12 +435,17 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
   check_linear(W, ldx, T);
   RB_REQUIRE(T <= 8, "gemv: at most 8 tokens");
   if (T == 0) return;
+  // fp16 weights stream faster through TMA (whole 128-byte row pieces) than through per-lane
+  // 16-byte loads, so the few-token case uses the tcgen05 kernel with a 16-token tile.
+  if (W.f16 && !gemm_forced_legacy() && umma_gemm_usable(W, x, ldx)) return launch_umma_gemm(W, x, ldx, y, T, beta, st);
+  unsigned* counters = static_cast<unsigned*>(scratch);
+  float* partials = scratch ? reinterpret_cast<float*>(static_cast<char*>(scratch) + gemv_counter_bytes(W.N)) : nullptr;
   const GemvPlan p = plan_gemv(W.N, W.K);
   RB_REQUIRE(p.splits == 1 || (scratch != nullptr && scratch_bytes >= gemv_scratch_bytes(W.N, W.K)),
              "gemv: scratch too small");
-  unsigned* counters = static_cast<unsigned*>(scratch);
-  float* partials = scratch ? reinterpret_cast<float*>(static_cast<char*>(scratch) + gemv_counter_bytes(W.N)) : nullptr;
-  const size_t smem = static_cast<size_t>(8) * (p.chunk + gemv_x_pad(W.i8 != nullptr)) * sizeof(__half);
+  const size_t smem = static_cast<size_t>(8) * (round_up(p.chunk, 128) + gemv_x_pad(W.i8 != nullptr)) * sizeof(__half);
+  RB_REQUIRE((static_cast<size_t>(W.ld) * (W.i8 ? 1 : 2)) % 32 == 0 && (reinterpret_cast<uintptr_t>(W.i8 ? static_cast<const void*>(W.i8) : static_cast<const void*>(W.f16)) & 31) == 0,
+             "gemv: weight rows must be 32-byte aligned");
   dim3 grid(p.row_blocks, p.splits);
   count_launch();
   if (W.i8)
@@ -390,11 +459,7 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
 void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st) {
   check_linear(W, ldx, T);
   if (T == 0) return;
-  static const bool force_legacy = [] {
-    const char* e = std::getenv("RB200_GEMM");
-    return e && std::string(e) == "mma_sync";
-  }();
-  if (!force_legacy && umma_gemm_usable(W, x, ldx)) return launch_umma_gemm(W, x, ldx, y, T, beta, st);
+  if (!gemm_forced_legacy() && umma_gemm_usable(W, x, ldx)) return launch_umma_gemm(W, x, ldx, y, T, beta, st);
   launch_gemm_mma_sync(W, x, ldx, y, T, beta, st);
 }
 

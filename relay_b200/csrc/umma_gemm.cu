@@ -42,7 +42,8 @@ namespace {
 
 constexpr int kTileM = 128;
 constexpr int kBlockK = 64;        // halves per k block: one 128-byte swizzle atom
-constexpr int kUmmaThreads = 192;  // producer, MMA, 4 epilogue warps
+constexpr int kUmmaThreads = 192;      // producer, MMA, 4 epilogue warps
+constexpr int kUmmaThreadsInt8 = 320;  // + 4 more warps that only widen int8 tiles
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a pipeline wait gives up after 2 s
 
 // ---- PTX wrappers ----------------------------------------------------------------------
@@ -177,7 +178,7 @@ __device__ __forceinline__ void cvt_s8x4(uint32_t w, uint32_t& lo, uint32_t& hi)
 
 template <int BN, bool INT8>
 struct UmmaSmem {
-  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 5 : 6);
+  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 32 ? 6 : 8));
   static constexpr int kABytes = kTileM * kBlockK * 2;            // fp16 operand tile
   static constexpr int kBBytes = BN * kBlockK * 2;
   static constexpr int kRawBytes = INT8 ? kTileM * kBlockK : 0;   // int8 staging tile
@@ -187,7 +188,7 @@ struct UmmaSmem {
 };
 
 template <int BN, bool INT8>
-__global__ void __launch_bounds__(kUmmaThreads, 1)
+__global__ void __launch_bounds__(INT8 ? kUmmaThreadsInt8 : kUmmaThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  const float* __restrict__ scale, float* __restrict__ y, int T, int N, int K, float beta,
                  int* __restrict__ status) {
@@ -219,7 +220,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     for (int s = 0; s < NS; ++s) {
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
-      mbar_init(conv_bar + 8 * s, 128);
+      mbar_init(conv_bar + 8 * s, 8);
     }
     mbar_init(accum_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -271,38 +272,46 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     }
   } else {
     // ---- int8 widening (main loop), then the epilogue ----
-    const int et = threadIdx.x - 64;  // 0..127: one weight row of the tile each
+    const int et = threadIdx.x - 64;  // 0..127 (fp16) or 0..255 (int8: warps 6-9 only widen)
     if constexpr (INT8) {
       for (int kb = 0; kb < nk && ok; ++kb) {
         const int s = kb % NS;
         ok = mbar_wait(full_bar + 8 * s, (kb / NS) & 1);
         if (!ok) break;
-        const uint4* raw = reinterpret_cast<const uint4*>(gen_base + (sRaw + s * S::kRawBytes - base)) + et * 4;
+        const uint4* raw = reinterpret_cast<const uint4*>(gen_base + (sRaw + s * S::kRawBytes - base));
         uint4* dst = reinterpret_cast<uint4*>(gen_base + (sA + s * S::kABytes - base));
+        // 512 raw 16-byte chunks (128 rows x 4) over 256 threads: consecutive threads take consecutive chunks, so
+        // both the reads and the swizzled writes are free of bank conflicts.
+        uint4 r[2];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {  // 16 int8 -> two 16-byte fp16 chunks
-          const uint4 r = raw[c];
+        for (int i = 0; i < 2; ++i) r[i] = raw[et + 256 * i];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {  // 16 int8 -> two 16-byte fp16 chunks
+          const int idx = et + 256 * i, row = idx >> 2, c = idx & 3;
           uint4 o0, o1;
-          cvt_s8x4(r.x, o0.x, o0.y);
-          cvt_s8x4(r.y, o0.z, o0.w);
-          cvt_s8x4(r.z, o1.x, o1.y);
-          cvt_s8x4(r.w, o1.z, o1.w);
-          dst[et * 8 + ((2 * c) ^ (et & 7))] = o0;
-          dst[et * 8 + ((2 * c + 1) ^ (et & 7))] = o1;
+          cvt_s8x4(r[i].x, o0.x, o0.y);
+          cvt_s8x4(r[i].y, o0.z, o0.w);
+          cvt_s8x4(r[i].z, o1.x, o1.y);
+          cvt_s8x4(r[i].w, o1.z, o1.w);
+          dst[row * 8 + ((2 * c) ^ (row & 7))] = o0;
+          dst[row * 8 + ((2 * c + 1) ^ (row & 7))] = o1;
         }
         fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-        mbar_arrive(conv_bar + 8 * s);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(conv_bar + 8 * s);  // one arrival per warp
       }
       if (!ok) atomicExch(status, 3);
     }
-    bool done = mbar_wait(accum_bar, 0);
+    bool done = warp < 6 ? mbar_wait(accum_bar, 0) : true;  // warps 6-9 (int8 only) take no part in the epilogue
     if (!done) atomicExch(status, 4);
     tc_fence_after();
     const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
     const int row = quarter * 32 + lane;
     const int n = m0 + row;
     const float sc = (INT8 && n < N) ? scale[n] : 1.0f;
-    if (splits == 1) {
+    if (warp >= 6) {
+      // nothing: only widening warps
+    } else if (splits == 1) {
       if (done && ok) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -342,7 +351,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   }
   if (splits > 1) {
     cluster_sync_all();  // every member's partial tile is in its shared memory
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
       const int row = (warp & 3) * 32 + lane;
       const int n = m0 + row;
       const float sc = (INT8 && n < N) ? scale[n] : 1.0f;
@@ -464,7 +473,7 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
   if (forced > 0) splits = std::min({forced, 8, std::max(1, nk)});
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(div_up(W.N, kTileM), div_up(T, BN), splits);
-  cfg.blockDim = dim3(kUmmaThreads);
+  cfg.blockDim = dim3(INT8 ? kUmmaThreadsInt8 : kUmmaThreads);
   cfg.dynamicSmemBytes = S::kTotal;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -483,7 +492,8 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
 
 template <bool INT8>
 void launch_umma_i(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st) {
-  if (T <= 32) launch_umma_t<32, INT8>(W, x, ldx, y, T, beta, st);
+  if (T <= 16) launch_umma_t<16, INT8>(W, x, ldx, y, T, beta, st);
+  else if (T <= 32) launch_umma_t<32, INT8>(W, x, ldx, y, T, beta, st);
   else if (T <= 64) launch_umma_t<64, INT8>(W, x, ldx, y, T, beta, st);
   else if (T <= 128 || (T > 256 && T <= 384 && false)) launch_umma_t<128, INT8>(W, x, ldx, y, T, beta, st);
   else launch_umma_t<256, INT8>(W, x, ldx, y, T, beta, st);
