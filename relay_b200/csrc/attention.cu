@@ -711,6 +711,7 @@ void launch_decode_attention(const AttnShape& s, const float* q, const TokenMeta
 void launch_prefill_attention(const AttnShape& s, const float* q, const TokenMeta& m, const int2* tiles, int n_tiles,
                               const __half* kc, const __half* vc, __half* out, cudaStream_t st) {
   if (n_tiles == 0) return;
+  if (umma_prefill_usable(s, q, kc, vc, out)) return launch_umma_prefill(s, q, m, tiles, n_tiles, kc, vc, out, st);
   switch (s.D) {
     case 16: launch_prefill_d<16>(s, q, m, tiles, n_tiles, kc, vc, out, st); break;
     case 32: launch_prefill_d<32>(s, q, m, tiles, n_tiles, kc, vc, out, st); break;

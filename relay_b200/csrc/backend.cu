@@ -404,9 +404,9 @@ int Backend::forward(int n_seqs, const int32_t* tokens, const int32_t* chunk_len
   RB_CUDA(cudaGetLastError());
   RB_CUDA(cudaStreamSynchronize(stream_));
   end_profile(prof);
-  if (T > 8 || R > 8) {  // the tensor-core GEMM ran: make sure none of its bounded waits gave up
+  if (T > 8 || R > 8 || n_tiles > 0) {  // a tcgen05 kernel ran: make sure none of its bounded waits gave up
     const int code = umma_gemm_status();
-    if (code != 0) fail(RB200_ERR_RUNTIME, "tensor-core GEMM pipeline wait timed out (code " + std::to_string(code) + ")");
+    if (code != 0) fail(RB200_ERR_RUNTIME, "a tcgen05 pipeline wait timed out (code " + std::to_string(code) + ")");
   }
   return R;
 }

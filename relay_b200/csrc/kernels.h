@@ -76,6 +76,14 @@ void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T,
 // tcgen05 kernel of umma_gemm.cu and falls back to this one.
 void launch_gemm_mma_sync(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st);
 
+// ---- umma_prefill.cu ----
+// The tcgen05 flash prefill kernel covers head sizes 64 and 128 with an even number of query
+// heads per KV head and block sizes that are multiples of 16; launch_prefill_attention
+// prefers it and keeps prefill_flash_kernel (mma.sync) for everything else.
+bool umma_prefill_usable(const AttnShape& s, const float* q, const __half* kc, const __half* vc, const __half* out);
+void launch_umma_prefill(const AttnShape& s, const float* q, const TokenMeta& m, const int2* tiles, int n_tiles,
+                         const __half* kc, const __half* vc, __half* out, cudaStream_t st);
+
 // ---- umma_gemm.cu ----
 bool umma_gemm_usable(const WeightView& W, const __half* x, int ldx);
 void launch_umma_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st);

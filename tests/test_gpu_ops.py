@@ -181,6 +181,7 @@ def run_attention(ops, case, kind):
     else:
         ops.reference_attention(shape, q, meta, T, kp, vp, out)
     torch.cuda.synchronize()
+    assert ops.gemm_status() == 0  # no bounded pipeline wait of a tcgen05 kernel gave up
     return out.cpu().numpy().astype(np.float32)
 
 
@@ -228,6 +229,8 @@ PREFILL_CASES = [
     (32, 8, 4, 16, [300, 129], [192, 129]),
     (64, 32, 4, 16, [512, 1024], [512, 512]),                     # the prefill workload's shape, chunks 1 and 2
     (128, 8, 2, 16, [700, 90], [300, 90]),
+    (128, 32, 8, 16, [1100], [640]),                              # Llama-3-8B head layout
+    (64, 8, 2, 32, [333, 64], [333, 1]),                          # block size 32: two 16-key pages per block
     (64, 4, 4, 1, [70], [70]),
     (64, 6, 2, 8, [150], [77]),
 ]
