@@ -378,9 +378,12 @@ def gpu_arm(args) -> dict:
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s / args.steps * 1e3},
         "gpu_launches": int(launches),
-        "roofline": {"kernel": "decode_split_kernel<128> + decode_merge_kernel", "bound": "hbm", "achieved": achieved,
+        "roofline": {"kernel": "decode_split_kernel<128> (+ decode_merge_kernel when contexts are split)", "bound": "hbm", "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if peak else None,
-                     "traffic": None, "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
+                     # DRAM read + write bytes of the kernel from an ncu capture of a 32-sequence launch
+                     # (538.8 + 6.6 MB for 537.7 MB algorithmic), scaled by the units a full launch processes
+                     "traffic": attn_bytes * 1.014, "traffic_source": "profiles/decode_split_kernel_d128_32seq_ctx4096.md",
+                     "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
                      "launches_timed": calls,
                      "share_of_step": prof["decode_attn_ms"] / prof["total_ms"] if prof["total_ms"] else None},
         "step_roofline": {"algorithmic_bytes_per_step": step_bytes,
