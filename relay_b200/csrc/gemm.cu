@@ -438,6 +438,10 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
   // fp16 weights stream faster through TMA (whole 128-byte row pieces) than through per-lane
   // 16-byte loads, so the few-token case uses the tcgen05 kernel with a 16-token tile.
   if (W.f16 && !gemm_forced_legacy() && umma_gemm_usable(W, x, ldx)) return launch_umma_gemm(W, x, ldx, y, T, beta, st);
+  // int8: the same kernel (tile widened into TMEM) wins once the matrix is large enough to
+  // amortise its longer prologue; measured crossover near 32 MB
+  if (W.i8 && static_cast<long long>(W.N) * W.K >= (32LL << 20) && !gemm_forced_legacy() && umma_gemm_usable(W, x, ldx))
+    return launch_umma_gemm(W, x, ldx, y, T, beta, st);
   unsigned* counters = static_cast<unsigned*>(scratch);
   float* partials = scratch ? reinterpret_cast<float*>(static_cast<char*>(scratch) + gemv_counter_bytes(W.N)) : nullptr;
   const GemvPlan p = plan_gemv(W.N, W.K);

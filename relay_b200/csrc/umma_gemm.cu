@@ -62,12 +62,20 @@ __device__ __forceinline__ void cvt_s8x4(uint32_t w, uint32_t& lo, uint32_t& hi)
 
 template <int BN, bool INT8>
 struct UmmaSmem {
-  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 32 ? 6 : 8));
-  static constexpr int kABytes = kTileM * kBlockK * 2;            // fp16 operand tile
+  static constexpr int kAccCols = BN < 32 ? 32 : BN;               // TMEM columns of the accumulator
+  static constexpr int kABytes = INT8 ? 0 : kTileM * kBlockK * 2;  // fp16 operand tile (fp16 weights only)
   static constexpr int kBBytes = BN * kBlockK * 2;
-  static constexpr int kRawBytes = INT8 ? kTileM * kBlockK : 0;   // int8 staging tile
+  static constexpr int kRawBytes = INT8 ? kTileM * kBlockK : 0;    // int8 tile as TMA lands it
   static constexpr int kStageBytes = kABytes + kBBytes + kRawBytes;
-  static constexpr int kBarBytes = 256;
+  // Shared-memory stages: what is in flight from HBM. int8 stages are half the size of fp16
+  // ones, so there are about twice as many (up to 16).
+  static constexpr int kStages = INT8 ? (180 * 1024 / kStageBytes > 16 ? 16 : 180 * 1024 / kStageBytes)
+                                      : (BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 32 ? 6 : 8)));
+  // int8: the widened A tile of a k block lives in TMEM (32 columns: 64 halves per row) in a
+  // ring of its own, as deep as the allocation (a power of two) allows next to the accumulator.
+  static constexpr int kTmemCols = INT8 ? (BN >= 256 ? 512 : 256) : kAccCols;
+  static constexpr int kAStages = INT8 ? (kTmemCols - kAccCols) / 32 : 0;
+  static constexpr int kBarBytes = 1024;
   static constexpr size_t kTotal = static_cast<size_t>(kStages) * kStageBytes + kBarBytes + 1024;  // + alignment slack
 };
 
@@ -78,7 +86,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                  int* __restrict__ status) {
   using S = UmmaSmem<BN, INT8>;
   constexpr int NS = S::kStages;
-  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;  // power of two >= 32
+  constexpr uint32_t kTmemCols = S::kTmemCols;
+  constexpr uint32_t kACol0 = S::kAccCols;  // int8: TMEM column of A stage 0 (32 columns per stage)
   extern __shared__ unsigned char smem_dyn[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -86,11 +95,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const uint32_t sB = sA + NS * S::kABytes;
   const uint32_t sRaw = sB + NS * S::kBBytes;
   const uint32_t bars = sRaw + NS * S::kRawBytes;
+  constexpr int NA = S::kAStages > 0 ? S::kAStages : 1;
   const uint32_t full_bar = bars;              // NS x 8 bytes: TMA landed
-  const uint32_t empty_bar = bars + 8 * NS;    // NS x 8: MMA finished reading the stage
-  const uint32_t conv_bar = bars + 16 * NS;    // NS x 8: int8 tile widened (INT8 only)
-  const uint32_t accum_bar = bars + 24 * NS;   // accumulator complete
-  const uint32_t tmem_slot = bars + 24 * NS + 8;
+  const uint32_t empty_bar = bars + 8 * NS;    // NS x 8: MMA finished reading the stage's shared memory
+  const uint32_t raw_free = bars + 16 * NS;    // NS x 8: int8 only, the raw tile has been widened
+  const uint32_t conv_bar = bars + 24 * NS;    // NA x 8: int8 only, A stage written to TMEM
+  const uint32_t a_free = conv_bar + 8 * NA;   // NA x 8: int8 only, MMA finished reading the A stage
+  const uint32_t accum_bar = a_free + 8 * NA;  // accumulator complete
+  const uint32_t tmem_slot = accum_bar + 8;
   unsigned char* gen_base = smem_dyn + (base - smem_u32(smem_dyn));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -104,7 +116,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     for (int s = 0; s < NS; ++s) {
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
-      mbar_init(conv_bar + 8 * s, 8);
+      mbar_init(raw_free + 8 * s, 4);
+    }
+    for (int a = 0; a < NA; ++a) {
+      mbar_init(conv_bar + 8 * a, 4);
+      mbar_init(a_free + 8 * a, 1);
     }
     mbar_init(accum_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -126,6 +142,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       for (int kb = 0; kb < nk && ok; ++kb) {
         const int s = kb % NS;
         ok = mbar_wait(empty_bar + 8 * s, ((kb / NS) & 1) ^ 1);
+        if (INT8 && ok) ok = mbar_wait(raw_free + 8 * s, ((kb / NS) & 1) ^ 1);
         if (!ok) break;
         mbar_expect_tx(full_bar + 8 * s, (INT8 ? S::kRawBytes : S::kABytes) + S::kBBytes);
         const int kx = (kb_begin + kb) * kBlockK;
@@ -141,14 +158,22 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       constexpr uint32_t idesc = umma_idesc(kTileM, BN);
       for (int kb = 0; kb < nk && ok; ++kb) {
         const int s = kb % NS;
-        ok = mbar_wait((INT8 ? conv_bar : full_bar) + 8 * s, (kb / NS) & 1);
+        ok = mbar_wait(full_bar + 8 * s, (kb / NS) & 1);
+        if (INT8 && ok) ok = mbar_wait(conv_bar + 8 * (kb % NA), (kb / NA) & 1);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t da = smem_desc_sw128(sA + s * S::kABytes);
         const uint64_t db = smem_desc_sw128(sB + s * S::kBBytes);
+        if constexpr (INT8) {
+          const uint32_t ta = tmem_base + kACol0 + (kb % NA) * 32;  // 16 halves = 8 columns per step
 #pragma unroll
-        for (int k4 = 0; k4 < kBlockK / 16; ++k4)  // 16 halves = 32 bytes = 2 descriptor units per step
-          umma_f16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+          for (int k4 = 0; k4 < kBlockK / 16; ++k4) umma_f16_ta(tmem_base, ta + 8 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+          umma_commit(a_free + 8 * (kb % NA));
+        } else {
+          const uint64_t da = smem_desc_sw128(sA + s * S::kABytes);
+#pragma unroll
+          for (int k4 = 0; k4 < kBlockK / 16; ++k4)  // 16 halves = 32 bytes = 2 descriptor units per step
+            umma_f16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+        }
         umma_commit(empty_bar + 8 * s);  // arrives once the MMAs above have read the stage
       }
       umma_commit(accum_bar);
@@ -156,33 +181,39 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     }
   } else {
     // ---- int8 widening (main loop), then the epilogue ----
-    const int et = threadIdx.x - 64;  // 0..127 (fp16) or 0..255 (int8: warps 6-9 only widen)
     if constexpr (INT8) {
-      for (int kb = 0; kb < nk && ok; ++kb) {
-        const int s = kb % NS;
+      // Two groups of four warps take alternate k blocks, so two blocks are widened at a time.
+      // Thread = one weight row (the TMEM lane it may write): 64 int8 from the 64-byte-swizzled
+      // raw tile -> 64 fp16 -> the 32 TMEM columns of an A stage.
+      const int crow = (warp & 3) * 32 + lane, group = (warp - 2) >> 2;
+      const int sw = (crow >> 1) & 3;
+      const uint32_t tcol = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + kACol0;
+      for (int kb = group; kb < nk && ok; kb += 2) {
+        const int s = kb % NS, a = kb % NA;
         ok = mbar_wait(full_bar + 8 * s, (kb / NS) & 1);
         if (!ok) break;
-        const uint4* raw = reinterpret_cast<const uint4*>(gen_base + (sRaw + s * S::kRawBytes - base));
-        uint4* dst = reinterpret_cast<uint4*>(gen_base + (sA + s * S::kABytes - base));
-        // 512 raw 16-byte chunks (128 rows x 4) over 256 threads: consecutive threads take consecutive chunks, so
-        // both the reads and the swizzled writes are free of bank conflicts.
-        uint4 r[2];
+        const uint4* raw = reinterpret_cast<const uint4*>(gen_base + (sRaw + s * S::kRawBytes - base)) + crow * 4;
+        uint4 r[4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) r[i] = raw[et + 256 * i];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {  // 16 int8 -> two 16-byte fp16 chunks
-          const int idx = et + 256 * i, row = idx >> 2, c = idx & 3;
-          uint4 o0, o1;
-          cvt_s8x4(r[i].x, o0.x, o0.y);
-          cvt_s8x4(r[i].y, o0.z, o0.w);
-          cvt_s8x4(r[i].z, o1.x, o1.y);
-          cvt_s8x4(r[i].w, o1.z, o1.w);
-          dst[row * 8 + ((2 * c) ^ (row & 7))] = o0;
-          dst[row * 8 + ((2 * c + 1) ^ (row & 7))] = o1;
-        }
-        fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+        for (int c = 0; c < 4; ++c) r[c] = raw[c ^ sw];
         __syncwarp();
-        if (lane == 0) mbar_arrive(conv_bar + 8 * s);  // one arrival per warp
+        if (lane == 0) mbar_arrive(raw_free + 8 * s);  // the raw tile is in registers: its stage may be refilled
+        uint32_t h[32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          cvt_s8x4(r[c].x, h[8 * c], h[8 * c + 1]);
+          cvt_s8x4(r[c].y, h[8 * c + 2], h[8 * c + 3]);
+          cvt_s8x4(r[c].z, h[8 * c + 4], h[8 * c + 5]);
+          cvt_s8x4(r[c].w, h[8 * c + 6], h[8 * c + 7]);
+        }
+        ok = mbar_wait(a_free + 8 * a, ((kb / NA) & 1) ^ 1);  // the MMA that last read this A stage is done
+        if (!ok) break;
+        tc_fence_after();
+        tmem_st32(tcol + a * 32, h);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(conv_bar + 8 * a);  // one arrival per warp
       }
       if (!ok) atomicExch(status, 3);
     }
@@ -308,7 +339,7 @@ EncodeFn encode_fn() {
 
 // A 2-D tensor map over a row-major [rows][ld] matrix of 1- or 2-byte elements, box = [box_rows][box_cols].
 CUtensorMap tc::make_map(const void* ptr, int elem_bytes, long long rows, long long cols, long long ld, int box_rows,
-                     int box_cols, bool swizzle128) {
+                         int box_cols, bool swizzle128, bool swizzle64) {
   CUtensorMap m;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
@@ -316,7 +347,7 @@ CUtensorMap tc::make_map(const void* ptr, int elem_bytes, long long rows, long l
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = encode_fn()(&m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
                                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                 swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                 swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : (swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) fail(RB200_ERR_RUNTIME, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
   return m;
@@ -347,7 +378,7 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
     configured = true;
   }
-  const CUtensorMap mw = INT8 ? make_map(W.i8, 1, W.N, W.K, W.ld, kTileM, kBlockK, false)
+  const CUtensorMap mw = INT8 ? make_map(W.i8, 1, W.N, W.K, W.ld, kTileM, kBlockK, false, true)
                               : make_map(W.f16, 2, W.N, W.K, W.ld, kTileM, kBlockK, true);
   const CUtensorMap mx = make_map(x, 2, T, W.K, ldx, BN, kBlockK, true);
   // Split K across a cluster when the tiles alone would leave SMs idle.
