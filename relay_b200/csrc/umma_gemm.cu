@@ -6,7 +6,7 @@
 //
 // Shape of one CTA: 128 weight rows (the M axis of tcgen05.mma, one TMEM lane per row) by BN
 // tokens (the N axis, one TMEM column per token), K in blocks of 64 halves = one 128-byte
-// swizzle atom. Six warps with fixed roles:
+// swizzle atom. Six warps with fixed roles (ten with int8 weights):
 //   warp 0   TMA producer: one elected lane streams the weight tile and the activation tile
 //            of each k block into a ring of shared-memory stages (cp.async.bulk.tensor,
 //            128-byte swizzle, completion on an mbarrier);
@@ -15,10 +15,14 @@
 //            with tcgen05.commit; it also owns the TMEM allocation;
 //   warps 2-5  epilogue: read the accumulator with tcgen05.ld (each warp its own quarter of
 //            the 128 lanes), apply the row scale and beta*y, store fp32 rows coalesced along
-//            N. With int8 weights the same four warps first act as the dequantiser of the
-//            main loop: the producer lands raw int8 rows in a staging buffer, they widen
-//            them to fp16 straight into the swizzled operand layout (fence.proxy.async),
-//            so the fp16 copy of the matrix exists only in shared memory.
+//            N.
+// With int8 weights the fp16 copy of the matrix exists only in tensor memory. The producer lands
+// the raw int8 tile (64-byte swizzle) in the shared-memory ring; eight converter warps (2-5 take
+// the even k blocks, 6-9 the odd ones, one thread per weight row) widen 64 int8 to 64 halves
+// and write them with tcgen05.st into a second ring of 32-column TMEM slots; the MMA issuer
+// takes the A operand from that TMEM slot and the activation tile from shared memory. The two
+// rings are released separately (raw stage by the converters, TMEM slot and activation tile
+// by tcgen05.commit), so HBM loads run ahead of the conversion by the depth of the smem ring.
 // Weight bytes are read from HBM once per token tile; activations come from L2.
 //
 // Matrices with few 128-row tiles (the attention output and down projections have 32) would

@@ -10,11 +10,16 @@
 //                (K-major), D = S in TMEM (128 lanes x 128 columns, fp32), double-buffered so
 //                that the scores of tile j + 1 are computed while tile j is in softmax;
 //   softmax      eight warps, two threads per row, one per 64-key half of the tile, each with
-//                its own running (max, sum, O): tcgen05.ld the half row of S, scale, causal
-//                mask, P = exp2(.) as fp16 into shared memory in the A-operand layout;
-//   O_h = P_h V_h  one product per half: A = P_h, B = the V tile's 64 keys as they sit in
-//                shared memory ([key][d] = MN-major), D = O_h in TMEM;
-//   O = O * corr + O_h  in the softmax threads' registers (tcgen05.ld of O_h).
+//                its own running (reference max, sum): tcgen05.ld the half row of S, scale,
+//                causal mask (only on tiles that reach the diagonal), P = exp2(.) as fp16
+//                written back with tcgen05.st over the thread's own S columns;
+//   O_h += P_h V_h  one product per half: A = P_h read from TMEM, B = the V tile's 64 keys as
+//                they sit in shared memory ([key][d] = MN-major), D = O_h accumulating in TMEM.
+// O never leaves TMEM inside the loop. The exponent's reference max only moves when a row's
+// max has grown by more than 2^8 (any lane of the warp), and only then the warp waits for the
+// previous product and rescales its O_h in TMEM; P stays below 2^8 and exact in the final
+// quotient. So the softmax warps go from tile j straight to tile j + 1 while the tensor core
+// does P V of tile j and Q K^T of tile j + 2.
 // The two halves of a row are merged once, at the end (log-sum-exp), through shared memory.
 // Warp roles: warps 0 and 1 gather the K and the V tile (16-byte async copies that follow the
 // block table, swizzle applied by hand: a tile's rows come from eight scattered 16-key pages,
@@ -64,10 +69,9 @@ template <int D>
 struct PfSmem {
   static constexpr int kQBytes = kRows * D * 2;
   static constexpr int kKBytes = kKeys * D * 2;          // one K (or V) tile
-  static constexpr int kPBytes = kRows * kKeys * 2;
-  static constexpr int kStages = D == 64 ? 3 : 2;
+  static constexpr int kStages = D == 64 ? 4 : 3;
   static constexpr int kBarBytes = 256;
-  static constexpr size_t kTotal = kQBytes + static_cast<size_t>(kStages) * 2 * kKBytes + kPBytes + kBarBytes + 1024;
+  static constexpr size_t kTotal = kQBytes + static_cast<size_t>(kStages) * 2 * kKBytes + kBarBytes + 1024;
 };
 
 // Barrier for the 256 softmax threads only (the producer and MMA warps do not take part).
@@ -80,19 +84,19 @@ umma_prefill_kernel(const __half* __restrict__ kc, const __half* __restrict__ vc
                     float scale_log2e, int* __restrict__ status) {
   using S = PfSmem<D>;
   constexpr int NS = S::kStages;
-  // TMEM columns: S of even tiles 0..127, S of odd tiles 128..255, then the two halves' P V
-  // products (keys 0-63 and 64-127 of a tile), D columns each.
+  // TMEM columns: S of even tiles 0..127, S of odd tiles 128..255 (each half's P overwrites the
+  // first 32 of its 64 S columns), then the two halves' running O (keys 0-63 and 64-127 of
+  // every tile), D columns each.
   constexpr uint32_t kTmemCols = 512;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   unsigned char* gen = smem_dyn + (base - smem_u32(smem_dyn));
   const uint32_t sQ = base;
   const uint32_t sK = sQ + S::kQBytes;                 // NS stages of [K tile][V tile]
-  const uint32_t sP = sK + NS * 2 * S::kKBytes;
-  const uint32_t bars = sP + S::kPBytes;
-  const uint32_t kv_full = bars, kv_empty = bars + 24;                          // NS (<= 3) x 8 bytes each
-  const uint32_t s_ready = bars + 48;                                           // one per S buffer
-  const uint32_t p_ready = bars + 64, o_ready = bars + 80, o_free = bars + 96;  // one per half
+  const uint32_t bars = sK + NS * 2 * S::kKBytes;
+  const uint32_t kv_full = bars, kv_empty = bars + 32;     // NS (<= 4) x 8 bytes each
+  const uint32_t s_ready = bars + 64;                      // one per S buffer
+  const uint32_t p_ready = bars + 80, pv_done = bars + 96;  // one per half
   const uint32_t q_ready = bars + 112;
   const uint32_t tmem_slot = bars + 120;
 
@@ -114,8 +118,7 @@ umma_prefill_kernel(const __half* __restrict__ kc, const __half* __restrict__ vc
     for (int s = 0; s < 2; ++s) {
       mbar_init(s_ready + 8 * s, 1);
       mbar_init(p_ready + 8 * s, 4);
-      mbar_init(o_ready + 8 * s, 1);
-      mbar_init(o_free + 8 * s, 4);
+      mbar_init(pv_done + 8 * s, 1);
     }
     mbar_init(q_ready, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -148,9 +151,20 @@ umma_prefill_kernel(const __half* __restrict__ kc, const __half* __restrict__ vc
       if (lane == 0) mbar_arrive(kv_full + 8 * (j % NS));
     };
     int published = -1;  // last tile handed to the MMA warp
+    // Block-table entries are fetched 32 pages (four tiles) at a time, one per lane, a group
+    // ahead of their use, so no copy waits for a table lookup.
+    auto load_group = [&](int g) {
+      const int key0 = (g * 4 + lane / 8) * kKeys + (lane % 8) * 16;
+      return key0 < nk ? table[key0 / bs] : 0;
+    };
+    int tab_cur = 0, tab_next = load_group(0);
     for (int j = 0; j < ntiles && ok; ++j) {
       const int s = j % NS;
       const uint32_t free_parity = ((j / NS) & 1) ^ 1;
+      if (j % 4 == 0) {
+        tab_cur = tab_next;
+        tab_next = load_group(j / 4 + 1);
+      }
       // Never sleep on a stage with a landed tile still unpublished: the consumer that frees
       // the stage may itself be waiting for that tile.
       if (published < j - 1 && !__all_sync(0xffffffffu, mbar_test(kv_empty + 8 * s, free_parity))) {
@@ -161,15 +175,11 @@ umma_prefill_kernel(const __half* __restrict__ kc, const __half* __restrict__ vc
       ok = mbar_wait(kv_empty + 8 * s, free_parity);
       if (!ok) break;
       const uint32_t dst0 = sK + s * 2 * S::kKBytes + (warp == 0 ? 0 : S::kKBytes) + (c / 8) * (kKeys * 128);
-#pragma unroll 1
+#pragma unroll
       for (int pg = 0; pg < kKeys / 16; ++pg) {
         const int key0 = j * kKeys + pg * 16;
-        const bool page_ok = key0 < nk;
-        long long page_base = 0;
-        if (page_ok) {
-          const int blk = table[key0 / bs], slot = key0 % bs;
-          page_base = (static_cast<long long>(blk) * kv_heads + kvh) * bs * D + static_cast<long long>(slot) * D;
-        }
+        const int blk = __shfl_sync(0xffffffffu, tab_cur, (j % 4) * 8 + pg);
+        const long long page_base = (static_cast<long long>(blk) * kv_heads + kvh) * bs * D + static_cast<long long>(key0 % bs) * D;
 #pragma unroll
         for (int ii = 0; ii < 16 / RPI; ++ii) {
           const int rl = ii * RPI + rsub, r = pg * 16 + rl;  // row in the page, row in the tile
@@ -220,14 +230,14 @@ umma_prefill_kernel(const __half* __restrict__ kc, const __half* __restrict__ vc
 #pragma unroll 1
         for (int h = 0; h < 2 && ok; ++h) {  // keys 0-63, then 64-127: separate products, separate softmax states
           ok = mbar_wait(p_ready + 8 * h, j & 1);
-          if (ok && j > 0) ok = mbar_wait(o_free + 8 * h, (j - 1) & 1);
           if (!ok) break;
           tc_fence_after();
+          const uint32_t pa = tmem_base + (j & 1) * kKeys + h * 64;  // P_h: 64 halves = 32 columns per row
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_f16(tmem_base + 2 * kKeys + h * D, smem_desc_sw128(sP + h * (kRows * 128) + k * 32),
-                     smem_desc_mn_sw128(vt + (h * 4 + k) * 2048, kKeys * 128), idesc_pv, k != 0);
-          umma_commit(o_ready + 8 * h);
+            umma_f16_ta(tmem_base + 2 * kKeys + h * D, pa + 8 * k, smem_desc_mn_sw128(vt + (h * 4 + k) * 2048, kKeys * 128),
+                        idesc_pv, (j > 0) || (k != 0));
+          umma_commit(pv_done + 8 * h);
         }
         if (!ok) break;
         umma_commit(kv_empty + 8 * (j % NS));
@@ -267,93 +277,117 @@ umma_prefill_kernel(const __half* __restrict__ kc, const __half* __restrict__ vc
       __syncwarp();
       if (lane == 0) mbar_arrive(q_ready);
     }
-    float acc[D];
-#pragma unroll
-    for (int d = 0; d < D; ++d) acc[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_ref = -INFINITY, l_run = 0.f;  // m_ref: the max the exponents refer to (log2 domain)
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t tmem_o = tmem_base + 2 * kKeys + half * D + lane_sel;
     for (int j = 0; j < ntiles && ok; ++j) {
-      ok = mbar_wait(s_ready + 8 * (j & 1), (j >> 1) & 1);
+      ok = __all_sync(0xffffffffu, mbar_wait(s_ready + 8 * (j & 1), (j >> 1) & 1));
       if (!ok) break;
       tc_fence_after();
       const int key0 = j * kKeys + half * 64;
+      const uint32_t tmem_s = tmem_base + (j & 1) * kKeys + lane_sel + half * 64;
       uint32_t sv[64];
-      tmem_ld32(tmem_base + (j & 1) * kKeys + lane_sel + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-      tmem_ld32(tmem_base + (j & 1) * kKeys + lane_sel + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+      tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
       tmem_ld_wait();
+      const bool diag = j * kKeys + kKeys - 1 > pos0;  // some row of the tile does not see every key
+      if (diag) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (key0 + i > p) sv[i] = __float_as_uint(-INFINITY);
+      }
       float mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 64; ++i)
-        if (key0 + i <= p) mx = fmaxf(mx, __uint_as_float(sv[i]));
-      const float m_new = fmaxf(m_run, mx * scale_log2e);
-      // nothing visible to this half yet: keep everything at zero (exp2(-inf - -inf) would be NaN)
-      const float corr = m_new == -INFINITY ? 1.f : ex2(m_run - m_new);
-      float sum = 0.f;
+      for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+      const float m_cand = mx * scale_log2e;
+      if (__any_sync(0xffffffffu, m_cand > m_ref + 8.f)) {
+        // a row outgrew the reference by 2^8: move every row's reference to its exact max
+        // and rescale what has been accumulated (nothing yet on the first tile)
+        const float m_new = fmaxf(m_ref, m_cand);
+        const float corr = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);
+        if (j > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(pv_done + 8 * half, (j - 1) & 1));
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {  // eight 16-byte chunks = this half's 64 keys
-        uint32_t pk[4];
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tmem_o + c * 32, v);
+            tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int e = cc * 8 + 2 * i;
-          const float a = key0 + e <= p ? ex2(__uint_as_float(sv[e]) * scale_log2e - m_new) : 0.f;
-          const float b = key0 + e + 1 <= p ? ex2(__uint_as_float(sv[e + 1]) * scale_log2e - m_new) : 0.f;
-          sum += a + b;
-          pk[i] = pack_half2(a, b);
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+            tmem_st32(tmem_o + c * 32, v);
+          }
         }
-        *reinterpret_cast<uint4*>(gen + (sP - base) + half * (kRows * 128) + row * 128 + ((cc ^ (row & 7)) << 4)) =
-            make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        l_run *= corr;
+        m_ref = m_new;
       }
-      l_run = l_run * corr + sum;
-      m_run = m_new;
-      fence_async_smem();
+      // rows that see nothing yet keep m_ref = -inf; all their scores are masked to -inf
+      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+      float sum = 0.f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float a = ex2(fmaf(__uint_as_float(sv[2 * i]), scale_log2e, neg_m));
+        const float b = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), scale_log2e, neg_m));
+        sum += a + b;
+        pk[i] = pack_half2(a, b);
+      }
+      l_run += sum;
+      tmem_st32(tmem_s, pk);  // P over this thread's first 32 S columns
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready + 8 * half);
-
-      ok = mbar_wait(o_ready + 8 * half, j & 1);
-      if (!ok) break;
+    }
+    if (ok) {
+      ok = __all_sync(0xffffffffu, mbar_wait(pv_done + 8 * half, (ntiles - 1) & 1));
       tc_fence_after();
+    }
+    if (!ok) atomicExch(status, 13);
+    // Merge the two halves of each row: the second half parks (m, l, O) in the idle K/V stages
+    // as [value][row] (conflict-free), the first half combines and stores.
+    float* park = reinterpret_cast<float*>(gen + (sK - base));
+    if (half == 1 && ok) {
+      park[row] = m_ref;
+      park[kRows + row] = l_run;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t v[32];
         tmem_ld32(tmem_o + c * 32, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * corr + __uint_as_float(v[i]);
+        for (int i = 0; i < 32; ++i) park[(2 + c * 32 + i) * kRows + row] = __uint_as_float(v[i]);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(o_free + 8 * half);
-    }
-    if (!ok) atomicExch(status, 13);
-    // Merge the two halves of each row: the second half parks (m, l, O) in the idle K/V stages
-    // as [value][row] (conflict-free), the first half combines and stores.
-    float* park = reinterpret_cast<float*>(gen + (sK - base));
-    if (half == 1) {
-      park[row] = m_run;
-      park[kRows + row] = l_run;
-#pragma unroll
-      for (int d = 0; d < D; ++d) park[(2 + d) * kRows + row] = acc[d];
     }
     softmax_bar();
-    if (half == 0 && ok && (row & 63) < nrows) {
+    if (half == 0 && ok) {
       const float m_b = park[row], l_b = park[kRows + row];
-      const float M = fmaxf(m_run, m_b);  // the first half always sees key 0, so M is finite
-      const float wa = ex2(m_run - M), wb = m_b == -INFINITY ? 0.f : ex2(m_b - M);
+      const float M = fmaxf(m_ref, m_b);  // the first half always sees key 0, so M is finite
+      const float wa = ex2(m_ref - M), wb = m_b == -INFINITY ? 0.f : ex2(m_b - M);
       const float inv = 1.0f / (wa * l_run + wb * l_b);
+      const bool live = (row & 63) < nrows;
       __half* dst = out + static_cast<long long>(t0 + (row & 63)) * o_stride + head * D;
 #pragma unroll
-      for (int c = 0; c < D / 8; ++c) {
-        float o[8];
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_o + c * 32, v);  // every lane takes part in the load; only live rows store
+        tmem_ld_wait();
+        if (live) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = (wa * acc[c * 8 + i] + wb * park[(2 + c * 8 + i) * kRows + row]) * inv;
-        uint4 v;
-        v.x = pack_half2(o[0], o[1]);
-        v.y = pack_half2(o[2], o[3]);
-        v.z = pack_half2(o[4], o[5]);
-        v.w = pack_half2(o[6], o[7]);
-        *reinterpret_cast<uint4*>(dst + c * 8) = v;
+          for (int g = 0; g < 4; ++g) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              o[i] = (wa * __uint_as_float(v[g * 8 + i]) + wb * park[(2 + c * 32 + g * 8 + i) * kRows + row]) * inv;
+            uint4 w;
+            w.x = pack_half2(o[0], o[1]);
+            w.y = pack_half2(o[2], o[3]);
+            w.z = pack_half2(o[4], o[5]);
+            w.w = pack_half2(o[6], o[7]);
+            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = w;
+          }
+        }
       }
     }
   }
