@@ -272,6 +272,24 @@ def op_suite(peak_gbs: float, peak_tflops: float) -> dict:
     out["flash_prefill_attention"] = {"workload": "2048-token prompt as 4 x 512 chunks, 32q/4kv heads, D64, causal", "us": ms * 1e3,
                                       "tflops": flops / ms / 1e9, "frac_of_measured_bf16": flops / ms / 1e9 / peak_tflops,
                                       "tok_per_s": 2048 / (ms * 1e-3)}
+    # the same kernel at the decode model's head layout: one 512-token chunk at the end of a
+    # 16k-token context (long enough that the key loop, not the launch, sets the time)
+    heads, kvh, D, ctx = 32, 8, 128, 16384
+    nblk = ctx // bs
+    kp = torch.randn((nblk, kvh, bs, D), device=dev, dtype=torch.float16)
+    vp = torch.randn((nblk, kvh, bs, D), device=dev, dtype=torch.float16)
+    table = torch.randperm(nblk, device=dev).to(torch.int32)
+    p = torch.arange(ctx - 512, ctx, dtype=torch.int32, device=dev)
+    m = ops.TokenMeta(p, torch.zeros(512, dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev), table)
+    tiles = torch.tensor([[r, 64] for r in range(0, 512, 64)], dtype=torch.int32, device=dev).flatten()
+    q = torch.randn((512, (heads + 2 * kvh) * D), device=dev)
+    o = torch.zeros((512, heads * D), device=dev, dtype=torch.float16)
+    shape = ops.attn_shape(heads, kvh, D, bs)
+    ms = time_in_graph(lambda _: ops.prefill_attention(shape, q, m, tiles, kp, vp, o), 1, iters=10)
+    flops = 4 * D * heads * sum(pp + 1 for pp in range(ctx - 512, ctx))
+    out["flash_prefill_attention_long"] = {"workload": "512-token chunk at the end of a 16384-token context, 32q/8kv heads, D128, causal, pages in random order",
+                                           "us": ms * 1e3, "tflops": flops / ms / 1e9,
+                                           "frac_of_measured_bf16": flops / ms / 1e9 / peak_tflops}
     return out
 
 

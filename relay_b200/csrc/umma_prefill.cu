@@ -21,13 +21,14 @@
 // quotient. So the softmax warps go from tile j straight to tile j + 1 while the tensor core
 // does P V of tile j and Q K^T of tile j + 2.
 // The two halves of a row are merged once, at the end (log-sum-exp), through shared memory.
-// Warp roles: warps 0 and 1 gather the K and the V tile (16-byte async copies that follow the
-// block table, swizzle applied by hand: a tile's rows come from eight scattered 16-key pages,
-// and one small TMA box per page was measured slower than the copies), warp 2 issues the
-// MMAs and owns TMEM, warps 4-11 softmax / accumulate / epilogue.
+// Warp roles: warps 0, 1 and 3 fetch the K and V tiles (one TMA box per 16-key page and 64-wide
+// slice of the head, addressed through the block table), warp 2 issues the MMAs and owns
+// TMEM, warps 4-11 softmax / epilogue.
 //
 // Every mbarrier wait is bounded in time; a wait that gives up records a code in the
 // device's status word (tc::status_word) and the CTA still frees its TMEM and exits.
+#include <cuda.h>
+
 #include <cstdlib>
 #include <mutex>
 #include <string>
@@ -43,7 +44,7 @@ namespace {
 
 constexpr int kKeys = 128;      // keys per tile (N of the first MMA, K of the second)
 constexpr int kRows = 128;      // 2 heads x 64 query positions
-constexpr int kPfThreads = 384;  // K loader, V loader, MMA issuer, one idle warp, 8 softmax warps
+constexpr int kPfThreads = 384;  // two loader warps, MMA issuer, third loader warp, 8 softmax warps
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -79,11 +80,13 @@ __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" 
 
 template <int D>
 __global__ void __launch_bounds__(kPfThreads, 1)
-umma_prefill_kernel(const __half* __restrict__ kc, const __half* __restrict__ vc, const float* __restrict__ q, TokenMeta m, const int2* __restrict__ tiles,
+umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const __half* __restrict__ kc, const __half* __restrict__ vc, const float* __restrict__ q, TokenMeta m, const int2* __restrict__ tiles,
                     __half* __restrict__ out, int heads, int kv_heads, int bs, int q_stride, int o_stride,
                     float scale_log2e, int* __restrict__ status) {
   using S = PfSmem<D>;
   constexpr int NS = S::kStages;
+  // how far (log2) a row's max may outgrow the exponent reference before O is rescaled
+  constexpr float kGrow = 8.f;
   // TMEM columns: S of even tiles 0..127, S of odd tiles 128..255 (each half's P overwrites the
   // first 32 of its 64 S columns), then the two halves' running O (keys 0-63 and 64-127 of
   // every tile), D columns each.
@@ -112,7 +115,7 @@ umma_prefill_kernel(const __half* __restrict__ kc, const __half* __restrict__ vc
 
   if (warp == 0 && lane == 0) {
     for (int s = 0; s < NS; ++s) {
-      mbar_init(kv_full + 8 * s, 2);  // the K loader and the V loader
+      mbar_init(kv_full + 8 * s, 1);  // the loader's expect-tx arrival (or its plain arrival after a gathered tile)
       mbar_init(kv_empty + 8 * s, 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -134,68 +137,67 @@ umma_prefill_kernel(const __half* __restrict__ kc, const __half* __restrict__ vc
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(gen + (tmem_slot - base));
 
   bool ok = true;
-  if (warp < 2) {
-    // ---- loaders: warp 0 gathers the K tile, warp 1 the V tile, 16 bytes per lane and copy.
-    //      A tile's rows come from 8 pages (16 keys each) that the block table scatters over
-    //      the pool; async copies with the swizzle applied by hand move them faster than
-    //      one small TMA box per page would. A tile is published one tile late, after its
-    //      copies have landed and been made visible to the tensor core's proxy, so two
-    //      tiles' copies are in flight while the warp issues the next. ----
-    constexpr int CH = D / 8;              // 16-byte chunks per row
-    constexpr int RPI = 32 / CH;           // rows one warp instruction covers
-    const __half* pool = warp == 0 ? kc : vc;
-    const int c = lane % CH, rsub = lane / CH;
-    auto publish = [&](int j) {
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(kv_full + 8 * (j % NS));
-    };
-    int published = -1;  // last tile handed to the MMA warp
-    // Block-table entries are fetched 32 pages (four tiles) at a time, one per lane, a group
-    // ahead of their use, so no copy waits for a table lookup.
-    auto load_group = [&](int g) {
+  if (warp < 2 || warp == 3) {
+    // ---- loaders: a tile's 128 keys come from 8 pages (16 keys each) that the block table
+    //      scatters over the pool. One TMA box per page and 64-wide slice of the head (16 rows
+    //      x 128 bytes, 128-byte swizzle), completing on the stage's mbarrier. Issuing a box
+    //      costs the issuing warp some 90 cycles whatever its size, so the 16 (D = 64) or 32
+    //      boxes of a tile are dealt round-robin to three warps, one box per lane.
+    //      Block-table entries are read 32 pages (four tiles) at a time, one per lane, a
+    //      group ahead of their use, so no copy waits for a table lookup. A last tile that
+    //      reaches past the context is gathered by warp 0 with 16-byte async copies
+    //      instead, which write zeros for the missing keys (the pool may hold anything
+    //      there, and 0 x NaN would poison P V). ----
+    constexpr int kAtoms = D / 64;
+    constexpr int kBoxes = 2 * 8 * kAtoms;  // K then V; per operand: [64-wide slice][page]
+    const int li = warp == 3 ? 2 : warp;    // loader index 0..2
+    const int box = li + 3 * lane;          // this lane's box of every tile
+    const bool has_box = box < kBoxes;
+    const int box_pg = box & 7, box_atom = (box >> 3) % kAtoms, box_v = box / (8 * kAtoms);
+    auto load_group = [&](int g) {  // first pool row ([block][kv head][slot]) of this lane's page
       const int key0 = (g * 4 + lane / 8) * kKeys + (lane % 8) * 16;
-      return key0 < nk ? table[key0 / bs] : 0;
+      if (key0 >= nk) return 0;
+      return (table[key0 / bs] * kv_heads + kvh) * bs + key0 % bs;
     };
     int tab_cur = 0, tab_next = load_group(0);
     for (int j = 0; j < ntiles && ok; ++j) {
       const int s = j % NS;
-      const uint32_t free_parity = ((j / NS) & 1) ^ 1;
       if (j % 4 == 0) {
         tab_cur = tab_next;
         tab_next = load_group(j / 4 + 1);
       }
-      // Never sleep on a stage with a landed tile still unpublished: the consumer that frees
-      // the stage may itself be waiting for that tile.
-      if (published < j - 1 && !__all_sync(0xffffffffu, mbar_test(kv_empty + 8 * s, free_parity))) {
-        cp_async_wait<0>();
-        publish(j - 1);
-        published = j - 1;
-      }
-      ok = mbar_wait(kv_empty + 8 * s, free_parity);
+      ok = __all_sync(0xffffffffu, mbar_wait(kv_empty + 8 * s, ((j / NS) & 1) ^ 1));
       if (!ok) break;
-      const uint32_t dst0 = sK + s * 2 * S::kKBytes + (warp == 0 ? 0 : S::kKBytes) + (c / 8) * (kKeys * 128);
+      const uint32_t kdst = sK + s * 2 * S::kKBytes;
+      if ((j + 1) * kKeys <= nk) {
+        const int row = __shfl_sync(0xffffffffu, tab_cur, (j % 4) * 8 + box_pg);
+        if (warp == 0 && lane == 0) mbar_expect_tx(kv_full + 8 * s, 2 * S::kKBytes);
+        if (has_box)
+          tma_load_2d(kdst + box_v * S::kKBytes + box_atom * (kKeys * 128) + box_pg * 2048, box_v ? &map_v : &map_k,
+                      box_atom * 64, row, kv_full + 8 * s);
+      } else if (warp == 0) {
+        constexpr int CH = D / 8;     // 16-byte chunks per row
+        constexpr int RPI = 32 / CH;  // rows one warp instruction covers
+        const int c = lane % CH, rsub = lane / CH;
+#pragma unroll 1
+        for (int pg = 0; pg < 2 * (kKeys / 16); ++pg) {  // K pages, then V pages
+          const long long src_row = __shfl_sync(0xffffffffu, tab_cur, (j % 4) * 8 + (pg & 7));
+          const __half* src = (pg < 8 ? kc : vc) + src_row * D;
+          const uint32_t dst = kdst + (pg < 8 ? 0 : S::kKBytes) + (pg & 7) * 2048 + (c / 8) * (kKeys * 128);
 #pragma unroll
-      for (int pg = 0; pg < kKeys / 16; ++pg) {
-        const int key0 = j * kKeys + pg * 16;
-        const int blk = __shfl_sync(0xffffffffu, tab_cur, (j % 4) * 8 + pg);
-        const long long page_base = (static_cast<long long>(blk) * kv_heads + kvh) * bs * D + static_cast<long long>(key0 % bs) * D;
-#pragma unroll
-        for (int ii = 0; ii < 16 / RPI; ++ii) {
-          const int rl = ii * RPI + rsub, r = pg * 16 + rl;  // row in the page, row in the tile
-          const int bytes = key0 + rl < nk ? 16 : 0;          // keys past the context: zeros
-          cp_async16_zfill(dst0 + r * 128 + (((c & 7) ^ (r & 7)) << 4), pool + page_base + (bytes ? rl * D + c * 8 : 0), bytes);
+          for (int ii = 0; ii < 16 / RPI; ++ii) {
+            const int rl = ii * RPI + rsub;
+            const int bytes = j * kKeys + (pg & 7) * 16 + rl < nk ? 16 : 0;
+            cp_async16_zfill(dst + rl * 128 + (((c & 7) ^ (rl & 7)) << 4), src + (bytes ? rl * D + c * 8 : 0), bytes);
+          }
         }
-      }
-      cp_async_commit();
-      if (published < j - 1) {  // the usual case: tile j - 1 lands while tile j's copies are issued
-        cp_async_wait<1>();
-        publish(j - 1);
-        published = j - 1;
+        cp_async_commit();
+        cp_async_wait<0>();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(kv_full + 8 * s);
       }
     }
-    cp_async_wait<0>();
-    if (ok && published < ntiles - 1) publish(ntiles - 1);
     if (!ok && lane == 0) atomicExch(status, 11);
   } else if (warp == 2) {
     // ---- MMA issuer ----
@@ -296,13 +298,33 @@ umma_prefill_kernel(const __half* __restrict__ kc, const __half* __restrict__ vc
         for (int i = 0; i < 64; ++i)
           if (key0 + i > p) sv[i] = __float_as_uint(-INFINITY);
       }
-      float mx = -INFINITY;
+      // Exponentials against the current reference, with the row maximum gathered in the same
+      // pass (four chains each, not one 64-deep): the maximum is only needed to notice that a
+      // row outgrew the reference, and then the pass is repeated.
+      uint32_t pk[32];
+      float sum = 0.f, mx = 0.f;
+      auto exp_pass = [&](float neg_m) {
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        for (int i = 0; i < 32; ++i) {
+          const float s0 = __uint_as_float(sv[2 * i]), s1 = __uint_as_float(sv[2 * i + 1]);
+          const float a = ex2(fmaf(s0, scale_log2e, neg_m));
+          const float b = ex2(fmaf(s1, scale_log2e, neg_m));
+          mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(s0, s1));
+          sum4[i & 3] += a + b;
+          pk[i] = pack_half2(a, b);
+        }
+        sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      };
+      // rows that see nothing yet keep m_ref = -inf; all their scores are masked to -inf
+      exp_pass(m_ref == -INFINITY ? 0.f : -m_ref);
       const float m_cand = mx * scale_log2e;
-      if (__any_sync(0xffffffffu, m_cand > m_ref + 8.f)) {
-        // a row outgrew the reference by 2^8: move every row's reference to its exact max
-        // and rescale what has been accumulated (nothing yet on the first tile)
+      if (__any_sync(0xffffffffu, m_cand > m_ref + kGrow)) {
+        // a row outgrew the reference by 2^8 (always so on a row's first visible tile): move every
+        // row's reference to its exact max, rescale what has been accumulated (nothing yet on
+        // the first tile) and redo the exponentials
         const float m_new = fmaxf(m_ref, m_cand);
         const float corr = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);
         if (j > 0) {
@@ -321,19 +343,18 @@ umma_prefill_kernel(const __half* __restrict__ kc, const __half* __restrict__ vc
         }
         l_run *= corr;
         m_ref = m_new;
-      }
-      // rows that see nothing yet keep m_ref = -inf; all their scores are masked to -inf
-      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-      float sum = 0.f;
-      uint32_t pk[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float a = ex2(fmaf(__uint_as_float(sv[2 * i]), scale_log2e, neg_m));
-        const float b = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), scale_log2e, neg_m));
-        sum += a + b;
-        pk[i] = pack_half2(a, b);
+        exp_pass(m_ref == -INFINITY ? 0.f : -m_ref);
       }
       l_run += sum;
+      // Arrive for tile j only after this half's product of tile j - 1 has completed (normally
+      // long ago). The MMA warp looks at the halves in turn; without this a half could arrive
+      // for two tiles while the MMA warp waits for the other half, and a phase that completes
+      // twice unobserved looks incomplete to a parity wait. It also keeps the four warps that
+      // share p_ready (four arrivals per tile) within one tile of each other.
+      if (j > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(pv_done + 8 * half, (j - 1) & 1));
+        if (!ok) break;
+      }
       tmem_st32(tmem_s, pk);  // P over this thread's first 32 S columns
       tmem_st_wait();
       tc_fence_before();
@@ -409,10 +430,15 @@ void launch_umma_prefill_d(const AttnShape& s, const float* q, const TokenMeta& 
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
     configured = true;
   }
+  // The layer's pool as rows of D halves, box = one 16-key page x 64 dims; the row count only
+  // bounds coordinates (the kernel never asks for a row the block table does not name).
+  const long long rows = 1LL << 31;
+  const CUtensorMap mk = make_map(kc, 2, rows, D, D, 16, 64, true);
+  const CUtensorMap mv = make_map(vc, 2, rows, D, D, 16, 64, true);
   const float scale_log2e = kLog2e / sqrtf(static_cast<float>(D));
   dim3 grid(n_tiles, s.heads / 2);
   count_launch();
-  kernel<<<grid, kPfThreads, S::kTotal, st>>>(kc, vc, q, m, tiles, out, s.heads, s.kv_heads, s.block_size, s.q_stride,
+  kernel<<<grid, kPfThreads, S::kTotal, st>>>(mk, mv, kc, vc, q, m, tiles, out, s.heads, s.kv_heads, s.block_size, s.q_stride,
                                               s.o_stride, scale_log2e, status_word());
 }
 

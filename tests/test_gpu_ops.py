@@ -244,6 +244,29 @@ def test_prefill_attention_matches_oracle(ops, D, heads, kv_heads, bs, ctxs, chu
     assert row_err(got, want) < ATTN_TOL
 
 
+@pytest.mark.parametrize("D,heads,kv_heads,ctx,chunk", [(64, 8, 2, 1100, 640), (128, 8, 4, 900, 300), (64, 4, 2, 333, 333)])
+def test_prefill_attention_with_peaked_scores_and_dirty_pool(ops, D, heads, kv_heads, ctx, chunk):
+    # Scores three times wider than N(0,1) queries give: row maxima keep growing by several
+    # octaves after the first key tile, so the running output is rescaled in later tiles too.
+    # Cache slots past the context hold NaN: nothing outside the context may reach a result.
+    bs = 16
+    nb = (ctx + bs - 1) // bs + 2
+    case = paged_attention_case(50 + D, [ctx], [chunk], heads, kv_heads, D, bs, nb)
+    case["q"] = (case["q"] * 3).astype(np.float16).astype(np.float32)
+    want = oracle_attention(case)
+    dirty = dict(case)
+    used = np.zeros((nb, bs), bool)
+    for j in range(ctx):
+        used[case["tables"][case["table_off"][0] + j // bs], j % bs] = True
+    for name in ("k_pool", "v_pool"):
+        pool = case[name].copy()  # [blocks, kv heads, slots, D]
+        pool[np.broadcast_to(~used[:, None, :, None], pool.shape)] = np.nan
+        dirty[name] = pool
+    got = run_attention(ops, dirty, "prefill")
+    assert np.isfinite(got).all()
+    assert row_err(got, want) < ATTN_TOL
+
+
 @pytest.mark.parametrize("D,heads,kv_heads,bs", [(8, 8, 2, 16), (16, 4, 2, 16), (128, 32, 8, 16), (96, 6, 3, 4), (256, 2, 1, 16)])
 def test_reference_attention_matches_oracle(ops, D, heads, kv_heads, bs):
     ctxs, chunks = [1, 130, 300], [1, 60, 1]
