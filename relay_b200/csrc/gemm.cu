@@ -409,9 +409,24 @@ gemm_kernel(const void* __restrict__ wv, const float* __restrict__ scale, const 
 
 }  // namespace
 
-size_t gemv_scratch_bytes(int N, int K) {
+static size_t gemv_partials_bytes(int N, int K) {
   const int splits = plan_gemv(N, K).splits;
-  return gemv_counter_bytes(N) + (splits > 1 ? static_cast<size_t>(splits) * N * 8 * sizeof(float) : 0);
+  const size_t bytes = gemv_counter_bytes(N) + (splits > 1 ? static_cast<size_t>(splits) * N * 8 * sizeof(float) : 0);
+  return (bytes + 255) / 256 * 256;
+}
+
+size_t gemv_scratch_bytes(int N, int K, int max_tokens) {
+  return gemv_partials_bytes(N, K) + i8_digits_bytes(max_tokens, K);
+}
+
+// int8 weights with few tokens: the integer tensor-core kernel once the matrix is large enough
+// to pay for its activation pass (a second small launch); smaller ones stay on the register GEMV.
+static bool i8_digits_preferred(const WeightView& W) {
+  static const long long min_bytes = [] {
+    const char* e = std::getenv("RB200_I8_MIN_MB");
+    return (e ? std::atoll(e) : 2) << 20;
+  }();
+  return static_cast<long long>(W.N) * W.K >= min_bytes;
 }
 
 static bool gemm_forced_legacy() {
@@ -438,14 +453,13 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
   // fp16 weights stream faster through TMA (whole 128-byte row pieces) than through per-lane
   // 16-byte loads, so the few-token case uses the tcgen05 kernel with a 16-token tile.
   if (W.f16 && !gemm_forced_legacy() && umma_gemm_usable(W, x, ldx)) return launch_umma_gemm(W, x, ldx, y, T, beta, st);
-  // int8: the same kernel (tile widened into TMEM) wins once the matrix is large enough to
-  // amortise its longer prologue; measured crossover near 32 MB
-  if (W.i8 && static_cast<long long>(W.N) * W.K >= (32LL << 20) && !gemm_forced_legacy() && umma_gemm_usable(W, x, ldx))
-    return launch_umma_gemm(W, x, ldx, y, T, beta, st);
+  if (W.i8 && !gemm_forced_legacy() && i8_digits_preferred(W) && umma_i8_usable(W, x, ldx, T) && scratch != nullptr &&
+      scratch_bytes >= gemv_partials_bytes(W.N, W.K) + i8_digits_bytes(T, W.K))
+    return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + gemv_partials_bytes(W.N, W.K), st);
   unsigned* counters = static_cast<unsigned*>(scratch);
   float* partials = scratch ? reinterpret_cast<float*>(static_cast<char*>(scratch) + gemv_counter_bytes(W.N)) : nullptr;
   const GemvPlan p = plan_gemv(W.N, W.K);
-  RB_REQUIRE(p.splits == 1 || (scratch != nullptr && scratch_bytes >= gemv_scratch_bytes(W.N, W.K)),
+  RB_REQUIRE(p.splits == 1 || (scratch != nullptr && scratch_bytes >= gemv_partials_bytes(W.N, W.K)),
              "gemv: scratch too small");
   const size_t smem = static_cast<size_t>(8) * (round_up(p.chunk, 128) + gemv_x_pad(W.i8 != nullptr)) * sizeof(__half);
   RB_REQUIRE((static_cast<size_t>(W.ld) * (W.i8 ? 1 : 2)) % 32 == 0 && (reinterpret_cast<uintptr_t>(W.i8 ? static_cast<const void*>(W.i8) : static_cast<const void*>(W.f16)) & 31) == 0,
@@ -460,9 +474,19 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
                                                             p.splits, counters, partials);
 }
 
-void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st) {
+void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st, void* scratch,
+                 size_t scratch_bytes) {
   check_linear(W, ldx, T);
   if (T == 0) return;
+  if (W.i8 && !gemm_forced_legacy() && umma_i8_usable(W, x, ldx, T)) {
+    const size_t off = gemv_partials_bytes(W.N, W.K), need = i8_digits_bytes(T, W.K);
+    if (scratch != nullptr && scratch_bytes >= off + need) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + off, st);
+    void* tmp = nullptr;  // no caller buffer: stream-ordered allocation, released behind the kernels
+    RB_CUDA(cudaMallocAsync(&tmp, need, st));
+    launch_umma_i8(W, x, ldx, y, T, beta, tmp, st);
+    RB_CUDA(cudaFreeAsync(tmp, st));
+    return;
+  }
   if (!gemm_forced_legacy() && umma_gemm_usable(W, x, ldx)) return launch_umma_gemm(W, x, ldx, y, T, beta, st);
   launch_gemm_mma_sync(W, x, ldx, y, T, beta, st);
 }
@@ -481,7 +505,7 @@ void launch_gemm_mma_sync(const WeightView& W, const __half* x, int ldx, float* 
 void launch_linear(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch,
                    size_t scratch_bytes, cudaStream_t st) {
   if (T <= 8) launch_gemv(W, x, ldx, y, T, beta, scratch, scratch_bytes, st);
-  else launch_gemm(W, x, ldx, y, T, beta, st);
+  else launch_gemm(W, x, ldx, y, T, beta, st, scratch, scratch_bytes);
 }
 
 }  // namespace rb200
@@ -494,7 +518,7 @@ extern "C" {
 
 size_t rb200_gemv_scratch_bytes(int N, int K) {
   if (N <= 0 || K < 64) return 256;
-  return gemv_scratch_bytes(N, K);
+  return gemv_scratch_bytes(N, K, 8);
 }
 
 int rb200_gemv_int8(const int8_t* wq, const float* scale, const void* x, float* y, int T, int K, int N, int ldw, int ldx,

@@ -65,13 +65,18 @@ struct WeightView {
   const float* scale = nullptr;
   int N = 0, K = 0, ld = 0;
 };
-size_t gemv_scratch_bytes(int N, int K);
+// Scratch of the few-token kernels for an [N][K] matrix: split-K counters and partials of the
+// register GEMV, then room for `max_tokens` activation rows as int8 digits (umma_i8_gemm.cu).
+size_t gemv_scratch_bytes(int N, int K, int max_tokens = 8);
 // y[T,N] = x[T,K] W^T (+ beta*y); routes T <= 8 to the GEMV and larger T to the GEMM.
 void launch_linear(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch,
                    size_t scratch_bytes, cudaStream_t st);
 void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch,
                  size_t scratch_bytes, cudaStream_t st);
-void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st);
+// `scratch` (may be null) is the buffer gemv_scratch_bytes(N, K, 64) sizes; without it the int8
+// path for up to 64 tokens takes its digit buffer from the stream's memory pool.
+void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st,
+                 void* scratch = nullptr, size_t scratch_bytes = 0);
 // The same product with legacy mma.sync tiles (any alignment); launch_gemm prefers the
 // tcgen05 kernel of umma_gemm.cu and falls back to this one.
 void launch_gemm_mma_sync(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st);
@@ -89,5 +94,13 @@ bool umma_gemm_usable(const WeightView& W, const __half* x, int ldx);
 void launch_umma_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st);
 // 0, or the code a bounded pipeline wait of the tcgen05 GEMM left on the current device.
 int umma_gemm_status();
+
+// ---- umma_i8_gemm.cu ----
+// int8 weights x up to 64 tokens on the integer tensor cores: the activations are rewritten
+// as three int8 digits per element into `scratch` (i8_digits_bytes(T, K) bytes, 16-byte
+// aligned) by a first kernel, the second multiplies the raw int8 weight tiles by them.
+size_t i8_digits_bytes(int T, int K);
+bool umma_i8_usable(const WeightView& W, const __half* x, int ldx, int T);
+void launch_umma_i8(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch, cudaStream_t st);
 
 }  // namespace rb200

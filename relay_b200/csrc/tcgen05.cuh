@@ -15,6 +15,10 @@ namespace tc {
 // [box_rows][box_cols] box, optionally with the 128-byte swizzle.
 CUtensorMap make_map(const void* ptr, int elem_bytes, long long rows, long long cols, long long ld, int box_rows,
                      int box_cols, bool swizzle128, bool swizzle64 = false);
+// A 3-D descriptor over 1-byte elements, dims (d0 contiguous, d1, d2) with byte strides ld1 and
+// ld2 and a [box2][box1][box0] box, 128-byte swizzle.
+CUtensorMap make_map_3d(const void* ptr, long long d0, long long d1, long long d2, long long ld1, long long ld2, int box0,
+                        int box1, int box2);
 // One int per device, zero unless a bounded pipeline wait of a tcgen05 kernel gave up.
 int* status_word();
 

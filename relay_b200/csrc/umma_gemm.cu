@@ -357,6 +357,21 @@ CUtensorMap tc::make_map(const void* ptr, int elem_bytes, long long rows, long l
   return m;
 }
 
+// A 3-D tensor map over 1-byte elements [d2][d1][d0] (d0 contiguous, byte strides ld1, ld2), 128-byte swizzle.
+CUtensorMap tc::make_map_3d(const void* ptr, long long d0, long long d1, long long d2, long long ld1, long long ld2, int box0,
+                            int box1, int box2) {
+  CUtensorMap m;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(d0), static_cast<cuuint64_t>(d1), static_cast<cuuint64_t>(d2)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld1), static_cast<cuuint64_t>(ld2)};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(box0), static_cast<cuuint32_t>(box1), static_cast<cuuint32_t>(box2)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) fail(RB200_ERR_RUNTIME, "cuTensorMapEncodeTiled (3-D) failed with code " + std::to_string(static_cast<int>(r)));
+  return m;
+}
+
 int* tc::status_word() {
   // One word per device, allocated on first use and kept for the life of the process.
   static int* words[64] = {nullptr};
