@@ -86,7 +86,7 @@ struct UmmaSmem {
 template <int BN, bool INT8>
 __global__ void __launch_bounds__(INT8 ? kUmmaThreadsInt8 : kUmmaThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                 const float* __restrict__ scale, float* __restrict__ y, int T, int N, int K, float beta,
+                 const float* __restrict__ scale, float* __restrict__ y, int T, int N, int K, int rows, float beta,
                  int* __restrict__ status) {
   using S = UmmaSmem<BN, INT8>;
   constexpr int NS = S::kStages;
@@ -110,7 +110,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   unsigned char* gen_base = smem_dyn + (base - smem_u32(smem_dyn));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * kTileM, tok0 = blockIdx.y * BN;
+  // `rows` (a multiple of 8, at most 128) weight rows per CTA: the host shrinks the tile so that
+  // the grid fills the SMs evenly; the MMA still spans 128 lanes and the rest is ignored.
+  const int m0 = blockIdx.x * rows, tok0 = blockIdx.y * BN;
+  const uint32_t stage_tx = static_cast<uint32_t>(rows) * kBlockK * (INT8 ? 1 : 2) + S::kBBytes;
   const int splits = gridDim.z, split = blockIdx.z;  // the cluster spans z: split == rank in the cluster
   const int nk_all = K / kBlockK;
   const int kb_begin = static_cast<int>(static_cast<long long>(nk_all) * split / splits);
@@ -148,7 +151,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         ok = mbar_wait(empty_bar + 8 * s, ((kb / NS) & 1) ^ 1);
         if (INT8 && ok) ok = mbar_wait(raw_free + 8 * s, ((kb / NS) & 1) ^ 1);
         if (!ok) break;
-        mbar_expect_tx(full_bar + 8 * s, (INT8 ? S::kRawBytes : S::kABytes) + S::kBBytes);
+        mbar_expect_tx(full_bar + 8 * s, stage_tx);
         const int kx = (kb_begin + kb) * kBlockK;
         if (INT8) tma_load_2d(sRaw + s * S::kRawBytes, &map_w, kx, m0, full_bar + 8 * s);
         else tma_load_2d(sA + s * S::kABytes, &map_w, kx, m0, full_bar + 8 * s);
@@ -227,7 +230,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
     const int row = quarter * 32 + lane;
     const int n = m0 + row;
-    const float sc = (INT8 && n < N) ? scale[n] : 1.0f;
+    const bool live = row < rows && n < N;
+    const float sc = (INT8 && live) ? scale[n] : 1.0f;
     if (warp >= 6) {
       // nothing: only widening warps
     } else if (splits == 1) {
@@ -237,7 +241,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           uint32_t v[32];
           tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
           tmem_ld_wait();
-          if (n < N) {
+          if (live) {
             float* d0 = y + static_cast<long long>(tok0 + c0) * N + n;
             const int nt = min(32, T - tok0 - c0);  // valid token columns of this chunk
             if (beta != 0.f) {
@@ -273,7 +277,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     if (warp >= 2 && warp < 6) {
       const int row = (warp & 3) * 32 + lane;
       const int n = m0 + row;
-      const float sc = (INT8 && n < N) ? scale[n] : 1.0f;
+      const bool live = row < rows && n < N;
+      const float sc = (INT8 && live) ? scale[n] : 1.0f;
       const int per = (BN + splits - 1) / splits;  // token columns this CTA finishes
       const int c_begin = split * per, c_end = min(min(BN, c_begin + per), T - tok0);
       uint32_t peer[8];
@@ -285,7 +290,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           acc[j] = 0.f;
-          old[j] = (beta != 0.f && n < N && c + j < c_end) ? y[static_cast<long long>(tok0 + c + j) * N + n] : 0.f;
+          old[j] = (beta != 0.f && live && c + j < c_end) ? y[static_cast<long long>(tok0 + c + j) * N + n] : 0.f;
         }
 #pragma unroll
         for (int r = 0; r < 8; ++r) {  // members in rank order: the sum is the same on every run
@@ -300,7 +305,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[j] += part[j];
         }
-        if (n < N) {
+        if (live) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             if (c + j < c_end) y[static_cast<long long>(tok0 + c + j) * N + n] = acc[j] * sc + beta * old[j];
@@ -397,20 +402,60 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
     configured = true;
   }
-  const CUtensorMap mw = INT8 ? make_map(W.i8, 1, W.N, W.K, W.ld, kTileM, kBlockK, false, true)
-                              : make_map(W.f16, 2, W.N, W.K, W.ld, kTileM, kBlockK, true);
+  // Rows per CTA and the K split (a cluster along z): the pair that needs the fewest
+  // (waves x bytes per CTA), where a CTA's fixed cost (prologue, pipeline fill, epilogue) counts
+  // like 48 KB of weights. A cluster needs its CTAs on SMs of one GPC at the same time, so
+  // fewer clusters than SMs / size are resident together: the occupancy query says how many.
+  const int ttiles = div_up(T, BN), nk = W.K / kBlockK;
+  static int capacity[9] = {0};  // clusters of size s resident at once on this device
+  if (capacity[1] == 0) {
+    for (int sp = 1; sp <= 8; ++sp) {
+      cudaLaunchConfig_t q{};
+      q.gridDim = dim3(1, 1, sp);
+      q.blockDim = dim3(INT8 ? kUmmaThreadsInt8 : kUmmaThreads);
+      q.dynamicSmemBytes = S::kTotal;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 1;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = sp;
+      q.attrs = qa;
+      q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = std::max(1, sm_count() / sp / 2);  // a cautious guess
+      }
+      capacity[sp] = n;
+    }
+  }
+  const bool can_split = static_cast<size_t>(BN) * kTileM * 4 <= static_cast<size_t>(S::kStages) * S::kStageBytes;
+  const double elem = INT8 ? 1.0 : 2.0;
+  int rows = kTileM, splits = 1;
+  double best = 1e30;
+  for (int r = kTileM; r >= 64; r -= 8) {
+    for (int sp = 1; sp <= 8; ++sp) {
+      if (sp > 1 && (!can_split || nk / sp < 4)) break;
+      const long long clusters = static_cast<long long>(div_up(W.N, r)) * ttiles;
+      const double cost = static_cast<double>(div_up(clusters, static_cast<long long>(capacity[sp]))) *
+                          (static_cast<double>(r) * W.K * elem / sp + 48.0 * 1024 + (sp > 1 ? 8.0 * 1024 : 0.0));
+      if (cost < best - 1e-9) {
+        best = cost;
+        rows = r;
+        splits = sp;
+      }
+    }
+  }
+  const CUtensorMap mw = INT8 ? make_map(W.i8, 1, W.N, W.K, W.ld, rows, kBlockK, false, true)
+                              : make_map(W.f16, 2, W.N, W.K, W.ld, rows, kBlockK, true);
   const CUtensorMap mx = make_map(x, 2, T, W.K, ldx, BN, kBlockK, true);
-  // Split K across a cluster when the tiles alone would leave SMs idle.
-  const int tiles = div_up(W.N, kTileM) * div_up(T, BN), nk = W.K / kBlockK;
-  int splits = std::max(1, std::min({8, sm_count() / tiles, nk / 4}));
-  if (static_cast<size_t>(BN) * kTileM * 4 > static_cast<size_t>(S::kStages) * S::kStageBytes) splits = 1;
   static const int forced = [] {
     const char* e = std::getenv("RB200_GEMM_SPLITS");
     return e ? std::atoi(e) : 0;
   }();
-  if (forced > 0) splits = std::min({forced, 8, std::max(1, nk)});
+  if (forced > 0 && can_split) splits = std::min({forced, 8, std::max(1, nk)});
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(div_up(W.N, kTileM), div_up(T, BN), splits);
+  cfg.gridDim = dim3(div_up(W.N, rows), ttiles, splits);
   cfg.blockDim = dim3(INT8 ? kUmmaThreadsInt8 : kUmmaThreads);
   cfg.dynamicSmemBytes = S::kTotal;
   cfg.stream = st;
@@ -425,7 +470,7 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
   int* status = status_word();
   const float* scale = W.scale;
   const int N = W.N, K = W.K;
-  RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, mw, mx, scale, y, T, N, K, beta, status));
+  RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, mw, mx, scale, y, T, N, K, rows, beta, status));
 }
 
 template <bool INT8>
