@@ -119,6 +119,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const int kb_begin = static_cast<int>(static_cast<long long>(nk_all) * split / splits);
   const int nk = static_cast<int>(static_cast<long long>(nk_all) * (split + 1) / splits) - kb_begin;
 
+  const int pre = min(nk, NS);  // stages the first thread fills before the block is set up
   if (warp == 0 && lane == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(full_bar + 8 * s, 1);
@@ -132,6 +133,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     mbar_init(accum_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
+    // The first tiles leave for HBM before anything else is set up (TMEM, the block barrier):
+    // the barriers they complete on are this thread's own work above, and the ring starts empty.
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
+    for (int kb = 0; kb < pre; ++kb) {
+      mbar_expect_tx(full_bar + 8 * kb, stage_tx);
+      const int kx = (kb_begin + kb) * kBlockK;
+      if (INT8) tma_load_2d(sRaw + kb * S::kRawBytes, &map_w, kx, m0, full_bar + 8 * kb);
+      else tma_load_2d(sA + kb * S::kABytes, &map_w, kx, m0, full_bar + 8 * kb);
+      tma_load_2d(sB + kb * S::kBBytes, &map_x, kx, tok0, full_bar + 8 * kb);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -146,7 +158,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (warp == 0) {
     // ---- TMA producer ----
     if (elect_one()) {
-      for (int kb = 0; kb < nk && ok; ++kb) {
+      for (int kb = pre; kb < nk && ok; ++kb) {
         const int s = kb % NS;
         ok = mbar_wait(empty_bar + 8 * s, ((kb / NS) & 1) ^ 1);
         if (INT8 && ok) ok = mbar_wait(raw_free + 8 * s, ((kb / NS) & 1) ^ 1);
