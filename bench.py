@@ -192,7 +192,7 @@ def time_in_graph(fn, n_variants: int, iters: int = 20) -> float:
     return best
 
 
-def op_suite(peak_gbs: float, peak_tflops: float) -> dict:
+def op_suite(peak_gbs: float, peak_tflops: float, only=None, int8_case=None) -> dict:
     """Paged split-decode attention (32 sequences, contexts uniform in [1024, 4096], 32 q / 8 kv
     heads, D 128), weight-only int8 GEMV / GEMM on the Llama-3-8B projection shapes, and flash
     prefill (32 q / 4 kv heads, D 64, a 2048-token prompt as four 512-token chunks)."""
@@ -201,7 +201,20 @@ def op_suite(peak_gbs: float, peak_tflops: float) -> dict:
     from tests.workloads import c2_contexts
     out = {}
     dev = "cuda"
-    # -- decode attention --
+    want = lambda name: only is None or name in only  # --ops: a subset, for profiler captures of one kernel
+    if want("decode"):
+        out.update(_op_decode(ops, torch, np, c2_contexts, peak_gbs))
+    if want("int8"):
+        out["int8_linear"] = _op_int8(ops, torch, peak_gbs, int8_case)
+    if want("prefill"):
+        out.update(_op_prefill(ops, torch, peak_tflops))
+    if want("prefill_long"):
+        out.update(_op_prefill_long(ops, torch, peak_tflops))
+    return out
+
+
+def _op_decode(ops, torch, np, c2_contexts, peak_gbs):
+    out, dev = {}, "cuda"
     heads, kvh, D, bs, nblk = 32, 8, 128, 16, 16384
     ctxs = c2_contexts()
     rng = np.random.Generator(np.random.PCG64(2))
@@ -229,15 +242,22 @@ def op_suite(peak_gbs: float, peak_tflops: float) -> dict:
     out["paged_decode_attention"] = {"workload": "32 seqs, ctx U[1024,4096], 32q/8kv heads, D128, block 16, 16384-block pool",
                                      "us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / peak_gbs,
                                      "algorithmic_bytes": nbytes}
-    del pools
-    # -- int8 GEMV / GEMM and the fp16 GEMV --
-    lin = {}
+    return out
+
+
+def _op_int8(ops, torch, peak_gbs, case=None):
+    """case = (K, N, T) restricts the sweep to one point."""
+    lin, dev = {}, "cuda"
     for (K, N) in ((4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)):
+        if case and (K, N) != tuple(case[:2]):
+            continue
         R = max(2, int(300e6 // (N * K)) + 1)
         Ws = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev) for _ in range(R)]
         sc = torch.rand(N, device=dev) * 0.019 + 0.001
         scr = ops.gemv_scratch(N, K)
         for T in (1, 8, 64):
+            if case and T != case[2]:
+                continue
             x = torch.randn((T, K), device=dev).half()
             y = torch.zeros((T, N), device=dev)
             if T <= 8:
@@ -247,8 +267,11 @@ def op_suite(peak_gbs: float, peak_tflops: float) -> dict:
             b = N * K + 4 * N + 2 * T * K + 4 * T * N
             lin[f"{K}->{N} T={T}"] = {"us": ms * 1e3, "gbs": b / ms / 1e6, "frac_of_measured_hbm": b / ms / 1e6 / peak_gbs}
         del Ws
-    out["int8_linear"] = lin
-    # -- flash prefill --
+    return lin
+
+
+def _op_prefill(ops, torch, peak_tflops):
+    out, dev = {}, "cuda"
     heads, kvh, D, bs = 32, 4, 64, 16
     nblk = 2048 // bs
     kp = torch.randn((nblk, kvh, bs, D), device=dev, dtype=torch.float16)
@@ -272,8 +295,13 @@ def op_suite(peak_gbs: float, peak_tflops: float) -> dict:
     out["flash_prefill_attention"] = {"workload": "2048-token prompt as 4 x 512 chunks, 32q/4kv heads, D64, causal", "us": ms * 1e3,
                                       "tflops": flops / ms / 1e9, "frac_of_measured_bf16": flops / ms / 1e9 / peak_tflops,
                                       "tok_per_s": 2048 / (ms * 1e-3)}
+    return out
+
+
+def _op_prefill_long(ops, torch, peak_tflops):
     # the same kernel at the decode model's head layout: one 512-token chunk at the end of a
     # 16k-token context (long enough that the key loop, not the launch, sets the time)
+    out, dev, bs = {}, "cuda", 16
     heads, kvh, D, ctx = 32, 8, 128, 16384
     nblk = ctx // bs
     kp = torch.randn((nblk, kvh, bs, D), device=dev, dtype=torch.float16)
@@ -434,6 +462,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ops", action="store_true", help="skip the single-kernel measurements")
     ap.add_argument("--ops-only", action="store_true", help="only the single-kernel measurements (prints their JSON)")
+    ap.add_argument("--ops", default=None, help="with --ops-only: comma-separated subset of decode,int8,prefill,prefill_long")
+    ap.add_argument("--int8-case", default=None, help="with --ops-only: one int8 point as K,N,T (e.g. 4096,14336,1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else max(args.warmup, 1)
 
@@ -446,7 +476,9 @@ def main() -> None:
 
     if args.ops_only:
         peak, peak_tf, _ = measured_peaks()
-        print(json.dumps(op_suite(peak, peak_tf)), flush=True)
+        only = set(args.ops.split(",")) if args.ops else None
+        case = tuple(int(v) for v in args.int8_case.split(",")) if args.int8_case else None
+        print(json.dumps(op_suite(peak, peak_tf, only, case)), flush=True)
         return
 
     if args.impl == "reference":
