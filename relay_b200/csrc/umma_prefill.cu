@@ -75,6 +75,12 @@ struct PfSmem {
   static constexpr size_t kTotal = kQBytes + static_cast<size_t>(kStages) * 2 * kKBytes + kBarBytes + 1024;
 };
 
+// Programmatic dependent launch: this kernel may start while the one before it in the stream is
+// still running. Everything that kernel may have written (Q, the K/V pages) is read only after
+// pdl_wait(); the batch metadata (tiles, positions, block tables) was uploaded earlier.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Barrier for the 256 softmax threads only (the producer and MMA warps do not take part).
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
@@ -103,6 +109,7 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   const uint32_t q_ready = bars + 112;
   const uint32_t tmem_slot = bars + 120;
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int2 tile = tiles[blockIdx.x];
   const int t0 = tile.x, nrows = tile.y;
@@ -160,6 +167,7 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       return (table[key0 / bs] * kv_heads + kvh) * bs + key0 % bs;
     };
     int tab_cur = 0, tab_next = load_group(0);
+    pdl_wait();
     for (int j = 0; j < ntiles && ok; ++j) {
       const int s = j % NS;
       if (j % 4 == 0) {
@@ -261,6 +269,7 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const int head = h0 + (row >> 6);
     const int rr = min(row & 63, nrows - 1);
     const int p = pos0 + rr;
+    pdl_wait();
     {  // Q row -> fp16 -> swizzled A operand (each half converts half of the row's chunks)
       const float* src = q + static_cast<long long>(t0 + rr) * q_stride + head * D;
 #pragma unroll
@@ -438,8 +447,20 @@ void launch_umma_prefill_d(const AttnShape& s, const float* q, const TokenMeta& 
   const float scale_log2e = kLog2e / sqrtf(static_cast<float>(D));
   dim3 grid(n_tiles, s.heads / 2);
   count_launch();
-  kernel<<<grid, kPfThreads, S::kTotal, st>>>(mk, mv, kc, vc, q, m, tiles, out, s.heads, s.kv_heads, s.block_size, s.q_stride,
-                                              s.o_stride, scale_log2e, status_word());
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kPfThreads);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // set-up may overlap the previous kernel's tail
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int heads = s.heads, kv_heads = s.kv_heads, bs = s.block_size, q_stride = s.q_stride, o_stride = s.o_stride;
+  int* status = status_word();
+  RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, mk, mv, kc, vc, q, m, tiles, out, heads, kv_heads, bs, q_stride, o_stride, scale_log2e,
+                             status));
 }
 
 }  // namespace
