@@ -87,6 +87,78 @@ def prefill_pass(be, fb, cfg, bs, out) -> dict:
             "timing": "host clock around the forward calls, best of 2 after a warm-up"}
 
 
+def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
+    """Disaggregated prefill -> decode hop between GPU pairs (even rank = prefill side, odd rank =
+    decode side): the K/V pages of a 2048-token prompt cross NVLink layer by layer with NCCL
+    send/recv (rb200_send_kv_layer / rb200_recv_kv_layer). Measured twice: all layers back to back
+    (the hop's own bandwidth), and issued from the layer observer while the prompt is prefilled
+    (what the hop adds to the prefill time). Times are the host clock up to rb200_kv_hop_sync, max
+    over ranks."""
+    from relay_b200.backend import Backend
+    uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+    if rank == 0:
+        uid.copy_(torch.frombuffer(bytearray(Backend.nccl_unique_id()), dtype=torch.uint8))
+    dist.broadcast(uid, src=0)
+    be.nccl_init(bytes(uid.cpu().numpy().tobytes()), world, rank)
+    per = PREFILL_PROMPT // bs
+    table = [int(b) for b in fb.tables[: int(fb.table_len[0])][:per]]
+    peer = rank ^ 1
+    paired = peer < world
+    sender = rank % 2 == 0
+
+    def mx(x):
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sync_all():
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    block_bytes = 2 * be.kv_block_bytes()  # K and V
+    raw = float("inf")
+    for _ in range(3):
+        sync_all()
+        t0 = time.perf_counter()
+        if paired:
+            for layer in range(cfg.layers):
+                (be.send_kv_layer if sender else be.recv_kv_layer)(peer, layer, table)
+            be.kv_hop_sync(30000)
+        raw = min(raw, mx(time.perf_counter() - t0))
+    hop_bytes = block_bytes * per * cfg.layers
+
+    rng = np.random.Generator(np.random.PCG64(11))
+    toks = rng.integers(0, cfg.vocab, PREFILL_PROMPT)
+    chunks = [(c, flatten(ForwardBatch([SeqChunk([int(t) for t in toks[c:c + PREFILL_CHUNK]], c, table,
+                                                 want_logits=(c + PREFILL_CHUNK == PREFILL_PROMPT))])))
+              for c in range(0, PREFILL_PROMPT, PREFILL_CHUNK)]
+    times = {}
+    for mode in ("plain", "streamed"):
+        best = float("inf")
+        for _ in range(3):
+            sync_all()
+            t0 = time.perf_counter()
+            if sender or not paired:
+                for c, ch in chunks:
+                    blocks = table[c // bs:(c + PREFILL_CHUNK) // bs]
+                    obs = (lambda layer, blocks=blocks: be.send_kv_layer(peer, layer, blocks)) if (mode == "streamed" and paired) else None
+                    be.forward_flat(ch, observer=obs, out=out)
+            elif mode == "streamed":
+                for c, ch in chunks:
+                    for layer in range(cfg.layers):
+                        be.recv_kv_layer(peer, layer, table[c // bs:(c + PREFILL_CHUNK) // bs])
+            if mode == "streamed" and paired:
+                be.kv_hop_sync(30000)
+            best = min(best, mx(time.perf_counter() - t0))
+        times[mode] = best
+    be.nccl_finalize()
+    return {"workload": f"K/V of a {PREFILL_PROMPT}-token prompt, {cfg.layers} layers, {hop_bytes / 1e6:.0f} MB per pair, "
+                        f"{world // 2} pair(s) at once (even rank -> odd rank)",
+            "bytes_per_pair": hop_bytes, "back_to_back_ms": raw * 1e3, "gbs_per_pair": hop_bytes / raw / 1e9,
+            "prefill_ms": times["plain"] * 1e3, "prefill_streaming_kv_ms": times["streamed"] * 1e3,
+            "transport": "NCCL send/recv over NVLink, page gather/scatter kernels on the copy stream"}
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
 
@@ -467,6 +539,8 @@ def gpu_arm(args) -> dict:
     }
     if world == 1 and ctx >= PREFILL_PROMPT:
         line["prefill"] = prefill_pass(be, fb, cfg, bs, out)
+    if world >= 2 and ctx >= PREFILL_PROMPT and not args.no_kv_hop:
+        line["kv_hop"] = kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch)
     if world == 1 and not args.no_ops:
         del be
         torch.cuda.empty_cache()
@@ -492,6 +566,7 @@ def main() -> None:
     ap.add_argument("--cpu-seqs", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ops", action="store_true", help="skip the single-kernel measurements")
+    ap.add_argument("--no-kv-hop", action="store_true", help="N >= 2: skip the prefill -> decode K/V hop measurement")
     ap.add_argument("--ops-only", action="store_true", help="only the single-kernel measurements (prints their JSON)")
     ap.add_argument("--ops", default=None, help="with --ops-only: comma-separated subset of decode,int8,prefill,prefill_long")
     ap.add_argument("--int8-case", default=None, help="with --ops-only: one int8 point as K,N,T (e.g. 4096,14336,1)")
