@@ -266,9 +266,12 @@ int rb200_reference_attention(const rb200_attn_shape* s, const float* q, const r
 
 /* Weight-only int8 GEMV for 1..8 tokens (replaces gemv_int8_kernel,
  * engine/src/cuda_kernels.cuh:378-430): y[T,N] = scale[n] * sum_k Wq[n,k] x[t,k] + beta*y.
- * Wq int8 [N][ldw], x fp16 [T][ldx], y fp32 [T][N]; K, ldw, ldx multiples of 32.
- * `scratch` (rb200_gemv_scratch_bytes) holds split-K partials and must be zero before its
- * first use; the kernel leaves it zero again. */
+ * Wq int8 [N][ldw], x fp16 [T][ldx], y fp32 [T][N]; K a multiple of 64, ldw and ldx
+ * multiples of 16 and 8 elements. `scratch` (rb200_gemv_scratch_bytes, 16-byte aligned)
+ * holds two things: split-K partials of the register kernel, which must be zero before
+ * the first use and are left zero again, and the activations rewritten as int8 digits
+ * for the integer tensor-core kernel (no initial state). Calls that share a scratch
+ * buffer must be ordered on one stream. */
 size_t rb200_gemv_scratch_bytes(int N, int K);
 int rb200_gemv_int8(const int8_t* wq, const float* scale, const void* x, float* y, int T, int K, int N, int ldw,
                     int ldx, float beta, void* scratch, size_t scratch_bytes, void* stream);
@@ -278,9 +281,12 @@ int rb200_gemv_f16(const void* w, const void* x, float* y, int T, int K, int N, 
                    void* scratch, size_t scratch_bytes, void* stream);
 
 /* y[T,N] = x[T,K] W[N,K]^T (+ beta*y) on tensor cores for any T: fp16 weights (replaces
- * cublasGemmEx, engine/src/cuda_backend.cu:724-730) or int8 weights dequantised in the
- * main loop (replaces dequant_int8_kernel + cuBLAS, engine/src/cuda_kernels.cuh:432-436,
- * engine/src/cuda_backend.cu:719-721). Exactly one of w_f16 / w_i8 is non-NULL. */
+ * cublasGemmEx, engine/src/cuda_backend.cu:724-730) or int8 weights (replaces
+ * dequant_int8_kernel + cuBLAS, engine/src/cuda_kernels.cuh:432-436,
+ * engine/src/cuda_backend.cu:719-721): multiplied as integers against int8 digits of the
+ * activations for few tokens, widened to fp16 inside the main loop for more. Exactly one
+ * of w_f16 / w_i8 is non-NULL. The int8 few-token path takes a temporary buffer from the
+ * stream's memory pool (cudaMallocAsync / cudaFreeAsync on `stream`). */
 int rb200_gemm(const void* w_f16, const int8_t* w_i8, const float* scale, const void* x, float* y, int T, int K,
                int N, int ldw, int ldx, float beta, void* stream);
 

@@ -1,7 +1,14 @@
 // The linear layers: y[T,N] = x[T,K] W[N,K]^T (+ beta*y), W fp16 or weight-only int8 with
 // one fp32 scale per output row, x fp16, y fp32.
 //
-//  * gemv_kernel (T <= 8) — replaces gemv_int8_kernel (engine/src/cuda_kernels.cuh:378-430).
+// Dispatch (launch_linear): fp16 weights go to the tcgen05 kernel of umma_gemm.cu for every
+// token count; int8 weights go to the integer tensor-core kernel of umma_i8_gemm.cu up to 16
+// tokens (32 on large matrices) and to umma_gemm.cu's int8 instantiation (widening into TMEM)
+// above. The two kernels of this file are what remains for operands those cannot take:
+//
+//  * gemv_kernel (T <= 8) — the register-path form of gemv_int8_kernel
+//    (engine/src/cuda_kernels.cuh:378-430), used for matrices under 2 MB, callers without
+//    scratch for the digit buffer, and pointers TMA cannot address.
 //    Bound by weight bandwidth: every weight byte is read from HBM exactly once, straight
 //    into registers with 256-bit loads (the four lanes of a quad cover a whole 128-byte line
 //    of a row), int8 spliced under an fp16 exponent with two byte permutes (the constant
@@ -14,7 +21,7 @@
 //    fp16 weights with up to 8 tokens go to the tcgen05 kernel of umma_gemm.cu (a 16-token
 //    tile): TMA streams them faster than per-lane loads do. This kernel keeps an fp16
 //    instantiation for operands TMA cannot address.
-//  * gemm_kernel (T > 8) — replaces dequant_int8_kernel + cuBLAS (engine/src/cuda_kernels.cuh:432-436,
+//  * gemm_kernel (T > 8, mma.sync; RB200_GEMM=mma_sync forces it) — the legacy-tile form of dequant_int8_kernel + cuBLAS (engine/src/cuda_kernels.cuh:432-436,
 //    engine/src/cuda_backend.cu:719-721) and cublasGemmEx for fp16 weights: weights on the M
 //    axis, tokens on N, int8 dequantised on its way into shared memory (the fp16 copy of the
 //    matrix is never materialised in HBM), scale and residual applied in the epilogue.
@@ -454,7 +461,7 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
   // 16-byte loads, so the few-token case uses the tcgen05 kernel with a 16-token tile.
   if (W.f16 && !gemm_forced_legacy() && umma_gemm_usable(W, x, ldx)) return launch_umma_gemm(W, x, ldx, y, T, beta, st);
   if (W.i8 && !gemm_forced_legacy() && i8_digits_preferred(W) && umma_i8_usable(W, x, ldx, T) && scratch != nullptr &&
-      scratch_bytes >= gemv_partials_bytes(W.N, W.K) + i8_digits_bytes(T, W.K))
+      (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && scratch_bytes >= gemv_partials_bytes(W.N, W.K) + i8_digits_bytes(T, W.K))
     return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + gemv_partials_bytes(W.N, W.K), st);
   unsigned* counters = static_cast<unsigned*>(scratch);
   float* partials = scratch ? reinterpret_cast<float*>(static_cast<char*>(scratch) + gemv_counter_bytes(W.N)) : nullptr;
@@ -484,7 +491,7 @@ void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T,
   const bool digits = T <= 16 || (T <= 32 && static_cast<long long>(W.N) * W.K >= (32LL << 20));
   if (W.i8 && digits && !gemm_forced_legacy() && umma_i8_usable(W, x, ldx, T)) {
     const size_t off = gemv_partials_bytes(W.N, W.K), need = i8_digits_bytes(T, W.K);
-    if (scratch != nullptr && scratch_bytes >= off + need) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + off, st);
+    if (scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && scratch_bytes >= off + need) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + off, st);
     void* tmp = nullptr;  // no caller buffer: stream-ordered allocation, released behind the kernels
     RB_CUDA(cudaMallocAsync(&tmp, need, st));
     launch_umma_i8(W, x, ldx, y, T, beta, tmp, st);
