@@ -7,19 +7,20 @@
 // of TWO query heads that share a KV head: 128 rows on the M axis of tcgen05.mma, so every
 // K/V tile fetched is used by both heads. Per 128-key tile:
 //   S = Q K^T    A = Q (fp16, shared memory, K-major, 128-byte swizzle), B = the K tile
-//                (K-major), D = S in TMEM (128 lanes x 128 columns, fp32), double-buffered so
-//                that the scores of tile j + 1 are computed while tile j is in softmax;
+//                (K-major), D = S in TMEM (128 lanes x 128 columns, fp32). One buffer: the
+//                softmax warps release it as soon as they hold the scores in registers, and
+//                the product for tile j + 1 runs under the exponentials of tile j;
 //   softmax      eight warps, two threads per row, one per 64-key half of the tile, each with
 //                its own running (reference max, sum): tcgen05.ld the half row of S, scale,
 //                causal mask (only on tiles that reach the diagonal), P = exp2(.) as fp16
-//                written back with tcgen05.st over the thread's own S columns;
+//                written with tcgen05.st into one of two P buffers in TMEM;
 //   O_h += P_h V_h  one product per half: A = P_h read from TMEM, B = the V tile's 64 keys as
 //                they sit in shared memory ([key][d] = MN-major), D = O_h accumulating in TMEM.
 // O never leaves TMEM inside the loop. The exponent's reference max only moves when a row's
 // max has grown by more than 2^8 (any lane of the warp), and only then the warp waits for the
 // previous product and rescales its O_h in TMEM; P stays below 2^8 and exact in the final
 // quotient. So the softmax warps go from tile j straight to tile j + 1 while the tensor core
-// does P V of tile j and Q K^T of tile j + 2.
+// does P V of tile j and Q K^T of tile j + 2, and no product waits for the other's operands.
 // The two halves of a row are merged once, at the end (log-sum-exp), through shared memory.
 // Warp roles: warps 0, 1 and 3 fetch the K and V tiles (one TMA box per 16-key page and 64-wide
 // slice of the head, addressed through the block table), warp 2 issues the MMAs and owns
@@ -93,9 +94,10 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   constexpr int NS = S::kStages;
   // how far (log2) a row's max may outgrow the exponent reference before O is rescaled
   constexpr float kGrow = 8.f;
-  // TMEM columns: S of even tiles 0..127, S of odd tiles 128..255 (each half's P overwrites the
-  // first 32 of its 64 S columns), then the two halves' running O (keys 0-63 and 64-127 of
-  // every tile), D columns each.
+  // TMEM columns: S 0..127 (single buffer: it is free again as soon as the softmax warps hold
+  // it in registers), P of even tiles 128..191 and of odd tiles 192..255 (fp16 pairs: 32
+  // columns per half), then the two halves' running O (keys 0-63 and 64-127 of every tile),
+  // D columns each.
   constexpr uint32_t kTmemCols = 512;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -104,7 +106,7 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   const uint32_t sK = sQ + S::kQBytes;                 // NS stages of [K tile][V tile]
   const uint32_t bars = sK + NS * 2 * S::kKBytes;
   const uint32_t kv_full = bars, kv_empty = bars + 32;     // NS (<= 4) x 8 bytes each
-  const uint32_t s_ready = bars + 64;                      // one per S buffer
+  const uint32_t s_ready = bars + 64, s_free = bars + 72;  // S written by the MMA / read into registers by all 8 warps
   const uint32_t p_ready = bars + 80, pv_done = bars + 96;  // one per half
   const uint32_t q_ready = bars + 112;
   const uint32_t tmem_slot = bars + 120;
@@ -125,8 +127,9 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       mbar_init(kv_full + 8 * s, 1);  // the loader's expect-tx arrival (or its plain arrival after a gathered tile)
       mbar_init(kv_empty + 8 * s, 1);
     }
+    mbar_init(s_ready, 1);
+    mbar_init(s_free, 8);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(s_ready + 8 * s, 1);
       mbar_init(p_ready + 8 * s, 4);
       mbar_init(pv_done + 8 * s, 1);
     }
@@ -212,37 +215,37 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     if (elect_one()) {
       constexpr uint32_t idesc_qk = umma_idesc(kRows, kKeys);
       constexpr uint32_t idesc_pv = umma_idesc(kRows, D) | (1u << 16);  // B (V) is MN-major
-      // S of tile j goes to buffer j % 2, so the scores of tile j + 1 are computed while the
-      // softmax warps still work on tile j.
+      // Q K^T of tile j + 1 is issued as soon as the softmax warps have taken S of tile j into
+      // registers, so it runs under their exponentials; P V of tile j follows when P arrives
+      // and runs under the softmax of tile j + 1. Neither product waits for the other's data.
       auto issue_qk = [&](int j) {
         const uint32_t kt = sK + (j % NS) * 2 * S::kKBytes;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k / 4) * (kRows * 128) + (k % 4) * 32;  // 64-wide atom, then 32 bytes per 16 dims
-          umma_f16(tmem_base + (j & 1) * kKeys, smem_desc_sw128(sQ + off), smem_desc_sw128(kt + off), idesc_qk, k != 0);
+          umma_f16(tmem_base, smem_desc_sw128(sQ + off), smem_desc_sw128(kt + off), idesc_qk, k != 0);
         }
-        umma_commit(s_ready + 8 * (j & 1));
+        umma_commit(s_ready);
       };
       ok = mbar_wait(q_ready, 0) && mbar_wait(kv_full, 0);
       if (ok) {
         tc_fence_after();
         issue_qk(0);
       }
-      if (ok && ntiles > 1) {
-        ok = mbar_wait(kv_full + 8 * (1 % NS), (1 / NS) & 1);
-        if (ok) {
-          tc_fence_after();
-          issue_qk(1);
-        }
-      }
       for (int j = 0; j < ntiles && ok; ++j) {
+        if (j + 1 < ntiles) {
+          ok = mbar_wait(s_free, j & 1) && mbar_wait(kv_full + 8 * ((j + 1) % NS), ((j + 1) / NS) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_qk(j + 1);
+        }
         const uint32_t vt = sK + (j % NS) * 2 * S::kKBytes + S::kKBytes;
 #pragma unroll 1
         for (int h = 0; h < 2 && ok; ++h) {  // keys 0-63, then 64-127: separate products, separate softmax states
           ok = mbar_wait(p_ready + 8 * h, j & 1);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t pa = tmem_base + (j & 1) * kKeys + h * 64;  // P_h: 64 halves = 32 columns per row
+          const uint32_t pa = tmem_base + kKeys + (j & 1) * 64 + h * 32;  // P_h: 64 halves = 32 columns per row
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_f16_ta(tmem_base + 2 * kKeys + h * D, pa + 8 * k, smem_desc_mn_sw128(vt + (h * 4 + k) * 2048, kKeys * 128),
@@ -251,12 +254,6 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         }
         if (!ok) break;
         umma_commit(kv_empty + 8 * (j % NS));
-        if (j + 2 < ntiles) {  // both halves have read S of tile j: its buffer takes tile j + 2
-          ok = mbar_wait(kv_full + 8 * ((j + 2) % NS), ((j + 2) / NS) & 1);
-          if (!ok) break;
-          tc_fence_after();
-          issue_qk(j + 2);
-        }
       }
       if (!ok) atomicExch(status, 12);
     }
@@ -292,15 +289,19 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t tmem_o = tmem_base + 2 * kKeys + half * D + lane_sel;
     for (int j = 0; j < ntiles && ok; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(s_ready + 8 * (j & 1), (j >> 1) & 1));
+      ok = __all_sync(0xffffffffu, mbar_wait(s_ready, j & 1));
       if (!ok) break;
       tc_fence_after();
       const int key0 = j * kKeys + half * 64;
-      const uint32_t tmem_s = tmem_base + (j & 1) * kKeys + lane_sel + half * 64;
+      const uint32_t tmem_s = tmem_base + lane_sel + half * 64;
+      const uint32_t tmem_p = tmem_base + kKeys + (j & 1) * 64 + half * 32 + lane_sel;
       uint32_t sv[64];
       tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
       tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
       tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);  // the scores are in registers: S may take the next tile
       const bool diag = j * kKeys + kKeys - 1 > pos0;  // some row of the tile does not see every key
       if (diag) {
 #pragma unroll
@@ -359,12 +360,13 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       // long ago). The MMA warp looks at the halves in turn; without this a half could arrive
       // for two tiles while the MMA warp waits for the other half, and a phase that completes
       // twice unobserved looks incomplete to a parity wait. It also keeps the four warps that
-      // share p_ready (four arrivals per tile) within one tile of each other.
+      // share p_ready (four arrivals per tile) within one tile of each other, and it means the
+      // product of tile j - 2, the last reader of this tile's P buffer, is done.
       if (j > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(pv_done + 8 * half, (j - 1) & 1));
         if (!ok) break;
       }
-      tmem_st32(tmem_s, pk);  // P over this thread's first 32 S columns
+      tmem_st32(tmem_p, pk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
