@@ -314,18 +314,21 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       uint32_t pk[32];
       float sum = 0.f, mx = 0.f;
       auto exp_pass = [&](float neg_m) {
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        // packed fp32 pairs (fma.rn.f32x2 / add.f32x2) halve the instruction count of the scale and the sum
+        float2 sum2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        const float2 sc2 = make_float2(scale_log2e, scale_log2e), nm2 = make_float2(neg_m, neg_m);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float s0 = __uint_as_float(sv[2 * i]), s1 = __uint_as_float(sv[2 * i + 1]);
-          const float a = ex2(fmaf(s0, scale_log2e, neg_m));
-          const float b = ex2(fmaf(s1, scale_log2e, neg_m));
-          mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(s0, s1));
-          sum4[i & 3] += a + b;
-          pk[i] = pack_half2(a, b);
+          const float2 sp = make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1]));
+          const float2 x = __ffma2_rn(sp, sc2, nm2);
+          const float2 e = make_float2(ex2(x.x), ex2(x.y));
+          mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(sp.x, sp.y));
+          sum2[i & 3] = __fadd2_rn(sum2[i & 3], e);
+          pk[i] = pack_half2(e.x, e.y);
         }
-        sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        const float2 st = __fadd2_rn(__fadd2_rn(sum2[0], sum2[1]), __fadd2_rn(sum2[2], sum2[3]));
+        sum = st.x + st.y;
         mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       };
       // rows that see nothing yet keep m_ref = -inf; all their scores are masked to -inf
