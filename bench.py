@@ -293,10 +293,12 @@ def time_in_graph(fn, n_variants: int, iters: int = 20) -> float:
     return best
 
 
-def op_suite(peak_gbs: float, peak_tflops: float, only=None, int8_case=None) -> dict:
+def op_suite(peak_gbs: float, peak_tflops: float, only=None, int8_case=None, cpu: bool = False) -> dict:
     """Paged split-decode attention (32 sequences, contexts uniform in [1024, 4096], 32 q / 8 kv
     heads, D 128), weight-only int8 GEMV / GEMM on the Llama-3-8B projection shapes, and flash
-    prefill (32 q / 4 kv heads, D 64, a 2048-token prompt as four 512-token chunks)."""
+    prefill (32 q / 4 kv heads, D 64, a 2048-token prompt as four 512-token chunks). With `cpu`
+    each entry also carries `cpu_us`: the CPU restatement of the same operator (the oracle's
+    OpenMP loops, fp32) timed once on this host's cores, a reported baseline only."""
     import torch
     from relay_b200 import ops
     from tests.workloads import c2_contexts
@@ -304,17 +306,17 @@ def op_suite(peak_gbs: float, peak_tflops: float, only=None, int8_case=None) -> 
     dev = "cuda"
     want = lambda name: only is None or name in only  # --ops: a subset, for profiler captures of one kernel
     if want("decode"):
-        out.update(_op_decode(ops, torch, np, c2_contexts, peak_gbs))
+        out.update(_op_decode(ops, torch, np, c2_contexts, peak_gbs, cpu))
     if want("int8"):
-        out["int8_linear"] = _op_int8(ops, torch, peak_gbs, int8_case)
+        out["int8_linear"] = _op_int8(ops, torch, peak_gbs, int8_case, cpu)
     if want("prefill"):
-        out.update(_op_prefill(ops, torch, peak_tflops))
+        out.update(_op_prefill(ops, torch, peak_tflops, cpu))
     if want("prefill_long"):
         out.update(_op_prefill_long(ops, torch, peak_tflops))
     return out
 
 
-def _op_decode(ops, torch, np, c2_contexts, peak_gbs):
+def _op_decode(ops, torch, np, c2_contexts, peak_gbs, cpu=False):
     out, dev = {}, "cuda"
     heads, kvh, D, bs, nblk = 32, 8, 128, 16, 16384
     ctxs = c2_contexts()
@@ -343,10 +345,20 @@ def _op_decode(ops, torch, np, c2_contexts, peak_gbs):
     out["paged_decode_attention"] = {"workload": "32 seqs, ctx U[1024,4096], 32q/8kv heads, D128, block 16, 16384-block pool",
                                      "us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / peak_gbs,
                                      "algorithmic_bytes": nbytes}
+    if cpu:
+        from oracle import oracle
+        ids = sorted(set(tables))
+        remap = {b: i for i, b in enumerate(ids)}
+        idx = torch.tensor(ids, device=dev)
+        kh, vh = pools[0][0][idx].float().cpu().numpy(), pools[0][1][idx].float().cpu().numpy()
+        t0 = time.perf_counter()
+        oracle.attention(q.cpu().numpy(), q.shape[1], np.asarray(pos, np.int32), np.asarray(seq, np.int32),
+                         np.asarray(toff, np.int32), np.asarray([remap[b] for b in tables], np.int32), kh, vh, heads, kvh, D, bs)
+        out["paged_decode_attention"].update(cpu_us=(time.perf_counter() - t0) * 1e6, cpu_cores=os.cpu_count())
     return out
 
 
-def _op_int8(ops, torch, peak_gbs, case=None):
+def _op_int8(ops, torch, peak_gbs, case=None, cpu=False):
     """case = (K, N, T) restricts the sweep to one point."""
     lin, dev = {}, "cuda"
     for (K, N) in ((4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)):
@@ -356,7 +368,7 @@ def _op_int8(ops, torch, peak_gbs, case=None):
         Ws = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev) for _ in range(R)]
         sc = torch.rand(N, device=dev) * 0.019 + 0.001
         scr = ops.gemv_scratch(N, K)
-        for T in (1, 8, 64):
+        for T in (1, 2, 4, 8, 64):
             if case and T != case[2]:
                 continue
             x = torch.randn((T, K), device=dev).half()
@@ -367,11 +379,17 @@ def _op_int8(ops, torch, peak_gbs, case=None):
                 ms = time_in_graph(lambda i: ops.gemm(Ws[i], x, y, 0.0, sc), R)
             b = N * K + 4 * N + 2 * T * K + 4 * T * N
             lin[f"{K}->{N} T={T}"] = {"us": ms * 1e3, "gbs": b / ms / 1e6, "frac_of_measured_hbm": b / ms / 1e6 / peak_gbs}
+            if cpu and T in (1, 64):
+                from oracle import oracle
+                wh, sh, xh = Ws[0].cpu().numpy(), sc.cpu().numpy(), x.float().cpu().numpy()
+                t0 = time.perf_counter()
+                oracle.gemv_int8(wh, sh, xh)
+                lin[f"{K}->{N} T={T}"].update(cpu_us=(time.perf_counter() - t0) * 1e6, cpu_cores=os.cpu_count())
         del Ws
     return lin
 
 
-def _op_prefill(ops, torch, peak_tflops):
+def _op_prefill(ops, torch, peak_tflops, cpu=False):
     out, dev = {}, "cuda"
     heads, kvh, D, bs = 32, 4, 64, 16
     nblk = 2048 // bs
@@ -396,6 +414,15 @@ def _op_prefill(ops, torch, peak_tflops):
     out["flash_prefill_attention"] = {"workload": "2048-token prompt as 4 x 512 chunks, 32q/4kv heads, D64, causal", "us": ms * 1e3,
                                       "tflops": flops / ms / 1e9, "frac_of_measured_bf16": flops / ms / 1e9 / peak_tflops,
                                       "tok_per_s": 2048 / (ms * 1e-3)}
+    if cpu:
+        from oracle import oracle
+        kh, vh = kp.float().cpu().numpy(), vp.float().cpu().numpy()
+        qh = q.cpu().numpy()
+        t0 = time.perf_counter()
+        for c in range(4):  # the same four chunks (the queries repeat; the CPU time does not depend on their values)
+            oracle.attention(qh, qh.shape[1], np.arange(512 * c, 512 * (c + 1), dtype=np.int32), np.zeros(512, np.int32),
+                             np.zeros(1, np.int32), np.arange(nblk, dtype=np.int32), kh, vh, heads, kvh, D, bs)
+        out["flash_prefill_attention"].update(cpu_us=(time.perf_counter() - t0) * 1e6, cpu_cores=os.cpu_count())
     return out
 
 
@@ -544,7 +571,7 @@ def gpu_arm(args) -> dict:
     if world == 1 and not args.no_ops:
         del be
         torch.cuda.empty_cache()
-        line["ops"] = op_suite(peak, peak_tf)
+        line["ops"] = op_suite(peak, peak_tf, cpu=not args.no_cpu_baseline)
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:
@@ -569,6 +596,7 @@ def main() -> None:
     ap.add_argument("--no-kv-hop", action="store_true", help="N >= 2: skip the prefill -> decode K/V hop measurement")
     ap.add_argument("--ops-only", action="store_true", help="only the single-kernel measurements (prints their JSON)")
     ap.add_argument("--ops", default=None, help="with --ops-only: comma-separated subset of decode,int8,prefill,prefill_long")
+    ap.add_argument("--ops-cpu", action="store_true", help="with --ops-only: also time the CPU restatement of each operator")
     ap.add_argument("--int8-case", default=None, help="with --ops-only: one int8 point as K,N,T (e.g. 4096,14336,1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else max(args.warmup, 1)
@@ -584,7 +612,7 @@ def main() -> None:
         peak, peak_tf, _ = measured_peaks()
         only = set(args.ops.split(",")) if args.ops else None
         case = tuple(int(v) for v in args.int8_case.split(",")) if args.int8_case else None
-        print(json.dumps(op_suite(peak, peak_tf, only, case)), flush=True)
+        print(json.dumps(op_suite(peak, peak_tf, only, case, cpu=args.ops_cpu)), flush=True)
         return
 
     if args.impl == "reference":

@@ -352,6 +352,38 @@ def test_gemm_matches_oracle(ops, K, N, int8):
         assert row_err(y.cpu().numpy(), want) < LINEAR_TOL
 
 
+@pytest.mark.parametrize("T", [1, 5, 16])
+def test_int8_linear_with_outlier_zero_and_tiny_activation_rows(ops, T):
+    # The int8 few-token kernel rewrites each activation row as fixed-point digits relative to
+    # the row's largest magnitude: rows with one huge outlier, all-zero rows, rows of fp16
+    # subnormals and rows at the fp16 maximum must all stay within the linear tolerance.
+    K, N = 4096, 4096
+    rng = np.random.Generator(np.random.PCG64(5 + T))
+    x = round_f16(rng.standard_normal((T, K)))
+    x[0] = 0.0
+    if T > 1:
+        x[1] = round_f16(rng.standard_normal(K) * 1e-3)
+        x[1, 17] = -60000.0
+        x[2] = round_f16(rng.standard_normal(K) * 3e-7)  # fp16 subnormals
+        x[3] = np.where(rng.random(K) < 0.5, 65504.0, -65504.0) * (rng.random(K) < 0.01)
+        x[4, :] = round_f16(rng.standard_normal(K))
+        x[4, K - 1] = 2048.0
+    wq = rng.integers(-127, 128, (N, K)).astype(np.int8)
+    scale = rng.uniform(0.001, 0.02, N).astype(np.float32)
+    want = oracle.gemv_int8(wq, scale, x)
+    y = torch.zeros((T, N), device="cuda")
+    if T <= 8:
+        ops.gemv_int8(dev(wq), dev(scale), dev(x, torch.float16), y, 0.0, ops.gemv_scratch(N, K))
+    else:
+        ops.gemm(dev(wq), dev(x, torch.float16), y, 0.0, dev(scale))
+    torch.cuda.synchronize()
+    assert ops.gemm_status() == 0
+    got = y.cpu().numpy()
+    assert np.array_equal(got[0], np.zeros(N, np.float32))  # a zero row gives exact zeros
+    assert np.isfinite(got).all()
+    assert row_err(got[1:], want[1:]) < LINEAR_TOL if T > 1 else True
+
+
 def test_gemv_and_gemm_agree_and_are_deterministic(ops):
     x, y0, w, scale = linear_case(99, 8, 4096, 4096, True)
     a = ops.gemv_int8(dev(w), dev(scale), dev(x, torch.float16), torch.zeros((8, 4096), device="cuda"))
