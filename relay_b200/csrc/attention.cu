@@ -109,6 +109,8 @@ decode_split_kernel(const float* __restrict__ q, TokenMeta m, const int* __restr
   __shared__ int s_table[kDecodeSlice];   // block ids covering the slice: slice / block_size <= 512 entries
   __shared__ float s_m[kDecWarps][16], s_l[kDecWarps][16];
 
+  pdl_trigger();
+  pdl_wait();
   const int di = blockIdx.x, kvh = blockIdx.y, part = blockIdx.z;
   const int tok = decode_tokens[di];
   const int ctx = m.pos[tok] + 1;
@@ -337,6 +339,8 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
                                     const int* __restrict__ decode_tokens, const int* __restrict__ pos,
                                     __half* __restrict__ out, int heads, int D, int o_stride, int max_parts,
                                     int n_pairs, int slice) {
+  pdl_trigger();
+  pdl_wait();
   const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (pair >= n_pairs) return;
   const int lane = threadIdx.x & 31;
@@ -625,9 +629,8 @@ void launch_decode_t(const AttnShape& s, const float* q, const TokenMeta& m, con
   const float scale_log2e = kLog2e / sqrtf(static_cast<float>(D));
   dim3 grid(n_decode, s.kv_heads, parts);
   count_launch();
-  kernel<<<grid, kDecWarps * 32, decode_smem_bytes<D>(), st>>>(q, m, decode_tokens, kc, vc, part_o, part_ml, out, s.heads,
-                                                               s.kv_heads, s.block_size, shift_of(s.block_size),
-                                                               s.q_stride, s.o_stride, scale_log2e, parts, slice);
+  launch_pdl(kernel, grid, dim3(kDecWarps * 32), decode_smem_bytes<D>(), st, q, m, decode_tokens, kc, vc, part_o, part_ml, out,
+             s.heads, s.kv_heads, s.block_size, shift_of(s.block_size), s.q_stride, s.o_stride, scale_log2e, parts, slice);
 }
 
 template <int D>
@@ -703,8 +706,8 @@ void launch_decode_attention(const AttnShape& s, const float* q, const TokenMeta
   if (parts > 1) {
     const int pairs = n_decode * s.heads;
     count_launch();
-    decode_merge_kernel<<<div_up(pairs, 4), 128, 0, st>>>(part_o, part_ml, decode_tokens, m.pos, out, s.heads, s.D,
-                                                          s.o_stride, parts, pairs, slice);
+    launch_pdl(decode_merge_kernel, dim3(div_up(pairs, 4)), dim3(128), 0, st, part_o, part_ml, decode_tokens, m.pos, out,
+               s.heads, s.D, s.o_stride, parts, pairs, slice);
   }
 }
 

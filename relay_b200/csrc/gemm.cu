@@ -166,6 +166,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32)
 gemv_kernel(const void* __restrict__ wv, const float* __restrict__ scale, const __half* __restrict__ x,
             float* __restrict__ y, int T, int K, int N, int ldw, int ldx, float beta, int chunk, int splits,
             unsigned* __restrict__ counters, float* __restrict__ partials) {
+  pdl_trigger();
+  pdl_wait();
   // x[8][chunk] halves, each row padded (16 bytes for int8 weights, 64 for fp16) so that the
   // token rows a quarter-warp reads with 16-byte loads fall into different bank groups.
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -474,11 +476,11 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
   dim3 grid(p.row_blocks, p.splits);
   count_launch();
   if (W.i8)
-    gemv_kernel<true><<<grid, kGemvWarps * 32, smem, st>>>(W.i8, W.scale, x, y, T, W.K, W.N, W.ld, ldx, beta, p.chunk,
-                                                           p.splits, counters, partials);
+    launch_pdl(gemv_kernel<true>, grid, dim3(kGemvWarps * 32), smem, st, W.i8, W.scale, x, y, T, W.K, W.N, W.ld, ldx, beta,
+               p.chunk, p.splits, counters, partials);
   else
-    gemv_kernel<false><<<grid, kGemvWarps * 32, smem, st>>>(W.f16, nullptr, x, y, T, W.K, W.N, W.ld, ldx, beta, p.chunk,
-                                                            p.splits, counters, partials);
+    launch_pdl(gemv_kernel<false>, grid, dim3(kGemvWarps * 32), smem, st, W.f16, static_cast<const float*>(nullptr), x, y, T, W.K,
+               W.N, W.ld, ldx, beta, p.chunk, p.splits, counters, partials);
 }
 
 void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st, void* scratch,

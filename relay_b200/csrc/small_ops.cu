@@ -23,6 +23,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // x[t, :] = float(table[tokens[t], :])  (engine/src/cuda_backend.cu:150-154)
 __global__ void embed_kernel(const int* __restrict__ tokens, const __half* __restrict__ table, float* __restrict__ x,
                              int H, int ld_table) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const __half* row = table + static_cast<long long>(tokens[t]) * ld_table;
   float* dst = x + static_cast<long long>(t) * H;
@@ -43,6 +45,8 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const __half* __res
 // (engine/src/cuda_backend.cu:157-167; the CPU backend's form is engine/src/cpu_backend.cpp:47-52.)
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
                                __half* __restrict__ out, int H, int ld_out, float eps) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   const int r = blockIdx.x;
   const float* xr = x + static_cast<long long>(rows ? rows[r] : r) * H;
@@ -81,6 +85,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 __global__ void qkv_post_kernel(float* __restrict__ qkv, const float* __restrict__ bias,
                                 const float* __restrict__ inv_freq, TokenMeta m, __half* __restrict__ kc,
                                 __half* __restrict__ vc, int heads, int kv_heads, int D, int block_size) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float cs[];  // [D/2] cos, [D/2] sin
   const int t = blockIdx.x;
   const int Q = heads * D, KV = kv_heads * D, QKV = Q + 2 * KV, half = D / 2;
@@ -119,6 +125,8 @@ __global__ void qkv_post_kernel(float* __restrict__ qkv, const float* __restrict
 // act[t, i] = g / (1 + exp(-g)) * u  with g = gu[t, i], u = gu[t, I + i]
 // (engine/src/cuda_backend.cu:245-253; CPU form engine/src/cpu_backend.cpp:189-194).
 __global__ void silu_mul_kernel(const float* __restrict__ gu, __half* __restrict__ act, int I, int ld_act) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.y;
   const float* g = gu + static_cast<long long>(t) * 2 * I;
   const float* u = g + I;
@@ -141,6 +149,8 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, __half* __restrict
 // fp32 -> fp16 round-to-nearest-even, the bits of the host's f32_to_f16
 // (engine/src/cuda_backend.cu:110-116, engine/src/safetensors.cpp:65-88).
 __global__ void f32_to_f16_kernel(const float* __restrict__ in, __half* __restrict__ out, size_t n) {
+  pdl_trigger();
+  pdl_wait();
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<size_t>(gridDim.x) * blockDim.x)
     out[i] = __float2half_rn(in[i]);
@@ -198,6 +208,8 @@ __global__ void kv_scatter_kernel(uint4* __restrict__ k, uint4* __restrict__ v, 
 // Greedy token of each logits row; ties go to the lowest id (engine/src/sampler.cpp:17-22).
 __global__ void argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ token_out,
                                    float* __restrict__ logit_out) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   const float* row = logits + static_cast<long long>(blockIdx.x) * V;
@@ -241,7 +253,7 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int V, int*
 void launch_embed(const int* tokens, const __half* table, float* x, int T, int H, int ld_table, cudaStream_t st) {
   if (T == 0) return;
   count_launch();
-  embed_kernel<<<T, 128, 0, st>>>(tokens, table, x, H, ld_table);
+  launch_pdl(embed_kernel, dim3(T), dim3(128), 0, st, tokens, table, x, H, ld_table);
 }
 
 void launch_rmsnorm(const float* x, const int* rows, const float* w, __half* out, int R, int H, int ld_out, float eps,
@@ -249,28 +261,28 @@ void launch_rmsnorm(const float* x, const int* rows, const float* w, __half* out
   if (R == 0) return;
   const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
   count_launch();
-  rmsnorm_kernel<<<R, threads, 0, st>>>(x, rows, w, out, H, ld_out, eps);
+  launch_pdl(rmsnorm_kernel, dim3(R), dim3(threads), 0, st, x, rows, w, out, H, ld_out, eps);
 }
 
 void launch_qkv_post(float* qkv, const float* bias, const float* inv_freq, const TokenMeta& m, int T, __half* kc,
                      __half* vc, int heads, int kv_heads, int D, int block_size, cudaStream_t st) {
   if (T == 0) return;
   count_launch();
-  qkv_post_kernel<<<T, 256, D * sizeof(float), st>>>(qkv, bias, inv_freq, m, kc, vc, heads, kv_heads, D, block_size);
+  launch_pdl(qkv_post_kernel, dim3(T), dim3(256), D * sizeof(float), st, qkv, bias, inv_freq, m, kc, vc, heads, kv_heads, D, block_size);
 }
 
 void launch_silu_mul(const float* gu, __half* act, int T, int I, int ld_act, cudaStream_t st) {
   if (T == 0) return;
   dim3 grid(div_up(ld_act, 4 * 256), T);
   count_launch();
-  silu_mul_kernel<<<grid, 256, 0, st>>>(gu, act, I, ld_act);
+  launch_pdl(silu_mul_kernel, grid, dim3(256), 0, st, gu, act, I, ld_act);
 }
 
 void launch_f32_to_f16(const float* in, __half* out, size_t n, cudaStream_t st) {
   if (n == 0) return;
   const unsigned grid = static_cast<unsigned>(std::min<size_t>((n + 255) / 256, 8192));
   count_launch();
-  f32_to_f16_kernel<<<grid, 256, 0, st>>>(in, out, n);
+  launch_pdl(f32_to_f16_kernel, dim3(grid), dim3(256), 0, st, in, out, n);
 }
 
 void launch_convert_rows_f16(const float* in, __half* out, int rows, int K, int ld, cudaStream_t st) {
@@ -308,7 +320,7 @@ void launch_kv_scatter(void* k, void* v, const int* blocks, int n, size_t block_
 void launch_argmax_rows(const float* logits, int R, int V, int* token_out, float* logit_out, cudaStream_t st) {
   if (R == 0) return;
   count_launch();
-  argmax_rows_kernel<<<R, V >= 8192 ? 1024 : 256, 0, st>>>(logits, V, token_out, logit_out);
+  launch_pdl(argmax_rows_kernel, dim3(R), dim3(V >= 8192 ? 1024 : 256), 0, st, logits, V, token_out, logit_out);
 }
 
 }  // namespace rb200

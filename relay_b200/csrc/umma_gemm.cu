@@ -90,6 +90,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                  int* __restrict__ status) {
   using S = UmmaSmem<BN, INT8>;
   constexpr int NS = S::kStages;
+  pdl_trigger();
   constexpr uint32_t kTmemCols = S::kTmemCols;
   constexpr uint32_t kACol0 = S::kAccCols;  // int8: TMEM column of A stage 0 (32 columns per stage)
   extern __shared__ unsigned char smem_dyn[];
@@ -142,8 +143,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const int kx = (kb_begin + kb) * kBlockK;
       if (INT8) tma_load_2d(sRaw + kb * S::kRawBytes, &map_w, kx, m0, full_bar + 8 * kb);
       else tma_load_2d(sA + kb * S::kABytes, &map_w, kx, m0, full_bar + 8 * kb);
-      tma_load_2d(sB + kb * S::kBBytes, &map_x, kx, tok0, full_bar + 8 * kb);
     }
+    pdl_wait();  // the activations come from the kernel ahead, which may still be running
+    for (int kb = 0; kb < pre; ++kb)
+      tma_load_2d(sB + kb * S::kBBytes, &map_x, (kb_begin + kb) * kBlockK, tok0, full_bar + 8 * kb);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -158,6 +161,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (warp == 0) {
     // ---- TMA producer ----
     if (elect_one()) {
+      pdl_wait();
       for (int kb = pre; kb < nk && ok; ++kb) {
         const int s = kb % NS;
         ok = mbar_wait(empty_bar + 8 * s, ((kb / NS) & 1) ^ 1);
@@ -236,6 +240,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       }
       if (!ok) atomicExch(status, 3);
     }
+    pdl_wait();  // y (read with beta, written always) belongs to the kernels ahead until they complete
     bool done = warp < 6 ? mbar_wait(accum_bar, 0) : true;  // warps 6-9 (int8 only) take no part in the epilogue
     if (!done) atomicExch(status, 4);
     tc_fence_after();
@@ -471,13 +476,15 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
   cfg.blockDim = dim3(INT8 ? kUmmaThreadsInt8 : kUmmaThreads);
   cfg.dynamicSmemBytes = S::kTotal;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = splits;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start under the kernel ahead (common.cuh)
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   count_launch();
   int* status = status_word();
   const float* scale = W.scale;

@@ -85,10 +85,9 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 }
 
 // ---- activation rows -> digits ----------------------------------------------------------
-// Programmatic dependent launch: the GEMM that follows is launched while this kernel runs (its
-// weight loads do not depend on the digits) and waits for this grid before its first digit load.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait_primary() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Programmatic dependent launch (common.cuh): the GEMM that follows is launched while this kernel
+// runs (its weight loads do not depend on the digits) and waits for this grid before its first
+// digit load.
 
 constexpr int kQuantThreads = 512;
 constexpr int kQuantHeld = 4;  // 16-byte pieces of the row a thread keeps in registers between the passes
@@ -121,7 +120,8 @@ __device__ __forceinline__ void store_digits8(const uint4& v, float up, int8_t* 
 // One block per token. digits[d][t][k] (row pitch K), tscale[t] = 2^(e-20). K is a multiple of 8.
 __global__ void __launch_bounds__(kQuantThreads) quantize_tokens_kernel(const __half* __restrict__ x, int ldx, int K, int T,
                                                                         int8_t* __restrict__ digits, float* __restrict__ tscale) {
-  pdl_launch_dependents();
+  pdl_trigger();
+  pdl_wait();  // the activations come from the kernel ahead
   const int t = blockIdx.x;
   const uint4* row = reinterpret_cast<const uint4*>(x + static_cast<long long>(t) * ldx);
   const int pieces = K / 8;
@@ -166,6 +166,7 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   using S = I8Smem<BN>;
   constexpr int NS = S::kStages;
   constexpr uint32_t kTmemCols = S::kTmemCols;
+  pdl_trigger();
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   const uint32_t sA = base;
@@ -219,7 +220,7 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (elect_one()) {
       // The weight tiles of the first stages are already in flight; their digit tiles follow once
       // the kernel that writes the digits (it may still be running) has finished.
-      pdl_wait_primary();
+      pdl_wait();
       for (int kb = 0; kb < pre; ++kb)
         tma_load_3d(sB + kb * S::kBBytes, &map_q, (kb_begin + kb) * kBlockKB, tok0, 0, full_bar + 8 * kb);
       for (int kb = pre; kb < nk && ok; ++kb) {
@@ -251,7 +252,7 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!ok) atomicExch(status, 22);
     }
   } else {
-    pdl_wait_primary();  // token scales (and, with beta, y) come from kernels before this one
+    pdl_wait();  // token scales (and, with beta, y) come from kernels before this one
     const bool done = mbar_wait(accum_bar, 0);
     if (!done) atomicExch(status, 24);
     tc_fence_after();
@@ -428,7 +429,7 @@ void launch_umma_i8(const WeightView& W, const __half* x, int ldx, float* y, int
   int8_t* digits = static_cast<int8_t*>(scratch);
   float* tscale = reinterpret_cast<float*>(digits + (static_cast<size_t>(kDigits) * T * W.K + 15) / 16 * 16);
   count_launch();
-  quantize_tokens_kernel<<<T, kQuantThreads, 0, st>>>(x, ldx, W.K, T, digits, tscale);
+  launch_pdl(quantize_tokens_kernel, dim3(T), dim3(kQuantThreads), 0, st, x, ldx, W.K, T, digits, tscale);
   if (T <= 16) launch_i8_t<16>(W, digits, tscale, y, T, beta, st);
   else if (T <= 32) launch_i8_t<32>(W, digits, tscale, y, T, beta, st);
   else launch_i8_t<64>(W, digits, tscale, y, T, beta, st);

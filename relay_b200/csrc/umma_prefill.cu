@@ -76,11 +76,9 @@ struct PfSmem {
   static constexpr size_t kTotal = kQBytes + static_cast<size_t>(kStages) * 2 * kKBytes + kBarBytes + 1024;
 };
 
-// Programmatic dependent launch: this kernel may start while the one before it in the stream is
-// still running. Everything that kernel may have written (Q, the K/V pages) is read only after
-// pdl_wait(); the batch metadata (tiles, positions, block tables) was uploaded earlier.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Programmatic dependent launch (common.cuh): everything the kernel ahead may have written (Q, the
+// K/V pages) is read only after pdl_wait(); the batch metadata (tiles, positions, block tables)
+// was uploaded before the first kernel of the pass and is read before it.
 
 // Barrier for the 256 softmax threads only (the producer and MMA warps do not take part).
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
@@ -111,7 +109,7 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   const uint32_t q_ready = bars + 112;
   const uint32_t tmem_slot = bars + 120;
 
-  pdl_launch_dependents();
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int2 tile = tiles[blockIdx.x];
   const int t0 = tile.x, nrows = tile.y;
