@@ -35,6 +35,7 @@
 // stops issuing work, and still releases its TMEM before it returns.
 #include <cuda.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 
@@ -64,17 +65,21 @@ __device__ __forceinline__ void cvt_s8x4(uint32_t w, uint32_t& lo, uint32_t& hi)
   hi = *reinterpret_cast<uint32_t*>(&hb);
 }
 
-template <int BN, bool INT8>
+// MT = 128-row M tiles per CTA (1 or 2). Two tiles share every activation tile a CTA loads (a sixth
+// less shared-memory traffic per flop, which is what bounds the kernel from about 128 tokens up)
+// and let a grid of up to 256-row tiles fit the SMs in whole waves where 128-row tiles do not.
+// fp16 weights, no K split (the partial tile would not fit shared memory).
+template <int BN, bool INT8, int MT = 1>
 struct UmmaSmem {
-  static constexpr int kAccCols = BN < 32 ? 32 : BN;               // TMEM columns of the accumulator
-  static constexpr int kABytes = INT8 ? 0 : kTileM * kBlockK * 2;  // fp16 operand tile (fp16 weights only)
+  static constexpr int kAccCols = MT * (BN < 32 ? 32 : BN);             // TMEM columns of the accumulators
+  static constexpr int kABytes = INT8 ? 0 : MT * kTileM * kBlockK * 2;  // fp16 operand tiles (fp16 weights only)
   static constexpr int kBBytes = BN * kBlockK * 2;
   static constexpr int kRawBytes = INT8 ? kTileM * kBlockK : 0;    // int8 tile as TMA lands it
   static constexpr int kStageBytes = kABytes + kBBytes + kRawBytes;
   // Shared-memory stages: what is in flight from HBM. int8 stages are half the size of fp16
   // ones, so there are about twice as many (up to 16).
   static constexpr int kStages = INT8 ? (180 * 1024 / kStageBytes > 16 ? 16 : 180 * 1024 / kStageBytes)
-                                      : (BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 32 ? 6 : 8)));
+                                      : (MT == 2 ? (BN >= 256 ? 3 : 4) : (BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 32 ? 6 : 8))));
   // int8: the widened A tile of a k block lives in TMEM (32 columns: 64 halves per row) in a
   // ring of its own, as deep as the allocation (a power of two) allows next to the accumulator.
   static constexpr int kTmemCols = INT8 ? (BN >= 256 ? 512 : 256) : kAccCols;
@@ -83,12 +88,13 @@ struct UmmaSmem {
   static constexpr size_t kTotal = static_cast<size_t>(kStages) * kStageBytes + kBarBytes + 1024;  // + alignment slack
 };
 
-template <int BN, bool INT8>
+template <int BN, bool INT8, int MT>
 __global__ void __launch_bounds__(INT8 ? kUmmaThreadsInt8 : kUmmaThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  const float* __restrict__ scale, float* __restrict__ y, int T, int N, int K, int rows, float beta,
                  int* __restrict__ status) {
-  using S = UmmaSmem<BN, INT8>;
+  static_assert(MT == 1 || !INT8, "two M tiles per CTA: fp16 weights only");
+  using S = UmmaSmem<BN, INT8, MT>;
   constexpr int NS = S::kStages;
   pdl_trigger();
   constexpr uint32_t kTmemCols = S::kTmemCols;
@@ -111,7 +117,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   unsigned char* gen_base = smem_dyn + (base - smem_u32(smem_dyn));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // `rows` (a multiple of 8, at most 128) weight rows per CTA: the host shrinks the tile so that
+  // `rows` (a multiple of 8, at most 128 * MT) weight rows per CTA: the host shrinks the tile so that
   // the grid fills the SMs evenly; the MMA still spans 128 lanes and the rest is ignored.
   const int m0 = blockIdx.x * rows, tok0 = blockIdx.y * BN;
   const uint32_t stage_tx = static_cast<uint32_t>(rows) * kBlockK * (INT8 ? 1 : 2) + S::kBBytes;
@@ -194,8 +200,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         } else {
           const uint64_t da = smem_desc_sw128(sA + s * S::kABytes);
 #pragma unroll
-          for (int k4 = 0; k4 < kBlockK / 16; ++k4)  // 16 halves = 32 bytes = 2 descriptor units per step
+          for (int k4 = 0; k4 < kBlockK / 16; ++k4) {  // 16 halves = 32 bytes = 2 descriptor units per step
             umma_f16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+            if constexpr (MT == 2)  // rows 128.. of the tile (16 KB further on), the same activations
+              umma_f16(tmem_base + BN, da + (kTileM * kBlockK * 2 >> 4) + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+          }
         }
         umma_commit(empty_bar + 8 * s);  // arrives once the MMAs above have read the stage
       }
@@ -254,24 +263,30 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     } else if (splits == 1) {
       if (done && ok) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
-          tmem_ld_wait();
-          if (live) {
-            float* d0 = y + static_cast<long long>(tok0 + c0) * N + n;
-            const int nt = min(32, T - tok0 - c0);  // valid token columns of this chunk
-            if (beta != 0.f) {
-              float old[32];  // all loads first, so that they are in flight together
+        for (int a = 0; a < MT; ++a) {  // the CTA's M tiles: TMEM columns a * BN .., weight rows a * 128 ..
+          const int row_a = a * kTileM + row, n_a = m0 + row_a;
+          const bool live_a = row_a < rows && n_a < N;
+          const float sc_a = (INT8 && live_a) ? scale[n_a] : 1.0f;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN + c0, v);
+            tmem_ld_wait();
+            if (live_a) {
+              float* d0 = y + static_cast<long long>(tok0 + c0) * N + n_a;
+              const int nt = min(32, T - tok0 - c0);  // valid token columns of this chunk
+              if (beta != 0.f) {
+                float old[32];  // all loads first, so that they are in flight together
 #pragma unroll
-              for (int j = 0; j < 32; ++j) old[j] = j < nt ? d0[static_cast<long long>(j) * N] : 0.f;
+                for (int j = 0; j < 32; ++j) old[j] = j < nt ? d0[static_cast<long long>(j) * N] : 0.f;
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < nt) d0[static_cast<long long>(j) * N] = __uint_as_float(v[j]) * sc + beta * old[j];
-            } else {
+                for (int j = 0; j < 32; ++j)
+                  if (j < nt) d0[static_cast<long long>(j) * N] = __uint_as_float(v[j]) * sc_a + beta * old[j];
+              } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < nt) d0[static_cast<long long>(j) * N] = __uint_as_float(v[j]) * sc;
+                for (int j = 0; j < 32; ++j)
+                  if (j < nt) d0[static_cast<long long>(j) * N] = __uint_as_float(v[j]) * sc_a;
+              }
             }
           }
         }
@@ -410,22 +425,53 @@ int* tc::status_word() {
 
 namespace {
 
-template <int BN, bool INT8>
-void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st) {
-  using S = UmmaSmem<BN, INT8>;
+// One launch with the tile shape the planner chose.
+template <int BN, bool INT8, int MT>
+void launch_umma_cfg(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st, int rows,
+                     int splits) {
+  using S = UmmaSmem<BN, INT8, MT>;
   static bool configured = false;
-  auto kernel = umma_gemm_kernel<BN, INT8>;
+  auto kernel = umma_gemm_kernel<BN, INT8, MT>;
   if (!configured) {
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
     configured = true;
   }
-  // Rows per CTA and the K split (a cluster along z): the pair that needs the fewest
-  // (waves x bytes per CTA), where a CTA's fixed cost (prologue, pipeline fill, epilogue) counts
-  // like 48 KB of weights. A cluster needs its CTAs on SMs of one GPC at the same time, so
-  // fewer clusters than SMs / size are resident together: the occupancy query says how many.
+  const CUtensorMap mw = INT8 ? make_map(W.i8, 1, W.N, W.K, W.ld, rows, kBlockK, false, true)
+                              : make_map(W.f16, 2, W.N, W.K, W.ld, rows, kBlockK, true);
+  const CUtensorMap mx = make_map(x, 2, T, W.K, ldx, BN, kBlockK, true);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(div_up(W.N, rows), div_up(T, BN), splits);
+  cfg.blockDim = dim3(INT8 ? kUmmaThreadsInt8 : kUmmaThreads);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = splits;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start under the kernel ahead (common.cuh)
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  count_launch();
+  int* status = status_word();
+  const float* scale = W.scale;
+  const int N = W.N, K = W.K;
+  RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, mw, mx, scale, y, T, N, K, rows, beta, status));
+}
+
+template <int BN, bool INT8>
+void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st) {
+  using S = UmmaSmem<BN, INT8, 1>;
+  // Rows per CTA, M tiles per CTA and the K split (a cluster along z): the combination that needs
+  // the fewest (waves x weight bytes per CTA), where a CTA's fixed cost (prologue, pipeline fill,
+  // epilogue) counts like 48 KB of weights. A cluster needs its CTAs on SMs of one GPC at the same
+  // time, so fewer clusters than SMs / size are resident together: the occupancy query says how many.
   const int ttiles = div_up(T, BN), nk = W.K / kBlockK;
   static int capacity[9] = {0};  // clusters of size s resident at once on this device
   if (capacity[1] == 0) {
+    auto kernel = umma_gemm_kernel<BN, INT8, 1>;
+    RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
     for (int sp = 1; sp <= 8; ++sp) {
       cudaLaunchConfig_t q{};
       q.gridDim = dim3(1, 1, sp);
@@ -447,49 +493,50 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
     }
   }
   const bool can_split = static_cast<size_t>(BN) * kTileM * 4 <= static_cast<size_t>(S::kStages) * S::kStageBytes;
+  constexpr bool kTwoTiles = !INT8 && BN >= 128;  // two M tiles per CTA: fp16, wide token tiles, no K split
+  static const bool two_off = [] {
+    const char* e = std::getenv("RB200_GEMM_MT");
+    return e && std::atoi(e) == 1;
+  }();
   const double elem = INT8 ? 1.0 : 2.0;
-  int rows = kTileM, splits = 1;
+  int rows = kTileM, splits = 1, mt = 1;
   double best = 1e30;
-  for (int r = kTileM; r >= 64; r -= 8) {
-    for (int sp = 1; sp <= 8; ++sp) {
-      if (sp > 1 && (!can_split || nk / sp < 4)) break;
-      const long long clusters = static_cast<long long>(div_up(W.N, r)) * ttiles;
-      const double cost = static_cast<double>(div_up(clusters, static_cast<long long>(capacity[sp]))) *
-                          (static_cast<double>(r) * W.K * elem / sp + 48.0 * 1024 + (sp > 1 ? 8.0 * 1024 : 0.0));
-      if (cost < best - 1e-9) {
-        best = cost;
-        rows = r;
-        splits = sp;
+  // Two M tiles only with at least 200 of their 256 rows in use: the second MMA tile costs the
+  // same however few of its rows count (176-row tiles measured slower than 128-row ones).
+  for (int m = 1; m <= ((kTwoTiles && !two_off) ? 2 : 1); ++m) {
+    for (int r = kTileM * m; r >= (m == 1 ? 64 : 200); r -= 8) {
+      for (int sp = 1; sp <= (m == 1 ? 8 : 1); ++sp) {
+        if (sp > 1 && (!can_split || nk / sp < 4)) break;
+        const long long clusters = static_cast<long long>(div_up(W.N, r)) * ttiles;
+        const int cap = m == 1 ? capacity[sp] : sm_count();
+        const double cost = static_cast<double>(div_up(clusters, static_cast<long long>(cap))) *
+                            (static_cast<double>(r) * elem * W.K / sp + 48.0 * 1024 + (sp > 1 ? 8.0 * 1024 : 0.0));
+        if (cost < best - 1e-9) {
+          best = cost;
+          rows = r;
+          splits = sp;
+          mt = m;
+        }
       }
     }
   }
-  const CUtensorMap mw = INT8 ? make_map(W.i8, 1, W.N, W.K, W.ld, rows, kBlockK, false, true)
-                              : make_map(W.f16, 2, W.N, W.K, W.ld, rows, kBlockK, true);
-  const CUtensorMap mx = make_map(x, 2, T, W.K, ldx, BN, kBlockK, true);
   static const int forced = [] {
     const char* e = std::getenv("RB200_GEMM_SPLITS");
     return e ? std::atoi(e) : 0;
   }();
-  if (forced > 0 && can_split) splits = std::min({forced, 8, std::max(1, nk)});
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(div_up(W.N, rows), ttiles, splits);
-  cfg.blockDim = dim3(INT8 ? kUmmaThreadsInt8 : kUmmaThreads);
-  cfg.dynamicSmemBytes = S::kTotal;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = splits;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start under the kernel ahead (common.cuh)
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 2;
-  count_launch();
-  int* status = status_word();
-  const float* scale = W.scale;
-  const int N = W.N, K = W.K;
-  RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, mw, mx, scale, y, T, N, K, rows, beta, status));
+  if (forced > 0 && can_split) {
+    splits = std::min({forced, 8, std::max(1, nk)});
+    if (mt == 2) rows = kTileM;
+    mt = 1;
+  }
+  static const bool debug = std::getenv("RB200_GEMM_DEBUG") != nullptr;
+  if (debug)
+    std::fprintf(stderr, "umma_gemm N=%d K=%d T=%d int8=%d: token tile %d, %d rows per CTA (%d M tiles), K split %d, grid %d x %d x %d\n",
+                 W.N, W.K, T, INT8 ? 1 : 0, BN, rows, mt, splits, div_up(W.N, rows), ttiles, splits);
+  if constexpr (kTwoTiles) {
+    if (mt == 2) return launch_umma_cfg<BN, INT8, 2>(W, x, ldx, y, T, beta, st, rows, 1);
+  }
+  launch_umma_cfg<BN, INT8, 1>(W, x, ldx, y, T, beta, st, rows, splits);
 }
 
 template <bool INT8>
