@@ -514,6 +514,16 @@ def gpu_arm(args) -> dict:
         e2e_s = time.perf_counter() - t0
     e2e_s = max_over_ranks(e2e_s)
 
+    # the same call returning the greedy token of each row instead of its logits (the device
+    # reduces the 128 256-wide rows): 2 KB instead of 131 MB come back per step
+    be.forward_greedy_flat(fb)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        be.forward_greedy_flat(fb)
+    barrier()
+    greedy_s = max_over_ranks(time.perf_counter() - t0)
+
     # value: the same passes from device-resident metadata, timed with CUDA events
     be.set_profiling(True)
     be.take_profile()
@@ -551,6 +561,9 @@ def gpu_arm(args) -> dict:
                    "l2": "per-step working set (KV + weights) is far larger than L2"},
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s / args.steps * 1e3},
+        "e2e_greedy": {"value": seqs * world / (greedy_s / args.steps), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+                       "d2h_bytes_per_step": seqs * 8, "ms_per_step": greedy_s / args.steps * 1e3,
+                       "note": "rb200_forward_greedy: token id and logit per row instead of the logits"},
         "gpu_launches": int(launches),
         "roofline": {"kernel": "decode_split_kernel<128> (+ decode_merge_kernel when contexts are split)", "bound": "hbm", "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if peak else None,

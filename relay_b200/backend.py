@@ -117,6 +117,16 @@ class Backend:
             ptr(want), int(fb.all_logits), cb, None, ptr(tok), ptr(val), rows))
         return tok[:r], val[:r]
 
+    def forward_greedy_flat(self, fb: FlatBatch) -> Tuple[np.ndarray, np.ndarray]:
+        """forward_greedy() on an already flattened batch."""
+        rows = max(fb.n_rows, 1)
+        tok, val = np.empty(rows, np.int32), np.empty(rows, np.float32)
+        want = fb.want_logits.astype(np.uint8)
+        r = _lib.check(self._L.rb200_forward_greedy(
+            self._h, fb.n_seqs, ptr(fb.tokens), ptr(fb.chunk_len), ptr(fb.start_pos), ptr(fb.table_len), ptr(fb.tables),
+            ptr(want), int(fb.all_logits), _lib.LAYER_CB(), None, ptr(tok), ptr(val), rows))
+        return tok[:r], val[:r]
+
     def kv_block_bytes(self) -> int:
         return self._L.rb200_kv_block_bytes(self._h)
 
