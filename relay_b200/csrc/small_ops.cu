@@ -88,7 +88,9 @@ __global__ void qkv_post_kernel(float* __restrict__ qkv, const float* __restrict
   pdl_trigger();
   pdl_wait();
   extern __shared__ float cs[];  // [D/2] cos, [D/2] sin
-  const int t = blockIdx.x;
+  // gridDim.y blocks share a token (heads and kv_heads are multiples of it): each takes its share
+  // of the q heads and of the k/v heads.
+  const int t = blockIdx.x, part = blockIdx.y, parts = gridDim.y;
   const int Q = heads * D, KV = kv_heads * D, QKV = Q + 2 * KV, half = D / 2;
   float* row = qkv + static_cast<long long>(t) * QKV;
   const int p = m.pos[t];
@@ -98,25 +100,38 @@ __global__ void qkv_post_kernel(float* __restrict__ qkv, const float* __restrict
     cs[i] = c;
     cs[half + i] = s;
   }
-  if (bias)
-    for (int i = threadIdx.x; i < QKV; i += blockDim.x) row[i] += bias[i];
-  __syncthreads();
   const int block = m.tables[m.table_off[m.seq[t]] + p / block_size], slot = p % block_size;
-  for (int idx = threadIdx.x; idx < (heads + kv_heads) * half; idx += blockDim.x) {
-    const int h = idx / half, i = idx - h * half;
-    float* v = row + h * D;  // q heads, then the k heads right behind them
+  __syncthreads();
+  // rotation: this part's q heads, then this part's k heads (stored below by the same block)
+  const int qh = heads / parts, kh = kv_heads / parts;
+  const int items = (qh + kh) * half;
+  for (int idx = threadIdx.x; idx < items; idx += blockDim.x) {
+    const int hl = idx / half, i = idx - hl * half;
+    const int h = hl < qh ? part * qh + hl : heads + part * kh + (hl - qh);  // head index in the qkv row
+    float* v = row + h * D;
     const float c = cs[i], s = cs[half + i];
-    const float a = v[i], b = v[i + half];
+    float a = v[i], b = v[i + half];
+    if (bias) {
+      a += bias[h * D + i];
+      b += bias[h * D + i + half];
+    }
     v[i] = a * c - b * s;
     v[i + half] = b * c + a * s;
   }
   __syncthreads();
-  for (int idx = threadIdx.x * 2; idx < KV; idx += blockDim.x * 2) {
+  // k (rotated above by this very block) and v (plus its bias) -> fp16 pages
+  const int kv0 = part * kh * D, kv1 = kv0 + kh * D;
+  for (int idx = kv0 + threadIdx.x * 2; idx < kv1; idx += blockDim.x * 2) {
     const int h = idx / D, d = idx - h * D;
     const long long off = (static_cast<long long>(block) * kv_heads + h) * block_size * D +
                           static_cast<long long>(slot) * D + d;
     const float2 k2 = *reinterpret_cast<const float2*>(row + Q + idx);
-    const float2 v2 = *reinterpret_cast<const float2*>(row + Q + KV + idx);
+    float2 v2 = *reinterpret_cast<const float2*>(row + Q + KV + idx);
+    if (bias) {  // written back as well: the row then is what the reference's kernel leaves in place
+      v2.x += bias[Q + KV + idx];
+      v2.y += bias[Q + KV + idx + 1];
+      *reinterpret_cast<float2*>(row + Q + KV + idx) = v2;
+    }
     *reinterpret_cast<__half2*>(kc + off) = __floats2half2_rn(k2.x, k2.y);
     *reinterpret_cast<__half2*>(vc + off) = __floats2half2_rn(v2.x, v2.y);
   }
@@ -268,7 +283,15 @@ void launch_qkv_post(float* qkv, const float* bias, const float* inv_freq, const
                      __half* vc, int heads, int kv_heads, int D, int block_size, cudaStream_t st) {
   if (T == 0) return;
   count_launch();
-  launch_pdl(qkv_post_kernel, dim3(T), dim3(256), D * sizeof(float), st, qkv, bias, inv_freq, m, kc, vc, heads, kv_heads, D, block_size);
+  // Several blocks per token when the heads divide evenly (a block stores the k values it rotated itself).
+  int parts = 1;
+  for (int c : {4, 2})
+    if (kv_heads % c == 0 && (heads % c == 0) && T * c <= 8192) {
+      parts = c;
+      break;
+    }
+  launch_pdl(qkv_post_kernel, dim3(T, parts), dim3(256), D * sizeof(float), st, qkv, bias, inv_freq, m, kc, vc, heads, kv_heads, D,
+             block_size);
 }
 
 void launch_silu_mul(const float* gu, __half* act, int T, int I, int ld_act, cudaStream_t st) {
