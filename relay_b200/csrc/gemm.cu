@@ -489,8 +489,8 @@ void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T,
   if (T == 0) return;
   // Above 16 tokens the digit tiles (three bytes per activation) crowd the weight tiles out of
   // shared memory and L2 bandwidth, and the kernel that widens int8 into TMEM takes over
-  // (measured crossover: 32 tokens on 58 MB matrices, 16 on 16 MB ones).
-  const bool digits = T <= 16 || (T <= 32 && static_cast<long long>(W.N) * W.K >= (32LL << 20));
+  // (58.7 MB matrix, 32 tokens: 15.3 us against 14.5 us).
+  const bool digits = T <= 16;
   if (W.i8 && digits && !gemm_forced_legacy() && umma_i8_usable(W, x, ldx, T)) {
     const size_t off = gemv_partials_bytes(W.N, W.K), need = i8_digits_bytes(T, W.K);
     if (scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && scratch_bytes >= off + need) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + off, st);

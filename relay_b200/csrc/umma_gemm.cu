@@ -71,10 +71,14 @@ __device__ __forceinline__ void cvt_s8x4(uint32_t w, uint32_t& lo, uint32_t& hi)
 // fp16 weights, no K split (the partial tile would not fit shared memory).
 template <int BN, bool INT8, int MT = 1>
 struct UmmaSmem {
+  // Elements of K per block. int8 weights with up to 128 tokens take 128 (two swizzle atoms of
+  // activations per stage): there the pace is set by the hand-offs per block, not by the MMAs.
+  static constexpr int kKB = (INT8 && BN <= 128) ? 2 * kBlockK : kBlockK;
+  static constexpr int kAtoms = kKB / kBlockK;                          // 128-byte activation atoms per block
   static constexpr int kAccCols = MT * (BN < 32 ? 32 : BN);             // TMEM columns of the accumulators
   static constexpr int kABytes = INT8 ? 0 : MT * kTileM * kBlockK * 2;  // fp16 operand tiles (fp16 weights only)
-  static constexpr int kBBytes = BN * kBlockK * 2;
-  static constexpr int kRawBytes = INT8 ? kTileM * kBlockK : 0;    // int8 tile as TMA lands it
+  static constexpr int kBBytes = BN * kKB * 2;
+  static constexpr int kRawBytes = INT8 ? kTileM * kKB : 0;             // int8 tile as TMA lands it
   static constexpr int kStageBytes = kABytes + kBBytes + kRawBytes;
   // Shared-memory stages: what is in flight from HBM. int8 stages are half the size of fp16
   // ones, so there are about twice as many (up to 16).
@@ -83,7 +87,8 @@ struct UmmaSmem {
   // int8: the widened A tile of a k block lives in TMEM (32 columns: 64 halves per row) in a
   // ring of its own, as deep as the allocation (a power of two) allows next to the accumulator.
   static constexpr int kTmemCols = INT8 ? (BN >= 256 ? 512 : 256) : kAccCols;
-  static constexpr int kAStages = INT8 ? (kTmemCols - kAccCols) / 32 : 0;
+  static constexpr int kASlotCols = kKB / 2;  // fp16 pairs per row of a widened block
+  static constexpr int kAStages = INT8 ? (kTmemCols - kAccCols) / kASlotCols : 0;
   static constexpr int kBarBytes = 1024;
   static constexpr size_t kTotal = static_cast<size_t>(kStages) * kStageBytes + kBarBytes + 1024;  // + alignment slack
 };
@@ -120,9 +125,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   // `rows` (a multiple of 8, at most 128 * MT) weight rows per CTA: the host shrinks the tile so that
   // the grid fills the SMs evenly; the MMA still spans 128 lanes and the rest is ignored.
   const int m0 = blockIdx.x * rows, tok0 = blockIdx.y * BN;
-  const uint32_t stage_tx = static_cast<uint32_t>(rows) * kBlockK * (INT8 ? 1 : 2) + S::kBBytes;
+  constexpr int KB = S::kKB;
+  const uint32_t stage_tx = static_cast<uint32_t>(rows) * KB * (INT8 ? 1 : 2) + S::kBBytes;
   const int splits = gridDim.z, split = blockIdx.z;  // the cluster spans z: split == rank in the cluster
-  const int nk_all = K / kBlockK;
+  const int nk_all = (K + KB - 1) / KB;  // a last half block (K is a multiple of 64) reads zeros past K
   const int kb_begin = static_cast<int>(static_cast<long long>(nk_all) * split / splits);
   const int nk = static_cast<int>(static_cast<long long>(nk_all) * (split + 1) / splits) - kb_begin;
 
@@ -146,13 +152,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
     for (int kb = 0; kb < pre; ++kb) {
       mbar_expect_tx(full_bar + 8 * kb, stage_tx);
-      const int kx = (kb_begin + kb) * kBlockK;
+      const int kx = (kb_begin + kb) * KB;
       if (INT8) tma_load_2d(sRaw + kb * S::kRawBytes, &map_w, kx, m0, full_bar + 8 * kb);
       else tma_load_2d(sA + kb * S::kABytes, &map_w, kx, m0, full_bar + 8 * kb);
     }
     pdl_wait();  // the activations come from the kernel ahead, which may still be running
     for (int kb = 0; kb < pre; ++kb)
-      tma_load_2d(sB + kb * S::kBBytes, &map_x, (kb_begin + kb) * kBlockK, tok0, full_bar + 8 * kb);
+#pragma unroll
+      for (int at = 0; at < S::kAtoms; ++at)
+        tma_load_2d(sB + kb * S::kBBytes + at * (BN * 128), &map_x, (kb_begin + kb) * KB + at * kBlockK, tok0, full_bar + 8 * kb);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -174,10 +182,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         if (INT8 && ok) ok = mbar_wait(raw_free + 8 * s, ((kb / NS) & 1) ^ 1);
         if (!ok) break;
         mbar_expect_tx(full_bar + 8 * s, stage_tx);
-        const int kx = (kb_begin + kb) * kBlockK;
+        const int kx = (kb_begin + kb) * KB;
         if (INT8) tma_load_2d(sRaw + s * S::kRawBytes, &map_w, kx, m0, full_bar + 8 * s);
         else tma_load_2d(sA + s * S::kABytes, &map_w, kx, m0, full_bar + 8 * s);
-        tma_load_2d(sB + s * S::kBBytes, &map_x, kx, tok0, full_bar + 8 * s);
+#pragma unroll
+        for (int at = 0; at < S::kAtoms; ++at)
+          tma_load_2d(sB + s * S::kBBytes + at * (BN * 128), &map_x, kx + at * kBlockK, tok0, full_bar + 8 * s);
       }
       if (!ok) atomicExch(status, 1);
     }
@@ -193,9 +203,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         tc_fence_after();
         const uint64_t db = smem_desc_sw128(sB + s * S::kBBytes);
         if constexpr (INT8) {
-          const uint32_t ta = tmem_base + kACol0 + (kb % NA) * 32;  // 16 halves = 8 columns per step
+          const uint32_t ta = tmem_base + kACol0 + (kb % NA) * S::kASlotCols;  // 16 halves = 8 columns per step
 #pragma unroll
-          for (int k4 = 0; k4 < kBlockK / 16; ++k4) umma_f16_ta(tmem_base, ta + 8 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+          for (int k4 = 0; k4 < KB / 16; ++k4)  // activations: atom k4 / 4 (BN rows x 128 bytes each), 32 bytes per step inside it
+            umma_f16_ta(tmem_base, ta + 8 * k4, db + (k4 / 4) * (BN * 128 >> 4) + 2 * (k4 % 4), idesc, (kb | k4) != 0);
           umma_commit(a_free + 8 * (kb % NA));
         } else {
           const uint64_t da = smem_desc_sw128(sA + s * S::kABytes);
@@ -215,24 +226,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     // ---- int8 widening (main loop), then the epilogue ----
     if constexpr (INT8) {
       // Two groups of four warps take alternate k blocks, so two blocks are widened at a time.
-      // Thread = one weight row (the TMEM lane it may write): 64 int8 from the 64-byte-swizzled
-      // raw tile -> 64 fp16 -> the 32 TMEM columns of an A stage.
+      // Thread = one weight row (the TMEM lane it may write): the row's KB int8 from the swizzled
+      // raw tile (64-byte rows: 64-byte swizzle, 128-byte rows: 128-byte swizzle) -> KB fp16 ->
+      // the KB / 2 TMEM columns of an A stage.
+      constexpr int CH = KB / 16;  // 16-byte pieces of a raw row
       const int crow = (warp & 3) * 32 + lane, group = (warp - 2) >> 2;
-      const int sw = (crow >> 1) & 3;
+      const int sw = CH == 4 ? ((crow >> 1) & 3) : (crow & 7);
       const uint32_t tcol = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + kACol0;
       for (int kb = group; kb < nk && ok; kb += 2) {
         const int s = kb % NS, a = kb % NA;
         ok = mbar_wait(full_bar + 8 * s, (kb / NS) & 1);
         if (!ok) break;
-        const uint4* raw = reinterpret_cast<const uint4*>(gen_base + (sRaw + s * S::kRawBytes - base)) + crow * 4;
-        uint4 r[4];
+        const uint4* raw = reinterpret_cast<const uint4*>(gen_base + (sRaw + s * S::kRawBytes - base)) + crow * CH;
+        uint4 r[CH];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) r[c] = raw[c ^ sw];
+        for (int c = 0; c < CH; ++c) r[c] = raw[c ^ sw];
         __syncwarp();
         if (lane == 0) mbar_arrive(raw_free + 8 * s);  // the raw tile is in registers: its stage may be refilled
-        uint32_t h[32];
+        uint32_t h[CH * 8];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < CH; ++c) {
           cvt_s8x4(r[c].x, h[8 * c], h[8 * c + 1]);
           cvt_s8x4(r[c].y, h[8 * c + 2], h[8 * c + 3]);
           cvt_s8x4(r[c].z, h[8 * c + 4], h[8 * c + 5]);
@@ -241,7 +254,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         ok = mbar_wait(a_free + 8 * a, ((kb / NA) & 1) ^ 1);  // the MMA that last read this A stage is done
         if (!ok) break;
         tc_fence_after();
-        tmem_st32(tcol + a * 32, h);
+#pragma unroll
+        for (int q = 0; q < CH / 4; ++q)
+          tmem_st32(tcol + a * S::kASlotCols + 32 * q, *reinterpret_cast<uint32_t(*)[32]>(&h[32 * q]));
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -436,7 +451,7 @@ void launch_umma_cfg(const WeightView& W, const __half* x, int ldx, float* y, in
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
     configured = true;
   }
-  const CUtensorMap mw = INT8 ? make_map(W.i8, 1, W.N, W.K, W.ld, rows, kBlockK, false, true)
+  const CUtensorMap mw = INT8 ? make_map(W.i8, 1, W.N, W.K, W.ld, rows, S::kKB, S::kKB == 128, S::kKB == 64)
                               : make_map(W.f16, 2, W.N, W.K, W.ld, rows, kBlockK, true);
   const CUtensorMap mx = make_map(x, 2, T, W.K, ldx, BN, kBlockK, true);
   cudaLaunchConfig_t cfg{};
@@ -467,7 +482,7 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
   // the fewest (waves x weight bytes per CTA), where a CTA's fixed cost (prologue, pipeline fill,
   // epilogue) counts like 48 KB of weights. A cluster needs its CTAs on SMs of one GPC at the same
   // time, so fewer clusters than SMs / size are resident together: the occupancy query says how many.
-  const int ttiles = div_up(T, BN), nk = W.K / kBlockK;
+  const int ttiles = div_up(T, BN), nk = div_up(W.K, S::kKB);
   static int capacity[9] = {0};  // clusters of size s resident at once on this device
   if (capacity[1] == 0) {
     auto kernel = umma_gemm_kernel<BN, INT8, 1>;
