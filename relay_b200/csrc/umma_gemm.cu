@@ -546,8 +546,10 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
   }
   static const bool debug = std::getenv("RB200_GEMM_DEBUG") != nullptr;
   if (debug)
-    std::fprintf(stderr, "umma_gemm N=%d K=%d T=%d int8=%d: token tile %d, %d rows per CTA (%d M tiles), K split %d, grid %d x %d x %d\n",
-                 W.N, W.K, T, INT8 ? 1 : 0, BN, rows, mt, splits, div_up(W.N, rows), ttiles, splits);
+    std::fprintf(stderr, "umma_gemm N=%d K=%d T=%d int8=%d: token tile %d, %d rows per CTA (%d M tiles), K split %d, grid %d x %d x %d; "
+                 "resident clusters by size: %d %d %d %d %d %d %d %d\n",
+                 W.N, W.K, T, INT8 ? 1 : 0, BN, rows, mt, splits, div_up(W.N, rows), ttiles, splits, capacity[1], capacity[2],
+                 capacity[3], capacity[4], capacity[5], capacity[6], capacity[7], capacity[8]);
   if constexpr (kTwoTiles) {
     if (mt == 2) return launch_umma_cfg<BN, INT8, 2>(W, x, ldx, y, T, beta, st, rows, 1);
   }
