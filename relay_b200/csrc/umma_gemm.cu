@@ -322,40 +322,78 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (splits > 1) {
     cluster_sync_all();  // every member's partial tile is in its shared memory
     if (warp >= 2 && warp < 6) {
-      const int row = (warp & 3) * 32 + lane;
-      const int n = m0 + row;
-      const bool live = row < rows && n < N;
-      const float sc = (INT8 && live) ? scale[n] : 1.0f;
-      const int per = (BN + splits - 1) / splits;  // token columns this CTA finishes
+      // This CTA finishes `per` token columns of the tile: a thread takes four consecutive weight
+      // rows of one column (16-byte DSMEM loads; the rows are contiguous in red[token][row]), the
+      // four warps take the columns round-robin, the members are added in rank order.
+      const int tid = threadIdx.x - 64, r4 = (tid & 31) * 4, cg = tid >> 5;
+      const int n4 = m0 + r4;
+      const int per = (BN + splits - 1) / splits;
       const int c_begin = split * per, c_end = min(min(BN, c_begin + per), T - tok0);
+      bool live[4];
+      float sc[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        live[k] = r4 + k < rows && n4 + k < N;
+        sc[k] = (INT8 && live[k]) ? scale[n4 + k] : 1.0f;
+      }
+      const bool vec = (N & 3) == 0 && live[3];  // the four outputs form one aligned float4 of y
       uint32_t peer[8];
 #pragma unroll
       for (int r = 0; r < 8; ++r)  // fully unrolled so that peer[] stays in registers
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[r]) : "r"(base + static_cast<uint32_t>(row) * 4), "r"(r < splits ? r : 0));
-      for (int c = c_begin; c < c_end; c += 8) {
-        float acc[8], old[8];
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[r]) : "r"(base + static_cast<uint32_t>(r4) * 4), "r"(r < splits ? r : 0));
+      for (int c = c_begin + cg; c < c_end; c += 8) {
+        float4 acc[2], old[2];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          acc[j] = 0.f;
-          old[j] = (beta != 0.f && live && c + j < c_end) ? y[static_cast<long long>(tok0 + c + j) * N + n] : 0.f;
+        for (int u = 0; u < 2; ++u) {
+          acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          old[u] = acc[u];
+          const int cc = c + 4 * u;
+          if (beta != 0.f && cc < c_end) {
+            const float* src = y + static_cast<long long>(tok0 + cc) * N + n4;
+            if (vec) old[u] = *reinterpret_cast<const float4*>(src);
+            else {
+              if (live[0]) old[u].x = src[0];
+              if (live[1]) old[u].y = src[1];
+              if (live[2]) old[u].z = src[2];
+              if (live[3]) old[u].w = src[3];
+            }
+          }
         }
 #pragma unroll
         for (int r = 0; r < 8; ++r) {  // members in rank order: the sum is the same on every run
           if (r >= splits) break;
-          float part[8];
+          float4 part[2];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            part[j] = 0.f;
-            if (c + j < c_end)
-              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[j]) : "r"(peer[r] + static_cast<uint32_t>((c + j) * kTileM) * 4) : "memory");
+          for (int u = 0; u < 2; ++u) {
+            part[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c + 4 * u < c_end)
+              asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(part[u].x), "=f"(part[u].y), "=f"(part[u].z), "=f"(part[u].w)
+                           : "r"(peer[r] + static_cast<uint32_t>((c + 4 * u) * kTileM) * 4)
+                           : "memory");
           }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] += part[j];
+          for (int u = 0; u < 2; ++u) {
+            acc[u].x += part[u].x;
+            acc[u].y += part[u].y;
+            acc[u].z += part[u].z;
+            acc[u].w += part[u].w;
+          }
         }
-        if (live) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (c + j < c_end) y[static_cast<long long>(tok0 + c + j) * N + n] = acc[j] * sc + beta * old[j];
+        for (int u = 0; u < 2; ++u) {
+          const int cc = c + 4 * u;
+          if (cc >= c_end) continue;
+          float* dst = y + static_cast<long long>(tok0 + cc) * N + n4;
+          const float4 v = make_float4(acc[u].x * sc[0] + beta * old[u].x, acc[u].y * sc[1] + beta * old[u].y,
+                                       acc[u].z * sc[2] + beta * old[u].z, acc[u].w * sc[3] + beta * old[u].w);
+          if (vec) *reinterpret_cast<float4*>(dst) = v;
+          else {
+            if (live[0]) dst[0] = v.x;
+            if (live[1]) dst[1] = v.y;
+            if (live[2]) dst[2] = v.z;
+            if (live[3]) dst[3] = v.w;
+          }
         }
       }
     }
