@@ -438,6 +438,15 @@ static bool i8_digits_preferred(const WeightView& W) {
   return static_cast<long long>(W.N) * W.K >= min_bytes;
 }
 
+// Up to umma_i8_fused_tokens() tokens the kernel can make the digits itself (every CTA then reads
+// the activation rows for their largest magnitude). Measured against the separate digit pass it
+// wins where a CTA streams much more weight data than activations: 58.7 MB, 1 / 2 / 4 tokens,
+// K = 4096: 12.1 / 12.4 / 12.7 us against 13.0 / 13.1 / 13.2; K = 14336: 13.2 / 14.0 / 15.6 against
+// 13.5 / 14.2 / 15.2; 16.8 MB (K split over a cluster of four): 7.0 against 6.5.
+static bool i8_fused_preferred(const WeightView& W, int T) {
+  return T <= umma_i8_fused_tokens() && static_cast<long long>(W.N) * W.K >= (32ll << 20) && static_cast<long long>(T) * W.K <= 32768;
+}
+
 static bool gemm_forced_legacy() {
   static const bool v = [] {
     const char* e = std::getenv("RB200_GEMM");
@@ -462,9 +471,13 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
   // fp16 weights stream faster through TMA (whole 128-byte row pieces) than through per-lane
   // 16-byte loads, so the few-token case uses the tcgen05 kernel with a 16-token tile.
   if (W.f16 && !gemm_forced_legacy() && umma_gemm_usable(W, x, ldx)) return launch_umma_gemm(W, x, ldx, y, T, beta, st);
-  if (W.i8 && !gemm_forced_legacy() && i8_digits_preferred(W) && umma_i8_usable(W, x, ldx, T) && scratch != nullptr &&
-      (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && scratch_bytes >= gemv_partials_bytes(W.N, W.K) + i8_digits_bytes(T, W.K))
-    return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + gemv_partials_bytes(W.N, W.K), st);
+  if (W.i8 && !gemm_forced_legacy() && i8_digits_preferred(W) && umma_i8_usable(W, x, ldx, T)) {
+    const bool room = scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 &&
+                      scratch_bytes >= gemv_partials_bytes(W.N, W.K) + i8_digits_bytes(T, W.K);
+    if (i8_fused_preferred(W, T) || (!room && T <= umma_i8_fused_tokens()))
+      return launch_umma_i8(W, x, ldx, y, T, beta, nullptr, st);  // digits made in the kernel
+    if (room) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + gemv_partials_bytes(W.N, W.K), st);
+  }
   unsigned* counters = static_cast<unsigned*>(scratch);
   float* partials = scratch ? reinterpret_cast<float*>(static_cast<char*>(scratch) + gemv_counter_bytes(W.N)) : nullptr;
   const GemvPlan p = plan_gemv(W.N, W.K);
@@ -493,6 +506,8 @@ void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T,
   const bool digits = T <= 16;
   if (W.i8 && digits && !gemm_forced_legacy() && umma_i8_usable(W, x, ldx, T)) {
     const size_t off = gemv_partials_bytes(W.N, W.K), need = i8_digits_bytes(T, W.K);
+    const bool room = scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && scratch_bytes >= off + need;
+    if (i8_fused_preferred(W, T) || (!room && T <= umma_i8_fused_tokens())) return launch_umma_i8(W, x, ldx, y, T, beta, nullptr, st);
     if (scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && scratch_bytes >= off + need) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + off, st);
     void* tmp = nullptr;  // no caller buffer: stream-ordered allocation, released behind the kernels
     RB_CUDA(cudaMallocAsync(&tmp, need, st));

@@ -101,6 +101,9 @@ int umma_gemm_status();
 // aligned) by a first kernel, the second multiplies the raw int8 weight tiles by them.
 size_t i8_digits_bytes(int T, int K);
 bool umma_i8_usable(const WeightView& W, const __half* x, int ldx, int T);
+// Up to this many tokens the GEMM makes the digits itself and `scratch` may be null (0 when
+// RB200_I8_FUSED=0 turns that off).
+int umma_i8_fused_tokens();
 void launch_umma_i8(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch, cudaStream_t st);
 
 }  // namespace rb200

@@ -48,7 +48,7 @@ struct I8Smem {
   static constexpr int kStages = 196 * 1024 / kStageBytes > 10 ? 10 : 196 * 1024 / kStageBytes;
   static constexpr int kAccCols = kDigits * BN;
   static constexpr int kTmemCols = kAccCols <= 64 ? 64 : (kAccCols <= 128 ? 128 : 256);
-  static constexpr int kBarBytes = 256;
+  static constexpr int kBarBytes = 512;  // barriers, the TMEM slot, the fused digit pass's row maxima
   static constexpr size_t kTotal = static_cast<size_t>(kStages) * kStageBytes + kBarBytes + 1024;
 };
 
@@ -98,10 +98,11 @@ __device__ __forceinline__ float abs_max8(const uint4& v) {
   return fmaxf(__low2float(m), __high2float(m));
 }
 
-// Eight halves -> eight bytes of each digit plane.
-__device__ __forceinline__ void store_digits8(const uint4& v, float up, int8_t* out, long long plane) {
+// Eight halves -> eight bytes (two words) of each digit.
+__device__ __forceinline__ void digits8(const uint4& v, float up, uint32_t (&w)[kDigits][2]) {
   const __half* h = reinterpret_cast<const __half*>(&v);
-  uint32_t w[kDigits][2] = {};
+#pragma unroll
+  for (int g = 0; g < kDigits; ++g) w[g][0] = w[g][1] = 0u;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     int X = __float2int_rn(__half2float(h[i]) * up);  // |X| < 2^20
@@ -113,8 +114,22 @@ __device__ __forceinline__ void store_digits8(const uint4& v, float up, int8_t* 
       X = (X - d) >> 7;
     }
   }
+}
+
+__device__ __forceinline__ void store_digits8(const uint4& v, float up, int8_t* out, long long plane) {
+  uint32_t w[kDigits][2];
+  digits8(v, up, w);
 #pragma unroll
   for (int g = 0; g < kDigits; ++g) *reinterpret_cast<uint2*>(out + g * plane) = make_uint2(w[g][0], w[g][1]);
+}
+
+// The row's scale pair from its largest magnitude: 2^e > mx (frexp: mx = m 2^e with m in
+// [0.5, 1)); exact powers of two; an all-zero row keeps scale 0.
+__device__ __forceinline__ void digit_scales(float mx, float& up, float& down) {
+  int e = 0;
+  if (mx > 0.f) frexpf(mx, &e);
+  up = mx > 0.f ? ldexpf(1.0f, kFracBits - e) : 0.f;
+  down = mx > 0.f ? ldexpf(1.0f, e - kFracBits) : 0.f;
 }
 
 // One block per token. digits[d][t][k] (row pitch K), tscale[t] = 2^(e-20). K is a multiple of 8.
@@ -142,11 +157,9 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_tokens_kernel(const __
   mx = s_max[0];
 #pragma unroll
   for (int w = 1; w < kQuantThreads / 32; ++w) mx = fmaxf(mx, s_max[w]);
-  // 2^e > mx (frexp: mx = m 2^e with m in [0.5, 1)); an all-zero row keeps scale 0
-  int e = 0;
-  if (mx > 0.f) frexpf(mx, &e);
-  const float up = mx > 0.f ? ldexpf(1.0f, kFracBits - e) : 0.f;  // exact powers of two
-  if (threadIdx.x == 0) tscale[t] = mx > 0.f ? ldexpf(1.0f, e - kFracBits) : 0.f;
+  float up, down;
+  digit_scales(mx, up, down);
+  if (threadIdx.x == 0) tscale[t] = down;
   const long long plane = static_cast<long long>(T) * K;
   int8_t* out = digits + static_cast<long long>(t) * K;
 #pragma unroll
@@ -158,11 +171,18 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_tokens_kernel(const __
 }
 
 // ---- the GEMM -----------------------------------------------------------------------------
-template <int BN>
+// FUSED (at most kFusedTokens tokens): no digit buffer and no kernel ahead. The four epilogue
+// warps, idle during the main loop otherwise, find each token row's largest magnitude (every
+// CTA reads the few activation rows from L2) and then write the digit tile of each k block
+// straight into the ring in the 128-byte-swizzled layout the MMA reads, one warp per k block
+// in turn; the stage's barrier takes the weight tile's bytes and that warp's arrival.
+constexpr int kFusedTokens = 4;
+
+template <int BN, bool FUSED>
 __global__ void __launch_bounds__(kI8Threads, 1)
 umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_q,
-               const float* __restrict__ scale, const float* __restrict__ tscale, float* __restrict__ y, int T, int N, int K,
-               int rows, float beta, int* __restrict__ status) {
+               const float* __restrict__ scale, const float* __restrict__ tscale, const __half* __restrict__ x, int ldx,
+               float* __restrict__ y, int T, int N, int K, int rows, float beta, int* __restrict__ status) {
   using S = I8Smem<BN>;
   constexpr int NS = S::kStages;
   constexpr uint32_t kTmemCols = S::kTmemCols;
@@ -176,13 +196,14 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t empty_bar = bars + 8 * NS;  // NS x 8: the MMAs have read the stage
   const uint32_t accum_bar = bars + 16 * NS;
   const uint32_t tmem_slot = accum_bar + 8;
+  const uint32_t rowmax_slot = accum_bar + 16;  // FUSED: [4 warps][kFusedTokens] floats
   unsigned char* gen_base = smem_dyn + (base - smem_u32(smem_dyn));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // `rows` (a multiple of 8, at most 128) weight rows per CTA: the host shrinks the tile so that
   // the grid fills the SMs evenly; the MMA still spans 128 lanes and the rest is ignored.
   const int m0 = blockIdx.x * rows, tok0 = blockIdx.y * BN;
-  const uint32_t stage_tx = static_cast<uint32_t>(rows) * kBlockKB + S::kBBytes;
+  const uint32_t stage_tx = static_cast<uint32_t>(rows) * kBlockKB + (FUSED ? 0 : S::kBBytes);
   const int splits = gridDim.z, split = blockIdx.z;  // the cluster spans z: split == rank in the cluster
   const int nk_all = (K + kBlockKB - 1) / kBlockKB;  // a last half block reads zeros past K
   const int kb_begin = static_cast<int>(static_cast<long long>(nk_all) * split / splits);
@@ -191,9 +212,9 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int pre = min(nk, NS);  // the ring starts empty: stages the producer fills without waiting
   if (warp == 0 && lane == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
+    if (!FUSED) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
     for (int s = 0; s < NS; ++s) {
-      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(full_bar + 8 * s, FUSED ? 2 : 1);
       mbar_init(empty_bar + 8 * s, 1);
     }
     mbar_init(accum_bar, 1);
@@ -216,13 +237,16 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - base));
 
   bool ok = true;
+  float ts[kFusedTokens] = {};  // FUSED: the token scales, known to warps 2-5
   if (warp == 0) {
     if (elect_one()) {
       // The weight tiles of the first stages are already in flight; their digit tiles follow once
       // the kernel that writes the digits (it may still be running) has finished.
-      pdl_wait();
-      for (int kb = 0; kb < pre; ++kb)
-        tma_load_3d(sB + kb * S::kBBytes, &map_q, (kb_begin + kb) * kBlockKB, tok0, 0, full_bar + 8 * kb);
+      if (!FUSED) {
+        pdl_wait();
+        for (int kb = 0; kb < pre; ++kb)
+          tma_load_3d(sB + kb * S::kBBytes, &map_q, (kb_begin + kb) * kBlockKB, tok0, 0, full_bar + 8 * kb);
+      }
       for (int kb = pre; kb < nk && ok; ++kb) {
         const int s = kb % NS;
         ok = mbar_wait(empty_bar + 8 * s, ((kb / NS) & 1) ^ 1);
@@ -230,7 +254,7 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         mbar_expect_tx(full_bar + 8 * s, stage_tx);
         const int kx = (kb_begin + kb) * kBlockKB;
         tma_load_2d(sA + s * S::kABytes, &map_w, kx, m0, full_bar + 8 * s);
-        tma_load_3d(sB + s * S::kBBytes, &map_q, kx, tok0, 0, full_bar + 8 * s);
+        if (!FUSED) tma_load_3d(sB + s * S::kBBytes, &map_q, kx, tok0, 0, full_bar + 8 * s);
       }
       if (!ok) atomicExch(status, 21);
     }
@@ -252,7 +276,94 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!ok) atomicExch(status, 22);
     }
   } else {
-    pdl_wait();  // token scales (and, with beta, y) come from kernels before this one
+    if (FUSED) {
+      const int pw = warp - 2, ptid = static_cast<int>(threadIdx.x) - 64;
+      // Token rows T..BN-1 of every digit tile stay zero; rows below T are rewritten per k block.
+      uint4* bz = reinterpret_cast<uint4*>(gen_base + (sB - base));
+      for (int i = ptid; i < NS * S::kBBytes / 16; i += 128) bz[i] = make_uint4(0u, 0u, 0u, 0u);
+      fence_async_smem();
+      pdl_wait();  // the activations (and, with beta, y) come from kernels before this one
+      float* rowmax = reinterpret_cast<float*>(gen_base + (rowmax_slot - base));
+      // A lane owns 16 consecutive k of one token: one 16-byte chunk of each digit's row.
+      const int tok = lane >> 3, ch = lane & 7;
+      const bool has = tok < T;
+      const __half* xrow = x + static_cast<long long>(tok) * ldx + ch * 16;
+      uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
+      auto fetch = [&](int kb, uint4& lo, uint4& hi) {
+        const int k = (kb_begin + kb) * kBlockKB;
+        lo = hi = make_uint4(0u, 0u, 0u, 0u);
+        if (has && k + ch * 16 < K) {  // a last half block: nothing past K is read
+          const uint4* p = reinterpret_cast<const uint4*>(xrow + k);
+          lo = p[0];
+          hi = p[1];
+        }
+      };
+      if (pw < nk) fetch(pw, a, b);  // in flight with the loads of the pass below
+      const int pieces = K / 8;
+      {
+        // Largest magnitude of each token row; the loads of all rows go out together (L2 latency,
+        // not bandwidth, is what this pass costs).
+        float mx[kFusedTokens] = {};
+        const uint4* row0 = reinterpret_cast<const uint4*>(x);
+        const long long pitch = ldx / 8;
+        for (int i0 = ptid; i0 < pieces; i0 += 128 * 8) {
+          uint4 v[8][kFusedTokens];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+#pragma unroll
+            for (int t = 0; t < kFusedTokens; ++t) {
+              const int i = i0 + u * 128;
+              v[u][t] = (t < T && i < pieces) ? row0[t * pitch + i] : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+#pragma unroll
+            for (int t = 0; t < kFusedTokens; ++t) mx[t] = fmaxf(mx[t], abs_max8(v[u][t]));
+        }
+#pragma unroll
+        for (int t = 0; t < kFusedTokens; ++t) {
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) mx[t] = fmaxf(mx[t], __shfl_xor_sync(0xffffffffu, mx[t], o));
+          if (lane == 0) rowmax[pw * kFusedTokens + t] = mx[t];
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // warps 2-5: the zeroed tiles and the row maxima
+      float ups[kFusedTokens];
+#pragma unroll
+      for (int t = 0; t < kFusedTokens; ++t) {
+        float mx = 0.f;
+        mx = fmaxf(fmaxf(rowmax[t], rowmax[kFusedTokens + t]), fmaxf(rowmax[2 * kFusedTokens + t], rowmax[3 * kFusedTokens + t]));
+        digit_scales(mx, ups[t], ts[t]);
+      }
+      const float up = tok == 0 ? ups[0] : tok == 1 ? ups[1] : tok == 2 ? ups[2] : ups[3];
+      const uint32_t dst0 = sB + static_cast<uint32_t>(tok) * kBlockKB + static_cast<uint32_t>((ch ^ (tok & 7)) << 4);
+      for (int kb = pw; kb < nk; kb += 4) {
+        uint4 na = make_uint4(0u, 0u, 0u, 0u), nb = na;
+        if (kb + 4 < nk) fetch(kb + 4, na, nb);
+        const int s = kb % NS;
+        if (kb >= NS) ok = mbar_wait(empty_bar + 8 * s, ((kb / NS) & 1) ^ 1);  // the MMAs have read the tile this overwrites
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (has) {
+          uint32_t lo[kDigits][2], hi[kDigits][2];
+          digits8(a, up, lo);
+          digits8(b, up, hi);
+#pragma unroll
+          for (int g = 0; g < kDigits; ++g)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + s * S::kBBytes + g * BN * kBlockKB), "r"(lo[g][0]),
+                         "r"(lo[g][1]), "r"(hi[g][0]), "r"(hi[g][1])
+                         : "memory");
+        }
+        fence_async_smem();  // generic-proxy writes, read by the MMA through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar + 8 * s);
+        a = na;
+        b = nb;
+      }
+      if (!ok && lane == 0) atomicExch(status, 25);
+    } else {
+      pdl_wait();  // token scales (and, with beta, y) come from kernels before this one
+    }
     const bool done = mbar_wait(accum_bar, 0);
     if (!done) atomicExch(status, 24);
     tc_fence_after();
@@ -286,7 +397,7 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int j = 0; j < 16; ++j) old[j] = (beta != 0.f && j < nt) ? dst[static_cast<long long>(j) * N] : 0.f;
 #pragma unroll
         for (int j = 0; j < 16; ++j)
-          if (j < nt) dst[static_cast<long long>(j) * N] = v[j] * (sc * tscale[tok0 + c0 + j]) + beta * old[j];
+          if (j < nt) dst[static_cast<long long>(j) * N] = v[j] * (sc * (FUSED ? ts[j & (kFusedTokens - 1)] : tscale[tok0 + c0 + j])) + beta * old[j];
       }
     }
   }
@@ -315,7 +426,8 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (live) {
           float* dst = y + static_cast<long long>(tok0 + c) * N + n;
           const float old = beta != 0.f ? *dst : 0.f;
-          *dst = acc * (sc * tscale[tok0 + c]) + beta * old;
+          const float tsc = !FUSED ? tscale[tok0 + c] : c == 0 ? ts[0] : c == 1 ? ts[1] : c == 2 ? ts[2] : ts[3];
+          *dst = acc * (sc * tsc) + beta * old;
         }
       }
     }
@@ -329,11 +441,12 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 }
 
-template <int BN>
-void launch_i8_t(const WeightView& W, const int8_t* digits, const float* tscale, float* y, int T, float beta, cudaStream_t st) {
+template <int BN, bool FUSED>
+void launch_i8_t(const WeightView& W, const int8_t* digits, const float* tscale, const __half* x, int ldx, float* y, int T,
+                 float beta, cudaStream_t st) {
   using S = I8Smem<BN>;
   static bool configured = false;
-  auto kernel = umma_i8_kernel<BN>;
+  auto kernel = umma_i8_kernel<BN, FUSED>;
   if (!configured) {
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
     configured = true;
@@ -386,7 +499,8 @@ void launch_i8_t(const WeightView& W, const int8_t* digits, const float* tscale,
   }();
   if (forced > 0) splits = std::min({forced, 8, std::max(1, nk)});
   const CUtensorMap mw = make_map(W.i8, 1, W.N, W.K, W.ld, rows, kBlockKB, true);
-  const CUtensorMap mq = make_map_3d(digits, W.K, T, kDigits, W.K, static_cast<long long>(T) * W.K, kBlockKB, BN, kDigits);
+  CUtensorMap mq{};  // FUSED: the kernel makes the digit tiles itself
+  if (!FUSED) mq = make_map_3d(digits, W.K, T, kDigits, W.K, static_cast<long long>(T) * W.K, kBlockKB, BN, kDigits);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(div_up(W.N, rows), ttiles, splits);
   cfg.blockDim = dim3(kI8Threads);
@@ -397,7 +511,7 @@ void launch_i8_t(const WeightView& W, const int8_t* digits, const float* tscale,
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = splits;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start under quantize_tokens_kernel
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start under the kernel ahead
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
@@ -405,7 +519,7 @@ void launch_i8_t(const WeightView& W, const int8_t* digits, const float* tscale,
   int* status = status_word();
   const float* scale = W.scale;
   const int N = W.N, K = W.K;
-  RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, mw, mq, scale, tscale, y, T, N, K, rows, beta, status));
+  RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, mw, mq, scale, tscale, x, ldx, y, T, N, K, rows, beta, status));
 }
 
 }  // namespace
@@ -424,15 +538,28 @@ bool umma_i8_usable(const WeightView& W, const __half* x, int ldx, int T) {
          (reinterpret_cast<uintptr_t>(W.i8) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
 }
 
+int umma_i8_fused_tokens() {
+  static const bool off = [] {
+    const char* e = std::getenv("RB200_I8_FUSED");
+    return e && std::string(e) == "0";
+  }();
+  return off ? 0 : kFusedTokens;
+}
+
 void launch_umma_i8(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch, cudaStream_t st) {
   if (T == 0) return;
+  // Without a digit buffer the GEMM makes the digits itself (few tokens only).
+  if (scratch == nullptr) {
+    RB_REQUIRE(T <= umma_i8_fused_tokens(), "int8 linear: the digit buffer is missing");
+    return launch_i8_t<16, true>(W, nullptr, nullptr, x, ldx, y, T, beta, st);
+  }
   int8_t* digits = static_cast<int8_t*>(scratch);
   float* tscale = reinterpret_cast<float*>(digits + (static_cast<size_t>(kDigits) * T * W.K + 15) / 16 * 16);
   count_launch();
   launch_pdl(quantize_tokens_kernel, dim3(T), dim3(kQuantThreads), 0, st, x, ldx, W.K, T, digits, tscale);
-  if (T <= 16) launch_i8_t<16>(W, digits, tscale, y, T, beta, st);
-  else if (T <= 32) launch_i8_t<32>(W, digits, tscale, y, T, beta, st);
-  else launch_i8_t<64>(W, digits, tscale, y, T, beta, st);
+  if (T <= 16) launch_i8_t<16, false>(W, digits, tscale, x, ldx, y, T, beta, st);
+  else if (T <= 32) launch_i8_t<32, false>(W, digits, tscale, x, ldx, y, T, beta, st);
+  else launch_i8_t<64, false>(W, digits, tscale, x, ldx, y, T, beta, st);
 }
 
 }  // namespace rb200

@@ -317,7 +317,7 @@ def linear_oracle(x, y0, w, scale, beta):
 # double: K * 2^-24 relative to sum|w x| in the worst case; 1e-4 of the row's largest output.
 LINEAR_TOL = 1e-4
 
-GEMV_SHAPES = [(64, 256), (192, 64), (4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096), (4096, 1000), (128, 72)]
+GEMV_SHAPES = [(64, 256), (192, 64), (4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096), (4096, 1000), (128, 72), (4160, 1024)]
 
 
 @pytest.mark.parametrize("K,N", GEMV_SHAPES)
@@ -352,10 +352,10 @@ def test_gemm_matches_oracle(ops, K, N, int8):
         assert row_err(y.cpu().numpy(), want) < LINEAR_TOL
 
 
-@pytest.mark.parametrize("T", [1, 5, 16])
+@pytest.mark.parametrize("T", [1, 4, 5, 16])
 def test_int8_linear_with_outlier_zero_and_tiny_activation_rows(ops, T):
     # The int8 few-token kernel rewrites each activation row as fixed-point digits relative to
-    # the row's largest magnitude: rows with one huge outlier, all-zero rows, rows of fp16
+    # the row's largest magnitude (inside the GEMM up to 4 tokens, in a kernel of its own above): rows with one huge outlier, all-zero rows, rows of fp16
     # subnormals and rows at the fp16 maximum must all stay within the linear tolerance.
     K, N = 4096, 4096
     rng = np.random.Generator(np.random.PCG64(5 + T))
@@ -366,15 +366,16 @@ def test_int8_linear_with_outlier_zero_and_tiny_activation_rows(ops, T):
         x[1, 17] = -60000.0
         x[2] = round_f16(rng.standard_normal(K) * 3e-7)  # fp16 subnormals
         x[3] = np.where(rng.random(K) < 0.5, 65504.0, -65504.0) * (rng.random(K) < 0.01)
+    if T > 4:
         x[4, :] = round_f16(rng.standard_normal(K))
         x[4, K - 1] = 2048.0
     wq = rng.integers(-127, 128, (N, K)).astype(np.int8)
     scale = rng.uniform(0.001, 0.02, N).astype(np.float32)
     want = oracle.gemv_int8(wq, scale, x)
     y = torch.zeros((T, N), device="cuda")
-    if T <= 8:
+    if T in (1, 5):
         ops.gemv_int8(dev(wq), dev(scale), dev(x, torch.float16), y, 0.0, ops.gemv_scratch(N, K))
-    else:
+    else:  # no scratch: 4 tokens take the kernel that makes the digits itself
         ops.gemm(dev(wq), dev(x, torch.float16), y, 0.0, dev(scale))
     torch.cuda.synchronize()
     assert ops.gemm_status() == 0
@@ -382,6 +383,23 @@ def test_int8_linear_with_outlier_zero_and_tiny_activation_rows(ops, T):
     assert np.array_equal(got[0], np.zeros(N, np.float32))  # a zero row gives exact zeros
     assert np.isfinite(got).all()
     assert row_err(got[1:], want[1:]) < LINEAR_TOL if T > 1 else True
+
+
+@pytest.mark.parametrize("K,N", [(4160, 1024), (4096, 4096), (14336, 4096), (4096, 14336)])
+def test_int8_few_tokens_without_scratch_make_their_digits_in_the_kernel(ops, K, N):
+    # Up to 4 tokens and no digit buffer: the CTAs find the row maxima and write the digit tiles
+    # into the shared-memory ring themselves (K = 4160 ends in a half k block; 4096 -> 4096 and
+    # 14336 -> 4096 split K over a cluster).
+    for T, beta in [(1, 1.0), (3, 0.0), (4, 1.0)]:
+        x, y0, wq, scale = linear_case(K + N + T + 7, T, K, N, True)
+        want = linear_oracle(x, y0, wq, scale, beta)
+        y = dev(y0)
+        ops.gemm(dev(wq), dev(x, torch.float16), y, beta, dev(scale))
+        torch.cuda.synchronize()
+        assert ops.gemm_status() == 0
+        assert row_err(y.cpu().numpy(), want) < LINEAR_TOL
+        again = ops.gemm(dev(wq), dev(x, torch.float16), dev(y0), beta, dev(scale))
+        assert torch.equal(again, y)
 
 
 def test_gemv_and_gemm_agree_and_are_deterministic(ops):
