@@ -14,6 +14,9 @@
 // kernel is the plain TMA -> shared-memory ring -> MMA -> TMEM pipeline and runs at the speed
 // the int8 bytes arrive from HBM.
 //
+// Up to four tokens the GEMM can also make the digit tiles itself (FUSED below): no kernel
+// ahead of it, no digit buffer.
+//
 // Warp roles as in umma_gemm.cu: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner,
 // warps 2-5 epilogue (combine the digits in fp32, row scale x token scale, beta*y). Matrices
 // with few 128-row tiles split K over a thread-block cluster and add the partial tiles over
