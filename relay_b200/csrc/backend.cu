@@ -440,8 +440,10 @@ void Backend::enqueue(const Plan& p, rb200_layer_cb cb, void* cb_ctx, bool argma
     Layer& L = layers_[l];
     __half* kc = kc_.as<__half>() + static_cast<size_t>(l) * layer_elems();
     __half* vc = vc_.as<__half>() + static_cast<size_t>(l) * layer_elems();
-    launch_rmsnorm(x, nullptr, L.attn_norm.as<float>(), xn, T, H, Hp_, eps, stream_);
-    launch_linear(L.wqkv.view(), xn, Hp_, qkv, T, 0.0f, gs, gsb, stream_);
+    // Where the projection behind a norm reads its input as int8 digits, the norm writes them.
+    const I8Digits dq = H % 4 == 0 ? linear_digits_dest(L.wqkv.view(), xn, Hp_, T, gs, gsb) : I8Digits{};
+    launch_rmsnorm(x, nullptr, L.attn_norm.as<float>(), xn, T, H, Hp_, eps, stream_, dq);
+    launch_linear(L.wqkv.view(), xn, Hp_, qkv, T, 0.0f, gs, gsb, stream_, dq.digits != nullptr);
     launch_qkv_post(qkv, c_.qkv_bias ? L.bqkv.as<float>() : nullptr, inv_freq_.as<float>(), meta, T, kc, vc, c_.heads,
                     c_.kv_heads, D, bs, stream_);
     // This layer's K and V are enqueued; a transfer thread may wait on the event and read
@@ -464,8 +466,9 @@ void Backend::enqueue(const Plan& p, rb200_layer_cb cb, void* cb_ctx, bool argma
       launch_reference_attention(shape, qkv, meta, T, kc, vc, attn, stream_);
     }
     launch_linear(L.wo.view(), attn, Qp_, x, T, 1.0f, gs, gsb, stream_);  // x += attn wo^T
-    launch_rmsnorm(x, nullptr, L.mlp_norm.as<float>(), xn, T, H, Hp_, eps, stream_);
-    launch_linear(L.w_gate_up.view(), xn, Hp_, gu, T, 0.0f, gs, gsb, stream_);
+    const I8Digits dm = H % 4 == 0 ? linear_digits_dest(L.w_gate_up.view(), xn, Hp_, T, gs, gsb) : I8Digits{};
+    launch_rmsnorm(x, nullptr, L.mlp_norm.as<float>(), xn, T, H, Hp_, eps, stream_, dm);
+    launch_linear(L.w_gate_up.view(), xn, Hp_, gu, T, 0.0f, gs, gsb, stream_, dm.digits != nullptr);
     launch_silu_mul(gu, act, T, I, Ip_, stream_);
     launch_linear(L.w_down.view(), act, Ip_, x, T, 1.0f, gs, gsb, stream_);  // x += act w_down^T
   }

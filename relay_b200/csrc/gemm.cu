@@ -463,8 +463,26 @@ static void check_linear(const WeightView& W, int ldx, int T) {
   RB_REQUIRE(T >= 0, "linear: bad token count");
 }
 
+I8Digits linear_digits_dest(const WeightView& W, const __half* x, int ldx, int T, void* scratch, size_t scratch_bytes) {
+  static const bool off = [] {
+    const char* e = std::getenv("RB200_NORM_DIGITS");
+    return e && std::string(e) == "0";
+  }();
+  // The conditions under which launch_linear reads digits from `scratch` (below), and rows whose
+  // pitch is the digit planes' pitch.
+  if (off || !W.i8 || gemm_forced_legacy() || T < 1 || T > 16 || ldx != W.K || !umma_i8_usable(W, x, ldx, T)) return {};
+  if (T <= 8 && !i8_digits_preferred(W)) return {};
+  const size_t po = gemv_partials_bytes(W.N, W.K);
+  const bool room = scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && scratch_bytes >= po + i8_digits_bytes(T, W.K);
+  if (!room || i8_fused_preferred(W, T)) return {};
+  I8Digits d;
+  d.digits = reinterpret_cast<int8_t*>(static_cast<char*>(scratch) + po);
+  d.tscale = i8_tscale(d.digits, T, W.K);
+  return d;
+}
+
 void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch,
-                 size_t scratch_bytes, cudaStream_t st) {
+                 size_t scratch_bytes, cudaStream_t st, bool digits_ready) {
   check_linear(W, ldx, T);
   RB_REQUIRE(T <= 8, "gemv: at most 8 tokens");
   if (T == 0) return;
@@ -476,7 +494,7 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
                       scratch_bytes >= gemv_partials_bytes(W.N, W.K) + i8_digits_bytes(T, W.K);
     if (i8_fused_preferred(W, T) || (!room && T <= umma_i8_fused_tokens()))
       return launch_umma_i8(W, x, ldx, y, T, beta, nullptr, st);  // digits made in the kernel
-    if (room) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + gemv_partials_bytes(W.N, W.K), st);
+    if (room) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + gemv_partials_bytes(W.N, W.K), st, digits_ready);
   }
   unsigned* counters = static_cast<unsigned*>(scratch);
   float* partials = scratch ? reinterpret_cast<float*>(static_cast<char*>(scratch) + gemv_counter_bytes(W.N)) : nullptr;
@@ -497,7 +515,7 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
 }
 
 void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st, void* scratch,
-                 size_t scratch_bytes) {
+                 size_t scratch_bytes, bool digits_ready) {
   check_linear(W, ldx, T);
   if (T == 0) return;
   // Above 16 tokens the digit tiles (three bytes per activation) crowd the weight tiles out of
@@ -508,7 +526,7 @@ void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T,
     const size_t off = gemv_partials_bytes(W.N, W.K), need = i8_digits_bytes(T, W.K);
     const bool room = scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && scratch_bytes >= off + need;
     if (i8_fused_preferred(W, T) || (!room && T <= umma_i8_fused_tokens())) return launch_umma_i8(W, x, ldx, y, T, beta, nullptr, st);
-    if (scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && scratch_bytes >= off + need) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + off, st);
+    if (room) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + off, st, digits_ready);
     void* tmp = nullptr;  // no caller buffer: stream-ordered allocation, released behind the kernels
     RB_CUDA(cudaMallocAsync(&tmp, need, st));
     launch_umma_i8(W, x, ldx, y, T, beta, tmp, st);
@@ -531,9 +549,9 @@ void launch_gemm_mma_sync(const WeightView& W, const __half* x, int ldx, float* 
 }
 
 void launch_linear(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch,
-                   size_t scratch_bytes, cudaStream_t st) {
-  if (T <= 8) launch_gemv(W, x, ldx, y, T, beta, scratch, scratch_bytes, st);
-  else launch_gemm(W, x, ldx, y, T, beta, st, scratch, scratch_bytes);
+                   size_t scratch_bytes, cudaStream_t st, bool digits_ready) {
+  if (T <= 8) launch_gemv(W, x, ldx, y, T, beta, scratch, scratch_bytes, st, digits_ready);
+  else launch_gemm(W, x, ldx, y, T, beta, st, scratch, scratch_bytes, digits_ready);
 }
 
 }  // namespace rb200

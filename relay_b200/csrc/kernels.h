@@ -29,8 +29,15 @@ constexpr int kPrefillRows = RB200_PREFILL_ROWS;  // query rows per prefill tile
 
 // ---- small_ops.cu ----
 void launch_embed(const int* tokens, const __half* table, float* x, int T, int H, int ld_table, cudaStream_t st);
+// Where a kernel ahead of an int8 linear may leave the activation rows as int8 digits
+// (i8_digits.cuh); null members: nobody does, the linear makes them itself.
+struct I8Digits {
+  int8_t* digits = nullptr;
+  float* tscale = nullptr;
+};
+// `dg` (from linear_digits_dest for the linear that reads `out` next): also write the rows as digits.
 void launch_rmsnorm(const float* x, const int* rows, const float* w, __half* out, int R, int H, int ld_out, float eps,
-                    cudaStream_t st);
+                    cudaStream_t st, I8Digits dg = {});
 void launch_qkv_post(float* qkv, const float* bias, const float* inv_freq, const TokenMeta& m, int T, __half* kc,
                      __half* vc, int heads, int kv_heads, int D, int block_size, cudaStream_t st);
 void launch_silu_mul(const float* gu, __half* act, int T, int I, int ld_act, cudaStream_t st);
@@ -69,14 +76,17 @@ struct WeightView {
 // register GEMV, then room for `max_tokens` activation rows as int8 digits (umma_i8_gemm.cu).
 size_t gemv_scratch_bytes(int N, int K, int max_tokens = 8);
 // y[T,N] = x[T,K] W^T (+ beta*y); routes T <= 8 to the GEMV and larger T to the GEMM.
+// `digits_ready`: the kernel ahead has written the rows of x as digits where
+// linear_digits_dest(same arguments) said (non-null result only).
 void launch_linear(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch,
-                   size_t scratch_bytes, cudaStream_t st);
+                   size_t scratch_bytes, cudaStream_t st, bool digits_ready = false);
+I8Digits linear_digits_dest(const WeightView& W, const __half* x, int ldx, int T, void* scratch, size_t scratch_bytes);
 void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch,
-                 size_t scratch_bytes, cudaStream_t st);
+                 size_t scratch_bytes, cudaStream_t st, bool digits_ready = false);
 // `scratch` (may be null) is the buffer gemv_scratch_bytes(N, K, 64) sizes; without it the int8
 // path for up to 64 tokens takes its digit buffer from the stream's memory pool.
 void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st,
-                 void* scratch = nullptr, size_t scratch_bytes = 0);
+                 void* scratch = nullptr, size_t scratch_bytes = 0, bool digits_ready = false);
 // The same product with legacy mma.sync tiles (any alignment); launch_gemm prefers the
 // tcgen05 kernel of umma_gemm.cu and falls back to this one.
 void launch_gemm_mma_sync(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st);
@@ -104,6 +114,10 @@ bool umma_i8_usable(const WeightView& W, const __half* x, int ldx, int T);
 // Up to this many tokens the GEMM makes the digits itself and `scratch` may be null (0 when
 // RB200_I8_FUSED=0 turns that off).
 int umma_i8_fused_tokens();
-void launch_umma_i8(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch, cudaStream_t st);
+// `digits_ready`: `scratch` already holds the digits and token scales of x (no pass over x).
+void launch_umma_i8(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch, cudaStream_t st,
+                    bool digits_ready = false);
+// The token scales' place behind the three digit planes of a buffer of i8_digits_bytes(T, K).
+float* i8_tscale(int8_t* digits, int T, int K);
 
 }  // namespace rb200

@@ -3,6 +3,7 @@
 // gather/scatter and the greedy-token reduction. Each replaces one small kernel of the
 // reference's CUDA backend (engine/src/cuda_backend.cu:110-270); all are vectorised and
 // bound by HBM traffic or launch latency.
+#include "i8_digits.cuh"
 #include "kernels.h"
 
 namespace rb200 {
@@ -16,6 +17,19 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   __syncthreads();
   float r = lane < nw ? red[lane] : 0.0f;
   r = warp_sum(r);
+  __syncthreads();
+  return r;
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = lane < nw ? red[lane] : 0.0f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, o));
   __syncthreads();
   return r;
 }
@@ -43,8 +57,12 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const __half* __res
 
 // out[r, :] = w * (x[row(r), :] * 1/sqrt(mean(x^2) + eps)) as fp16; columns H..ld_out-1 zero.
 // (engine/src/cuda_backend.cu:157-167; the CPU backend's form is engine/src/cpu_backend.cpp:47-52.)
+// With `digits` (H and ld_out multiples of 4): the fp16 row is also written as the int8 digits
+// the integer tensor-core linear reads (digits[d][r][0..ld_out), tscale[r]; i8_digits.cuh), so
+// that the GEMM behind this kernel needs no pass over the activations of its own.
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
-                               __half* __restrict__ out, int H, int ld_out, float eps) {
+                               __half* __restrict__ out, int H, int ld_out, float eps, int8_t* __restrict__ digits,
+                               float* __restrict__ tscale) {
   pdl_trigger();
   pdl_wait();
   __shared__ float red[32];
@@ -63,6 +81,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
   }
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / static_cast<float>(H) + eps);
+  float mx = 0.0f;  // largest magnitude of the rounded row
   if (vec) {
     for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
       float4 v = *reinterpret_cast<const float4*>(xr + i);
@@ -71,11 +90,29 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
       p.x = pack_half2(g.x * (v.x * inv), g.y * (v.y * inv));
       p.y = pack_half2(g.z * (v.z * inv), g.w * (v.w * inv));
       *reinterpret_cast<uint2*>(o + i) = p;
+      const __half2 m = __hmax2(__habs2(*reinterpret_cast<__half2*>(&p.x)), __habs2(*reinterpret_cast<__half2*>(&p.y)));
+      mx = fmaxf(mx, fmaxf(__low2float(m), __high2float(m)));
     }
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = __float2half_rn(w[i] * (xr[i] * inv));
   }
   for (int i = H + threadIdx.x; i < ld_out; i += blockDim.x) o[i] = __float2half_rn(0.0f);
+  if (digits != nullptr) {  // the whole grid or none of it
+    mx = block_max(mx, red);
+    float up, down;
+    i8d::digit_scales(mx, up, down);
+    if (threadIdx.x == 0) tscale[r] = down;
+    const long long plane = static_cast<long long>(gridDim.x) * ld_out;
+    int8_t* d = digits + static_cast<long long>(r) * ld_out;
+    for (int i = threadIdx.x * 4; i < ld_out; i += blockDim.x * 4) {
+      // i < H: the four halves this thread stored above
+      const uint2 p = i < H ? *reinterpret_cast<const uint2*>(o + i) : make_uint2(0u, 0u);
+      uint32_t dw[i8d::kDigits];
+      i8d::digits4(p, up, dw);
+#pragma unroll
+      for (int g = 0; g < i8d::kDigits; ++g) *reinterpret_cast<uint32_t*>(d + g * plane + i) = dw[g];
+    }
+  }
 }
 
 // Bias, RoPE on the q and k heads in place (pairs (i, i + D/2), angle = pos * inv_freq[i]),
@@ -272,11 +309,12 @@ void launch_embed(const int* tokens, const __half* table, float* x, int T, int H
 }
 
 void launch_rmsnorm(const float* x, const int* rows, const float* w, __half* out, int R, int H, int ld_out, float eps,
-                    cudaStream_t st) {
+                    cudaStream_t st, I8Digits dg) {
   if (R == 0) return;
   const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
   count_launch();
-  launch_pdl(rmsnorm_kernel, dim3(R), dim3(threads), 0, st, x, rows, w, out, H, ld_out, eps);
+  RB_REQUIRE(dg.digits == nullptr || (H % 4 == 0 && ld_out % 4 == 0 && dg.tscale != nullptr), "rmsnorm: digits need rows of whole 4-element groups");
+  launch_pdl(rmsnorm_kernel, dim3(R), dim3(threads), 0, st, x, rows, w, out, H, ld_out, eps, dg.digits, dg.tscale);
 }
 
 void launch_qkv_post(float* qkv, const float* bias, const float* inv_freq, const TokenMeta& m, int T, __half* kc,

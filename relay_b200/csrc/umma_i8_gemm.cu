@@ -28,6 +28,7 @@
 #include <cstdlib>
 #include <string>
 
+#include "i8_digits.cuh"
 #include "kernels.h"
 #include "tcgen05.cuh"
 
@@ -40,8 +41,7 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kBlockKB = 128;  // int8 per k block: one 128-byte swizzle atom
 constexpr int kI8Threads = 192;
-constexpr int kDigits = 3;
-constexpr int kFracBits = 20;  // |fixed-point activation| < 2^20 = 64 * 128^2
+using namespace i8d;
 
 template <int BN>
 struct I8Smem {
@@ -95,44 +95,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 constexpr int kQuantThreads = 512;
 constexpr int kQuantHeld = 4;  // 16-byte pieces of the row a thread keeps in registers between the passes
 
-__device__ __forceinline__ float abs_max8(const uint4& v) {
-  const __half2* h = reinterpret_cast<const __half2*>(&v);
-  const __half2 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
-  return fmaxf(__low2float(m), __high2float(m));
-}
-
-// Eight halves -> eight bytes (two words) of each digit.
-__device__ __forceinline__ void digits8(const uint4& v, float up, uint32_t (&w)[kDigits][2]) {
-  const __half* h = reinterpret_cast<const __half*>(&v);
-#pragma unroll
-  for (int g = 0; g < kDigits; ++g) w[g][0] = w[g][1] = 0u;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    int X = __float2int_rn(__half2float(h[i]) * up);  // |X| < 2^20
-#pragma unroll
-    for (int g = 0; g < kDigits; ++g) {
-      // signed digit in [-64, 63]; the last one takes what is left (|.| <= 64)
-      const int d = g == kDigits - 1 ? X : ((X + 64) & 127) - 64;
-      w[g][i >> 2] |= static_cast<uint32_t>(d & 0xff) << (8 * (i & 3));
-      X = (X - d) >> 7;
-    }
-  }
-}
-
 __device__ __forceinline__ void store_digits8(const uint4& v, float up, int8_t* out, long long plane) {
   uint32_t w[kDigits][2];
   digits8(v, up, w);
 #pragma unroll
   for (int g = 0; g < kDigits; ++g) *reinterpret_cast<uint2*>(out + g * plane) = make_uint2(w[g][0], w[g][1]);
-}
-
-// The row's scale pair from its largest magnitude: 2^e > mx (frexp: mx = m 2^e with m in
-// [0.5, 1)); exact powers of two; an all-zero row keeps scale 0.
-__device__ __forceinline__ void digit_scales(float mx, float& up, float& down) {
-  int e = 0;
-  if (mx > 0.f) frexpf(mx, &e);
-  up = mx > 0.f ? ldexpf(1.0f, kFracBits - e) : 0.f;
-  down = mx > 0.f ? ldexpf(1.0f, e - kFracBits) : 0.f;
 }
 
 // One block per token. digits[d][t][k] (row pitch K), tscale[t] = 2^(e-20). K is a multiple of 8.
@@ -549,7 +516,12 @@ int umma_i8_fused_tokens() {
   return off ? 0 : kFusedTokens;
 }
 
-void launch_umma_i8(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch, cudaStream_t st) {
+float* i8_tscale(int8_t* digits, int T, int K) {
+  return reinterpret_cast<float*>(digits + (static_cast<size_t>(kDigits) * T * K + 15) / 16 * 16);
+}
+
+void launch_umma_i8(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, void* scratch, cudaStream_t st,
+                    bool digits_ready) {
   if (T == 0) return;
   // Without a digit buffer the GEMM makes the digits itself (few tokens only).
   if (scratch == nullptr) {
@@ -557,9 +529,11 @@ void launch_umma_i8(const WeightView& W, const __half* x, int ldx, float* y, int
     return launch_i8_t<16, true>(W, nullptr, nullptr, x, ldx, y, T, beta, st);
   }
   int8_t* digits = static_cast<int8_t*>(scratch);
-  float* tscale = reinterpret_cast<float*>(digits + (static_cast<size_t>(kDigits) * T * W.K + 15) / 16 * 16);
-  count_launch();
-  launch_pdl(quantize_tokens_kernel, dim3(T), dim3(kQuantThreads), 0, st, x, ldx, W.K, T, digits, tscale);
+  float* tscale = i8_tscale(digits, T, W.K);
+  if (!digits_ready) {
+    count_launch();
+    launch_pdl(quantize_tokens_kernel, dim3(T), dim3(kQuantThreads), 0, st, x, ldx, W.K, T, digits, tscale);
+  }
   if (T <= 16) launch_i8_t<16, false>(W, digits, tscale, x, ldx, y, T, beta, st);
   else if (T <= 32) launch_i8_t<32, false>(W, digits, tscale, x, ldx, y, T, beta, st);
   else launch_i8_t<64, false>(W, digits, tscale, x, ldx, y, T, beta, st);

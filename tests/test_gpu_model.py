@@ -307,6 +307,25 @@ def test_llama3_8b_width_layers_match_cpu(mk, int8):
         assert worst_f32 < 1.5 * LOGIT_TOL
 
 
+def test_llama3_8b_width_int8_six_sequence_steps_match_cpu(mk):
+    # Six short sequences: a 6-token decode step is a token count at which every int8 projection
+    # reads its input as int8 digits from a buffer — written by RMSNorm itself for the QKV and
+    # gate/up projections, by the digit pass for the attention-output and down projections.
+    w = llama3_8b_width_model()
+    cfg = w.config
+    rng = np.random.Generator(np.random.PCG64(11))
+    passes, blocks = schedule(cfg, rng, [9, 5, 12, 7, 3, 10], 16, 3, 16)
+    cpu = oracle.cpu_model(dequantised(w), blocks, 16)
+    gpu = mk(w, blocks, 16, max_batch_tokens=64, options=CudaOptions(int8_weights=True))
+    worst = 0.0
+    for p in passes:
+        a, g = cpu.forward(p), gpu.forward(p)
+        worst = max(worst, rel_err_rows(g, a))
+        assert np.array_equal(a.argmax(1), g.argmax(1))
+    print(f"llama3-8b widths, int8, six sequences: rel err vs the held model {worst:.2e}")
+    assert worst < LOGIT_TOL
+
+
 def test_update_weight_equals_construction_and_accepts_device_pointers(mk):
     # tests/test_c_api.cpp (update_tensor == host write): a backend built empty and filled
     # tensor by tensor, half of them from device memory, gives the same bits
