@@ -226,7 +226,8 @@ Backend::Backend(const rb200_model_config& cfg, const rb200_weights* w, int num_
     RB_CUDA(cudaMemcpy(inv_freq_.p, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice));
   }
   layers_.resize(c_.layers);
-  size_t gemv_bytes = std::max(gemv_scratch_bytes(c_.vocab, Hp_, 64), size_t(256));
+  // The largest counters-and-partials region of any matrix, plus the largest digit buffer (64 tokens).
+  size_t gemv_head = std::max(gemv_scratch_bytes(c_.vocab, Hp_, 0), size_t(256)), gemv_digits = i8_digits_bytes(64, Hp_);
   for (Layer& L : layers_) {
     L.attn_norm = DeviceBuf(static_cast<size_t>(H) * 4, true);
     L.mlp_norm = DeviceBuf(static_cast<size_t>(H) * 4, true);
@@ -237,8 +238,11 @@ Backend::Backend(const rb200_model_config& cfg, const rb200_weights* w, int num_
     L.w_down = make_matrix(H, I, q8);
   }
   for (const Matrix* m : {&layers_[0].wqkv, &layers_[0].wo, &layers_[0].w_gate_up, &layers_[0].w_down})
-    gemv_bytes = std::max(gemv_bytes, gemv_scratch_bytes(m->N, m->ld, 64));
-  gemv_scratch_ = DeviceBuf(gemv_bytes, true);
+  {
+    gemv_head = std::max(gemv_head, gemv_scratch_bytes(m->N, m->ld, 0));
+    gemv_digits = std::max(gemv_digits, i8_digits_bytes(64, m->ld));
+  }
+  gemv_scratch_ = DeviceBuf(gemv_head + gemv_digits + 256, true);
 
   if (w) {
     RB_REQUIRE(w->embed && w->final_norm && w->layers, "weights: embed, final_norm and layers are required");

@@ -428,6 +428,13 @@ size_t gemv_scratch_bytes(int N, int K, int max_tokens) {
   return gemv_partials_bytes(N, K) + i8_digits_bytes(max_tokens, K);
 }
 
+// The digits of an int8 linear sit at the END of the caller's scratch (256-byte aligned), the
+// register GEMV's counters and partials at its start: a buffer shared by several matrices (sized
+// for the largest of each) never has one matrix's digits on top of another's counters.
+static size_t digits_offset(size_t scratch_bytes, int T, int K) {
+  return (scratch_bytes - i8_digits_bytes(T, K)) / 256 * 256;
+}
+
 // int8 weights with few tokens: the integer tensor-core kernel once the matrix is large enough
 // to pay for its activation pass (a second small launch); smaller ones stay on the register GEMV.
 static bool i8_digits_preferred(const WeightView& W) {
@@ -476,7 +483,7 @@ I8Digits linear_digits_dest(const WeightView& W, const __half* x, int ldx, int T
   const bool room = scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && scratch_bytes >= po + i8_digits_bytes(T, W.K);
   if (!room || i8_fused_preferred(W, T)) return {};
   I8Digits d;
-  d.digits = reinterpret_cast<int8_t*>(static_cast<char*>(scratch) + po);
+  d.digits = reinterpret_cast<int8_t*>(static_cast<char*>(scratch) + digits_offset(scratch_bytes, T, W.K));
   d.tscale = i8_tscale(d.digits, T, W.K);
   return d;
 }
@@ -494,7 +501,7 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
                       scratch_bytes >= gemv_partials_bytes(W.N, W.K) + i8_digits_bytes(T, W.K);
     if (i8_fused_preferred(W, T) || (!room && T <= umma_i8_fused_tokens()))
       return launch_umma_i8(W, x, ldx, y, T, beta, nullptr, st);  // digits made in the kernel
-    if (room) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + gemv_partials_bytes(W.N, W.K), st, digits_ready);
+    if (room) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + digits_offset(scratch_bytes, T, W.K), st, digits_ready);
   }
   unsigned* counters = static_cast<unsigned*>(scratch);
   float* partials = scratch ? reinterpret_cast<float*>(static_cast<char*>(scratch) + gemv_counter_bytes(W.N)) : nullptr;
@@ -526,7 +533,7 @@ void launch_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T,
     const size_t off = gemv_partials_bytes(W.N, W.K), need = i8_digits_bytes(T, W.K);
     const bool room = scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && scratch_bytes >= off + need;
     if (i8_fused_preferred(W, T) || (!room && T <= umma_i8_fused_tokens())) return launch_umma_i8(W, x, ldx, y, T, beta, nullptr, st);
-    if (room) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + off, st, digits_ready);
+    if (room) return launch_umma_i8(W, x, ldx, y, T, beta, static_cast<char*>(scratch) + digits_offset(scratch_bytes, T, W.K), st, digits_ready);
     void* tmp = nullptr;  // no caller buffer: stream-ordered allocation, released behind the kernels
     RB_CUDA(cudaMallocAsync(&tmp, need, st));
     launch_umma_i8(W, x, ldx, y, T, beta, tmp, st);

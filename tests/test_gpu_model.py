@@ -249,18 +249,31 @@ def dequantised(w: HostWeights) -> HostWeights:
     return HostWeights(w.config, out)
 
 
-@pytest.mark.parametrize("name", ["c1", "d128_g4"])
+# Matrices on both sides of the size at which the int8 few-token linear changes kernels: QKV
+# (1536 x 1024) and attention output (1024 x 1024) stay on the register GEMV, whose counters and
+# partials live at the start of the backend's shared scratch; gate/up (5632 x 1024) and down
+# (1024 x 2816) read int8 digits from the end of the same scratch.
+MIXED_SIZE_CONFIG = ModelConfig(hidden=1024, intermediate=2816, layers=2, heads=8, kv_heads=2, head_dim=128, vocab=512)
+
+
+@pytest.mark.parametrize("name", ["c1", "d128_g4", "mixed_sizes"])
 def test_int8_weights_match_cpu_on_the_dequantised_model(mk, name):
-    w = c1_inputs()[0] if name == "c1" else synthetic(WIDE_CONFIGS[name], 6)
+    if name == "mixed_sizes":
+        w = synthetic(MIXED_SIZE_CONFIG, 6, std=0.02)  # hidden 1024: the weight scale of the Llama-width model
+    else:
+        w = c1_inputs()[0] if name == "c1" else synthetic(WIDE_CONFIGS[name], 6)
     cfg = w.config
     rng = np.random.Generator(np.random.PCG64(8))
     passes, blocks = schedule(cfg, rng, [5, 60, 130], 64, 5, 16)
     cpu = oracle.cpu_model(dequantised(w), blocks, 16)
     gpu = mk(w, blocks, 16, max_batch_tokens=1024, options=CudaOptions(int8_weights=True))
+    worst = 0.0
     for p in passes:
         a, g = cpu.forward(p), gpu.forward(p)
-        assert rel_err_rows(g, a) < LOGIT_TOL
+        worst = max(worst, rel_err_rows(g, a))
         assert np.array_equal(a.argmax(1), g.argmax(1))
+    print(f"int8 {name}: rel err vs the dequantised model {worst:.2e}")
+    assert worst < LOGIT_TOL
 
 
 _WIDTH_MODEL = {}
