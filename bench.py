@@ -251,6 +251,9 @@ def cpu_arm(args, steps: int, warmup: int) -> dict:
     vocabulary (tied head), `cpu_layers` layers, `cpu_seqs` sequences at the same context;
     the full model's step time is extrapolated linearly in layers (stated in `sample`)."""
     from oracle import oracle
+    # every core this process may run on, whatever OMP_NUM_THREADS says (a multi-process launcher
+    # exports OMP_NUM_THREADS=1 to its ranks)
+    threads = oracle.set_threads()
     L, S, ctx, bs = args.cpu_layers, args.cpu_seqs, args.ctx, 16
     cfg = llama3_8b(layers=L, tie=True)
     rng = np.random.Generator(np.random.PCG64(1))
@@ -286,7 +289,7 @@ def cpu_arm(args, steps: int, warmup: int) -> dict:
     oracle.matmul(xr, tensors["embed"])
     head = min(time.perf_counter() - t0, step * 0.9)
     full = (step - head) / L * args.layers + head
-    return {"value": S / full, "unit": "tok/s", "cores": os.cpu_count(), "kind": kind,
+    return {"value": S / full, "unit": "tok/s", "cores": threads, "kind": kind, "sample_seqs": S, "sample_layers": L,
             "sample": f"{S} sequences at context {ctx}, {L} of {args.layers} layers at full width and vocabulary: "
                       f"{step * 1e3:.0f} ms per step measured ({head * 1e3:.0f} ms of it the LM head); layers scaled "
                       f"linearly to {args.layers} -> {full * 1e3:.0f} ms per {S}-token step",
@@ -332,6 +335,9 @@ def op_suite(peak_gbs: float, peak_tflops: float, only=None, int8_case=None, cpu
     from tests.workloads import c2_contexts
     out = {}
     dev = "cuda"
+    if cpu:
+        from oracle import oracle
+        oracle.set_threads()  # all the cores this process may use, whatever OMP_NUM_THREADS says
     want = lambda name: only is None or name in only  # --ops: a subset, for profiler captures of one kernel
     if want("decode"):
         out.update(_op_decode(ops, torch, np, c2_contexts, peak_gbs, cpu))
@@ -382,7 +388,7 @@ def _op_decode(ops, torch, np, c2_contexts, peak_gbs, cpu=False):
         t0 = time.perf_counter()
         oracle.attention(q.cpu().numpy(), q.shape[1], np.asarray(pos, np.int32), np.asarray(seq, np.int32),
                          np.asarray(toff, np.int32), np.asarray([remap[b] for b in tables], np.int32), kh, vh, heads, kvh, D, bs)
-        out["paged_decode_attention"].update(cpu_us=(time.perf_counter() - t0) * 1e6, cpu_cores=os.cpu_count())
+        out["paged_decode_attention"].update(cpu_us=(time.perf_counter() - t0) * 1e6, cpu_cores=oracle.set_threads())
     return out
 
 
@@ -412,7 +418,7 @@ def _op_int8(ops, torch, peak_gbs, case=None, cpu=False):
                 wh, sh, xh = Ws[0].cpu().numpy(), sc.cpu().numpy(), x.float().cpu().numpy()
                 t0 = time.perf_counter()
                 oracle.gemv_int8(wh, sh, xh)
-                lin[f"{K}->{N} T={T}"].update(cpu_us=(time.perf_counter() - t0) * 1e6, cpu_cores=os.cpu_count())
+                lin[f"{K}->{N} T={T}"].update(cpu_us=(time.perf_counter() - t0) * 1e6, cpu_cores=oracle.set_threads())
         del Ws
     return lin
 
@@ -450,7 +456,7 @@ def _op_prefill(ops, torch, peak_tflops, cpu=False):
         for c in range(4):  # the same four chunks (the queries repeat; the CPU time does not depend on their values)
             oracle.attention(qh, qh.shape[1], np.arange(512 * c, 512 * (c + 1), dtype=np.int32), np.zeros(512, np.int32),
                              np.zeros(1, np.int32), np.arange(nblk, dtype=np.int32), kh, vh, heads, kvh, D, bs)
-        out["flash_prefill_attention"].update(cpu_us=(time.perf_counter() - t0) * 1e6, cpu_cores=os.cpu_count())
+        out["flash_prefill_attention"].update(cpu_us=(time.perf_counter() - t0) * 1e6, cpu_cores=oracle.set_threads())
     return out
 
 
@@ -479,25 +485,16 @@ def _op_prefill_long(ops, torch, peak_tflops):
 
 # ---- the GPU arm ---------------------------------------------------------------------------
 
-def gpu_arm(args) -> dict:
-    import torch
-    import torch.distributed as dist
-    from relay_b200 import _lib
+def build_backend(args, torch, local: int, rank: int, int8: bool):
+    """A Llama-3-8B-shaped backend with random-init weights (N(0, 0.02), norm weights around 1)
+    generated on the device and a KV cache full of N(0,1) pages."""
     from relay_b200.backend import Backend
     from relay_b200.types import CudaOptions
-
-    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    affinity = bind_to_gpu_cores(local) if world > 1 else None
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-
     cfg = llama3_8b(layers=args.layers)
     bs, seqs, ctx = 16, args.seqs, args.ctx
     per = (ctx + bs - 1) // bs
     be = Backend(cfg, None, seqs * per, bs, device=local, max_batch_tokens=max(seqs, PREFILL_CHUNK), max_context=ctx,
-                 options=CudaOptions(int8_weights=args.int8))
+                 options=CudaOptions(int8_weights=int8))
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1000 + rank)
     for name, shape in tensor_shapes(cfg).items():
@@ -508,6 +505,35 @@ def gpu_arm(args) -> dict:
         del t
     torch.cuda.empty_cache()
     be.debug_fill_kv(77 + rank)
+    return cfg, be
+
+
+def step_bytes_of(cfg, seqs: int, ctx: int, bs: int, int8: bool) -> tuple:
+    """(decode-attention bytes of one layer's launch, bytes of the whole step) the algorithm must move."""
+    attn = seqs * ctx * (2 * cfg.kv_heads * cfg.head_dim * 2) + seqs * cfg.heads * cfg.head_dim * (4 + 2) + \
+        seqs * ((ctx + bs - 1) // bs) * 4
+    shapes = tensor_shapes(cfg)
+    layer_w = sum(int(np.prod(s)) for n, s in shapes.items() if n.startswith("layers.") and len(s) == 2)
+    other_w = sum(int(np.prod(s)) for n, s in shapes.items() if n != "embed" and not (n.startswith("layers.") and len(s) == 2))
+    weights = layer_w * (1 if int8 else 2) + other_w * 2  # the LM head and the norms stay fp16 / fp32
+    return attn, attn * cfg.layers + weights
+
+
+def gpu_arm(args) -> dict:
+    import torch
+    import torch.distributed as dist
+    from relay_b200 import _lib
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    affinity = bind_to_gpu_cores(local) if world > 1 else None
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    bs, seqs, ctx = 16, args.seqs, args.ctx
+    per = (ctx + bs - 1) // bs
+    cfg, be = build_backend(args, torch, local, rank, args.int8)
 
     fb = flatten(decode_batch(seqs, ctx, bs, cfg.vocab, 5 + rank))
     logits = torch.empty((seqs, cfg.vocab), dtype=torch.float32).pin_memory()
@@ -546,56 +572,76 @@ def gpu_arm(args) -> dict:
         d["note"] = "the timed region was shorter than the sampler's period: sampled while the same steps ran again, untimed"
         return d
 
+    def host_loop(fn) -> float:
+        """Seconds of args.steps calls of fn by the host clock, barrier + synchronize on both sides, max over ranks."""
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            fn()
+        barrier()
+        return time.perf_counter() - t0
+
     # e2e: the reference-facing call with host buffers, copies inside the timed region
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        be.forward_flat(fb, out=out)
-    barrier()
-    e2e_s = time.perf_counter() - t0
-    clocks_e2e = clocks_of(t0, t0 + e2e_s, lambda: be.forward_flat(fb, out=out))
+    t_start = time.perf_counter()
+    e2e_s = host_loop(lambda: be.forward_flat(fb, out=out))
+    clocks_e2e = clocks_of(t_start, t_start + e2e_s, lambda: be.forward_flat(fb, out=out))
     e2e_s = max_over_ranks(e2e_s)
+    finite = bool(np.isfinite(out).all())
+    host_greedy = out.argmax(axis=1).astype(np.int32)
 
     # the same call returning the greedy token of each row instead of its logits (the device
     # reduces the 128 256-wide rows): 2 KB instead of 131 MB come back per step
-    be.forward_greedy_flat(fb)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        be.forward_greedy_flat(fb)
-    barrier()
-    greedy_s = max_over_ranks(time.perf_counter() - t0)
+    dev_greedy, _ = be.forward_greedy_flat(fb)
+    greedy_s = max_over_ranks(host_loop(lambda: be.forward_greedy_flat(fb)))
+    # the timed step's own output, checked: finite logits, and the device's greedy tokens are the
+    # host argmax (lowest id on ties) of the logits the reference-facing call returned
+    checks = {"logits_finite": finite, "device_greedy_equals_host_argmax_of_logits": bool(np.array_equal(dev_greedy, host_greedy))}
 
     # value: the same passes from device-resident metadata, timed with CUDA events
-    be.set_profiling(True)
-    be.take_profile()
-    barrier()
-    launches0 = L.rb200_kernel_launches()
-    t0 = time.perf_counter()
-    dev_ms = be.forward_replay(args.steps)
-    barrier()
-    t1 = time.perf_counter()
-    launches = L.rb200_kernel_launches() - launches0
-    prof = be.take_profile()
-    be.set_profiling(False)
-    clocks = clocks_of(t0, t1, lambda: be.forward_replay(args.steps))
-    sampler.stop()
-    dev_ms = max_over_ranks(dev_ms)
+    def device_rate(b, fb_any) -> tuple:
+        """(ms per step, launches, profile, clocks) of args.steps replays of fb_any's step on backend b."""
+        for _ in range(3):
+            b.forward_flat(fb_any, out=out)
+        b.set_profiling(True)
+        b.take_profile()
+        barrier()
+        n0 = L.rb200_kernel_launches()
+        t0 = time.perf_counter()
+        ms = b.forward_replay(args.steps)
+        barrier()
+        t1 = time.perf_counter()
+        n1 = L.rb200_kernel_launches()
+        prof = b.take_profile()
+        b.set_profiling(False)
+        ck = clocks_of(t0, t1, lambda: b.forward_replay(args.steps))
+        return max_over_ranks(ms) / args.steps, int(n1 - n0), prof, ck
 
-    ms_per_step = dev_ms / args.steps
+    ms_per_step, launches, prof, clocks = device_rate(be, fb)
     value = seqs * world / (ms_per_step * 1e-3)
     e2e_value = seqs * world / (e2e_s / args.steps)
 
+    # the decode session: positions, block tables and the picked tokens stay on the device, a step
+    # uploads a few hundred bytes and brings the greedy tokens back; steps replay as a CUDA graph
+    session = None
+    n_sess = args.steps + 3
+    if ctx - n_sess > 0:
+        start = ctx - n_sess  # the last timed step stands at position ctx - 1, like the step above
+        be.decode_open([start] * seqs, [fb.tables[i * per:(i + 1) * per] for i in range(seqs)])
+        first = np.asarray(fb.tokens, np.int32)
+        for i in range(3):
+            be.decode_step(tokens=first if i == 0 else None)
+        sess_s = max_over_ranks(host_loop(lambda: be.decode_step(tokens=None)))
+        be.decode_close()
+        session = {"value": seqs * world / (sess_s / args.steps), "unit": "tok/s", "ms_per_step": sess_s / args.steps * 1e3,
+                   "h2d_bytes_per_step": (4 + S4 + (3 * seqs + 3) // 4 * 4 + 8 * seqs) * 4, "d2h_bytes_per_step": seqs * 4,
+                   "note": f"rb200_decode_step, greedy tokens fed back on the device, contexts {start + 4}..{ctx} over the timed steps"}
+
     # decode attention roofline: bytes the algorithm must move per launch (one layer, all sequences)
-    ctxs = [ctx] * seqs
-    attn_bytes = sum(ctxs) * (2 * cfg.kv_heads * cfg.head_dim * 2) + seqs * cfg.heads * cfg.head_dim * (4 + 2) + \
-        sum((c + bs - 1) // bs for c in ctxs) * 4
+    attn_bytes, step_bytes = step_bytes_of(cfg, seqs, ctx, bs, args.int8)
     calls = max(int(prof["decode_attn_calls"]), 1)
     attn_ms = prof["decode_attn_ms"] / calls
     peak, peak_tf, peak_kind = measured_peaks()
     achieved = attn_bytes / (attn_ms * 1e-3) / 1e9 if attn_ms > 0 else 0.0
-    weight_bytes = sum(int(np.prod(s)) for n, s in tensor_shapes(cfg).items() if n != "embed") * (1 if args.int8 else 2)
-    step_bytes = attn_bytes * cfg.layers + weight_bytes
     line = {
         "metric": "decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -610,7 +656,9 @@ def gpu_arm(args) -> dict:
         "e2e_greedy": {"value": seqs * world / (greedy_s / args.steps), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                        "d2h_bytes_per_step": seqs * 8, "ms_per_step": greedy_s / args.steps * 1e3,
                        "note": "rb200_forward_greedy: token id and logit per row instead of the logits"},
-        "gpu_launches": int(launches),
+        "e2e_session": session,
+        "checks": checks,
+        "gpu_launches": launches,
         "roofline": {"kernel": "decode_split_kernel<128> (+ decode_merge_kernel when contexts are split)", "bound": "hbm", "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if peak else None,
                      # DRAM read + write bytes of the kernel from an ncu capture of a 32-sequence launch
@@ -623,13 +671,50 @@ def gpu_arm(args) -> dict:
                           "achieved_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9, "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak},
         "clocks": clocks, "clocks_e2e": clocks_e2e,
     }
+
+    # The strong-scaling reading of the same workload: `seqs` sequences in total, split over the
+    # GPUs. Every replica still reads all of its weights each step, so the ideal speed-up at 8 GPUs
+    # is about 4.7x (fp16), not 8x; the >= 7x target refers to the weak reading above.
+    if seqs % world == 0 and not args.no_strong:
+        s_seqs = seqs // world
+        if world == 1:
+            s_ms = ms_per_step
+        else:
+            s_ms, _, _, _ = device_rate(be, flatten(decode_batch(s_seqs, ctx, bs, cfg.vocab, 5 + rank)))
+        _, s_bytes = step_bytes_of(cfg, s_seqs, ctx, bs, args.int8)
+        line["strong"] = {"value": seqs / (s_ms * 1e-3), "unit": "tok/s", "ms_per_step": s_ms, "seqs_total": seqs,
+                          "seqs_per_gpu": s_seqs,
+                          "step_roofline": {"algorithmic_bytes_per_step": s_bytes, "achieved_gbs": s_bytes / (s_ms * 1e-3) / 1e9,
+                                            "frac": s_bytes / (s_ms * 1e-3) / 1e9 / peak},
+                          "note": "the same step with the sequences of one 256-sequence job divided over the GPUs (device-timed replay)"}
+
     if world == 1 and ctx >= PREFILL_PROMPT:
         line["prefill"] = prefill_pass(be, fb, cfg, bs, out)
     if world >= 2 and ctx >= PREFILL_PROMPT and not args.no_kv_hop:
         line["kv_hop"] = kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch)
-    if world == 1 and not args.no_ops:
-        del be
+    be.close()
+    del be
+    torch.cuda.empty_cache()
+
+    # The int8 reading: the same step with weight-only int8 layer matrices (RB200_INT8_WEIGHTS).
+    if not args.int8 and not args.no_int8:
+        _, be8 = build_backend(args, torch, local, rank, True)
+        i_ms, i_launches, _, i_clocks = device_rate(be8, fb)
+        i_e2e = max_over_ranks(host_loop(lambda: be8.forward_greedy_flat(fb)))
+        _, i_bytes = step_bytes_of(cfg, seqs, ctx, bs, True)
+        line["int8"] = {"value": seqs * world / (i_ms * 1e-3), "unit": "tok/s", "ms_per_step": i_ms, "dtype": "int8w-f16",
+                        "e2e_greedy": {"value": seqs * world / (i_e2e / args.steps), "unit": "tok/s",
+                                       "ms_per_step": i_e2e / args.steps * 1e3},
+                        "gpu_launches": i_launches, "clocks": i_clocks,
+                        "step_roofline": {"algorithmic_bytes_per_step": i_bytes, "achieved_gbs": i_bytes / (i_ms * 1e-3) / 1e9,
+                                          "frac": i_bytes / (i_ms * 1e-3) / 1e9 / peak},
+                        "note": "the same workload with int8 layer matrices (per-row scales), weak reading"}
+        be8.close()
+        del be8
         torch.cuda.empty_cache()
+    sampler.stop()
+
+    if world == 1 and not args.no_ops:
         line["ops"] = op_suite(peak, peak_tf, cpu=not args.no_cpu_baseline)
     if world > 1:
         dist.destroy_process_group()
@@ -653,6 +738,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ops", action="store_true", help="skip the single-kernel measurements")
     ap.add_argument("--no-kv-hop", action="store_true", help="N >= 2: skip the prefill -> decode K/V hop measurement")
+    ap.add_argument("--no-int8", action="store_true", help="skip the int8-weights reading of the step")
+    ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling reading of the step")
     ap.add_argument("--ops-only", action="store_true", help="only the single-kernel measurements (prints their JSON)")
     ap.add_argument("--ops", default=None, help="with --ops-only: comma-separated subset of decode,int8,prefill,prefill_long")
     ap.add_argument("--ops-cpu", action="store_true", help="with --ops-only: also time the CPU restatement of each operator")
@@ -681,8 +768,11 @@ def main() -> None:
         line = {"impl": "reference", "metric": "decode_tok_per_s", "value": cpu["value"], "unit": "tok/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": cpu["ms_per_step_sample"],
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": f"llama3-8b-shape decode step: {args.seqs} sequences per GPU at context "
-                                       f"{args.ctx}, paged KV (block 16), {args.layers} layers, fp16 weights"},
+                "config": {"workload": f"llama3-8b-shape decode step, CPU sample: {cpu['sample_seqs']} sequences at context "
+                                       f"{args.ctx}, paged KV (block 16), {cpu['sample_layers']} of {args.layers} layers measured "
+                                       f"and scaled linearly to {args.layers}, float32 weights (the GPU arm runs {args.seqs} "
+                                       f"sequences per GPU on all {args.layers} layers)",
+                           "same_config": False, "host_threads": cpu["cores"]},
                 "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
                 "e2e": {"value": cpu["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line), flush=True)

@@ -135,6 +135,62 @@ int rb200_forward_greedy(rb200_backend* b, int n_seqs, const int32_t* tokens, co
                          const uint8_t* want_logits, int all_logits, rb200_layer_cb cb, void* cb_ctx,
                          int32_t* token_out, float* logit_out, size_t cap_rows);
 
+/* relay::SamplingParams (engine/include/relay/sampler.h:17-24), the fields the sampler reads,
+ * plus `index`: the request's n-th generated token, which with `seed` fixes the random number
+ * (engine/src/sampler.cpp:9-15), so a row samples the same token alone, in a batch or after
+ * a recompute. */
+typedef struct rb200_sampling_params {
+  float temperature; /* <= 0: greedy */
+  float top_p;       /* 1: no nucleus truncation */
+  int32_t top_k;     /* 0: no limit */
+  int32_t reserved;  /* 0 */
+  uint64_t seed;
+  uint64_t index;
+} rb200_sampling_params;
+
+/* The same forward pass with the sampler run on the device: per logits row, the token relay's
+ * sample() / sample_with_log_prob() pick from that row (engine/src/sampler.cpp:33-72, called
+ * per row by engine/src/engine.cpp:270-282) and, when logprob_out is not NULL, the
+ * log-probability Engine reports with it (float64; relay narrows it to float). `sampling` is a
+ * host array, one entry per logits row. Covered on the device: greedy rows (lowest id on ties)
+ * and temperature sampling without truncation (inverse CDF in id order). A row with top_k in
+ * (0, vocab) or top_p < 1 is refused with an invalid-argument error: such rows need the
+ * vocabulary in sorted order and stay on the host path (rb200_forward + relay's sampler). */
+int rb200_forward_sample(rb200_backend* b, int n_seqs, const int32_t* tokens, const int32_t* chunk_len,
+                         const int32_t* start_pos, const int32_t* table_len, const int32_t* tables,
+                         const uint8_t* want_logits, int all_logits, rb200_layer_cb cb, void* cb_ctx,
+                         const rb200_sampling_params* sampling, int32_t* token_out, double* logprob_out,
+                         size_t cap_rows);
+
+/* ---- decode sessions ------------------------------------------------------------------
+ * The step-with-deltas form of rb200_forward for steady-state decoding. The reference flattens
+ * and uploads every sequence's token, position and whole block table on every step
+ * (engine/src/cuda_backend.cu:508-566, driven by engine/src/engine.cpp:184-202); a session
+ * keeps them on the device and a step brings only what changed. Results are bit-identical to
+ * rb200_forward on the same batch. One session per backend; rb200_forward may be called in
+ * between (for example to prefill a sequence that then takes a slot). */
+
+/* Opens a session of n_seqs slots. Slot s has context_len[s] keys in the cache already (its
+ * next token goes to that position) and table_len[s] block ids, consecutive in `tables`; spare
+ * ids beyond what the context needs are kept for the positions to come. */
+int rb200_decode_open(rb200_backend* b, int n_seqs, const int32_t* context_len, const int32_t* table_len,
+                      const int32_t* tables);
+/* Replaces the sequence in one slot (a finished request's slot taken by a new one). */
+int rb200_decode_set_slot(rb200_backend* b, int slot, int context_len, int table_len, const int32_t* table);
+/* One decode step over every slot. `tokens`: this step's token id per slot, or NULL to feed
+ * each slot the token the previous step picked on the device (no token crosses to the host
+ * and back). `new_block_seq[i]` / `new_block_id[i]`: block ids appended to slots' tables since
+ * the last step (a slot whose context reaches a block boundary needs one: otherwise "block
+ * table too short"). Outputs, each optional: token_out[n_seqs] (picked per `sampling`, host
+ * array of n_seqs entries, NULL = greedy; same rules as rb200_forward_sample), logprob_out
+ * [n_seqs], logits_out [n_seqs][vocab]. Every slot then stands one position further. Steps
+ * of the same launch geometry are replayed as a CUDA graph from their second occurrence on
+ * (RB200_DECODE_GRAPH=0 turns that off). Returns n_seqs, or -1. */
+int rb200_decode_step(rb200_backend* b, const int32_t* tokens, int n_new_blocks, const int32_t* new_block_seq,
+                      const int32_t* new_block_id, const rb200_sampling_params* sampling, int32_t* token_out,
+                      double* logprob_out, float* logits_out, size_t cap_floats);
+int rb200_decode_close(rb200_backend* b);
+
 /* Backend::kv_block_bytes (engine/src/cuda_backend.cu:478): kv_heads * block_size * head_dim * 2. */
 size_t rb200_kv_block_bytes(const rb200_backend* b);
 /* Backend::read_kv_layer / write_kv_layer (backend.h:60-64; engine/src/cuda_backend.cu:630-664):
@@ -192,8 +248,9 @@ int rb200_nccl_finalize(rb200_backend* b);
 /* Enqueue one layer's blocks to / from `peer`; returns once enqueued on the copy stream. */
 int rb200_send_kv_layer(rb200_backend* b, int peer, int layer, const int32_t* blocks, int n);
 int rb200_recv_kv_layer(rb200_backend* b, int peer, int layer, const int32_t* blocks, int n);
-/* Waits for everything enqueued on the copy stream, at most timeout_ms (<= 0: no limit);
- * on timeout the communicator is aborted and -1 returned. */
+/* Waits for everything enqueued on the copy stream, at most timeout_ms (<= 0: 60 s); on
+ * timeout the communicator is aborted and -1 returned. rb200_nccl_finalize and rb200_destroy
+ * wait the same way with a 10 s limit, so an unmatched send or receive cannot block them. */
 int rb200_kv_hop_sync(rb200_backend* b, int timeout_ms);
 
 /* ---- operators on device buffers ----------------------------------------------------- */
@@ -220,9 +277,14 @@ typedef struct rb200_attn_shape {
 #define RB200_DECODE_SLICE 512 /* keys per split-context slice (engine/src/cuda_kernels.cuh:180-190); slices grow in
                                   multiples of it when a batch has enough (token, KV head) pairs to fill the GPU */
 
-/* Scratch the split decode needs for n_decode tokens whose longest context is max_ctx:
- * per (token, head, slice) D + 2 floats. Returns bytes. */
+/* Scratch that is always enough for the split decode of n_decode tokens whose longest context is
+ * max_ctx: per (token, head, 512-key slice) D + 2 floats. Returns bytes. */
 size_t rb200_decode_scratch_bytes(const rb200_attn_shape* s, int n_decode, int max_ctx);
+/* What rb200_decode_attention will do with such a batch on the current device: keys per slice
+ * (a multiple of RB200_DECODE_SLICE; the launch stand-in of the reference's fixed 512,
+ * engine/src/cuda_backend.cu:560-565), slices per context, and (returned) the bytes of partial
+ * results it will really park in the scratch: 0 when every context is one slice. */
+size_t rb200_decode_plan(const rb200_attn_shape* s, int n_decode, int max_ctx, int32_t* slice_out, int32_t* parts_out);
 /* Split-context decode attention + LSE merge (replaces decode_attention_kernel and
  * decode_combine_kernel, engine/src/cuda_kernels.cuh:223-362). q: fp32 rows of the batch
  * (token t's head h at q + t*q_stride + h*D); decode_tokens[i] is the batch row of the
@@ -239,10 +301,13 @@ int rb200_decode_attention(const rb200_attn_shape* s, const float* q, const rb20
  * library image (each GPU that loads the library carries it until the process exits);
  * inputs and outputs are still the caller's. This call allocates nothing, on the host side
  * or the device side. Limits and rules:
- *  - a batch whose partials (rb200_decode_scratch_bytes) exceed the array is rejected with
- *    an invalid-argument error naming both sizes;
- *  - the first call on each device looks up the array's device address; make that first
- *    call before starting any stream capture on that device;
+ *  - a batch whose partials (what rb200_decode_plan returns, never more than
+ *    rb200_decode_scratch_bytes) exceed the array is rejected with an invalid-argument error
+ *    naming both sizes;
+ *  - the first call on each device looks up the array's device address and keeps it for the
+ *    life of the process; make that first call before starting any stream capture on that
+ *    device, and do not call cudaDeviceReset in a process that uses this entry point (the
+ *    kept address would name memory of the destroyed context);
  *  - all calls share the one array, which keeps whatever the previous call left (nothing
  *    in it needs clearing: each call overwrites what it later reads); two calls that overlap
  *    on the GPU, e.g. on different streams, race on it and must be serialised by the caller. */
@@ -317,6 +382,11 @@ int rb200_kv_scatter(void* k_pool, void* v_pool, const int32_t* blocks, int n, s
                      const void* staging, void* stream);
 /* Greedy token of each row of logits [R][V] (lowest id wins ties, engine/src/sampler.cpp:17-22). */
 int rb200_argmax_rows(const float* logits, int R, int V, int32_t* token_out, float* logit_out, void* stream);
+/* The device sampler on rows of logits [R][V] (engine/src/sampler.cpp:33-72): `params` is a
+ * DEVICE array of R entries, each greedy or untruncated (see rb200_forward_sample; the caller
+ * checks, the kernel does not); logprob_out may be NULL. */
+int rb200_sample_rows(const float* logits, int R, int V, const rb200_sampling_params* params, int32_t* token_out,
+                      double* logprob_out, void* stream);
 
 #ifdef __cplusplus
 }

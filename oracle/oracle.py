@@ -25,11 +25,20 @@ _lib = None
 _ref = None
 
 
+def reference_root() -> Optional[str]:
+    """The relay checkout to compile the reference checker from: $RELAY_REFERENCE, else a
+    directory named `reference` beside this repository; None where neither holds relay's sources."""
+    for cand in (os.environ.get("RELAY_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "engine", "src")):
+            return cand
+    return None
+
+
 def build(reference: bool = True) -> None:
     """Compiles the restatement, and relay's CPU backend too where its sources are present."""
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
-    ref_root = os.environ.get("RELAY_REFERENCE", "/root/reference")
-    if reference and os.path.isdir(os.path.join(ref_root, "engine", "src")):
+    ref_root = reference_root()
+    if reference and ref_root:
         subprocess.run(["make", "-s", "-j8", "-C", HERE, "ref", f"REF={ref_root}"], check=True)
         if os.path.exists(os.path.join(os.path.dirname(HERE), "relay_b200", "librelay_b200.so")):
             # relay's own test programs linked against the B200 backend (tests/test_gpu_reference_suite.py)
@@ -56,6 +65,12 @@ def lib() -> C.CDLL:
         L.ro_forward.argtypes = [C.c_void_p, C.c_int] + [C.c_void_p] * 6 + [C.c_int, C.c_void_p, C.c_size_t]
         L.ro_read_kv_block.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         L.ro_write_kv_block.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        L.ro_uniform01.restype = C.c_double
+        L.ro_uniform01.argtypes = [C.c_uint64, C.c_uint64]
+        L.ro_sample.restype = C.c_int
+        L.ro_sample.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_int, C.c_uint64, C.c_uint64, C.c_void_p]
+        L.ro_set_threads.restype = C.c_int
+        L.ro_set_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
 
@@ -91,10 +106,27 @@ def ref_lib() -> C.CDLL:
         R.ref_f16_to_f32.restype = C.c_float
         R.ref_f16_to_f32.argtypes = [C.c_uint16]
         R.ref_argmax.argtypes = [C.c_void_p, C.c_int]
+        R.ref_sample.restype = C.c_int
+        R.ref_sample.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_int, C.c_ulonglong, C.c_ulonglong, C.c_void_p]
+        R.ref_uniform01.restype = C.c_double
+        R.ref_uniform01.argtypes = [C.c_ulonglong, C.c_ulonglong]
+        R.ref_set_threads.restype = C.c_int
+        R.ref_set_threads.argtypes = [C.c_int]
         R.ref_generate_greedy.restype = C.c_int
         R.ref_generate_greedy.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         _ref = R
     return _ref
+
+
+def set_threads(n: Optional[int] = None) -> int:
+    """Runs both checkers' OpenMP loops on n threads (default: every core this process may run
+    on), whatever OMP_NUM_THREADS says: a multi-process launcher exports OMP_NUM_THREADS=1 to
+    its ranks. Returns the count in force."""
+    n = len(os.sched_getaffinity(0)) if n is None else n
+    got = lib().ro_set_threads(int(n))
+    if have_ref():
+        got = ref_lib().ref_set_threads(int(n))
+    return int(got)
 
 
 def f32(a) -> np.ndarray:
@@ -197,6 +229,23 @@ def lse_merge(part_o: np.ndarray, part_ml: np.ndarray) -> np.ndarray:
 def argmax(logits: np.ndarray) -> int:
     logits = f32(logits)
     return int(lib().ro_argmax(ptr(logits), logits.size))
+
+
+def sample(logits: np.ndarray, temperature: float, top_p: float, top_k: int, seed: int, index: int,
+           prefer_reference: bool = True):
+    """(token, log-probability) relay's sampler gives for one row of logits: relay's own code
+    where it was compiled, else the restatement."""
+    logits = f32(logits)
+    lp = C.c_double(0.0)
+    if prefer_reference and have_ref():
+        tok = ref_lib().ref_sample(ptr(logits), logits.size, temperature, top_p, top_k, seed, index, C.byref(lp))
+    else:
+        tok = lib().ro_sample(ptr(logits), logits.size, temperature, top_p, top_k, seed, index, C.byref(lp))
+    return int(tok), float(lp.value)
+
+
+def uniform01(seed: int, index: int) -> float:
+    return float(lib().ro_uniform01(seed, index))
 
 
 def kv_gather(k_pool: np.ndarray, v_pool: np.ndarray, blocks, block_bytes: int) -> np.ndarray:

@@ -3,6 +3,8 @@
 // benchmark's cpu_baseline leg can drive the real reference through ctypes. It is compiled
 // by oracle/Makefile together with the reference's sources, where they lie, into
 // oracle/_ref/librelay_ref.so. Nothing under relay_b200/ may link or load it.
+#include <omp.h>
+
 #include <cstring>
 #include <memory>
 #include <stdexcept>
@@ -239,6 +241,28 @@ int ref_rope_inv_freq(const rb200_model_config* cfg, float* out) {
 unsigned short ref_f32_to_f16(float f) { return relay::f32_to_f16(f); }
 float ref_f16_to_f32(unsigned short h) { return relay::f16_to_f32(h); }
 int ref_argmax(const float* logits, int vocab) { return relay::argmax(logits, vocab); }
+
+// relay's sampler (engine/src/sampler.cpp) on one row of logits: the token it picks for
+// (seed, index) and, when lp_out is given, the log-probability Engine reports with it
+// (engine/src/engine.cpp:270-282).
+int ref_sample(const float* logits, int vocab, float temperature, float top_p, int top_k, unsigned long long seed,
+               unsigned long long index, double* lp_out) {
+  relay::SamplingParams p;
+  p.temperature = temperature;
+  p.top_p = top_p;
+  p.top_k = top_k;
+  p.seed = seed;
+  if (lp_out) return relay::sample_with_log_prob(logits, vocab, p, index, lp_out);
+  return relay::sample(logits, vocab, p, index);
+}
+double ref_uniform01(unsigned long long seed, unsigned long long index) { return relay::uniform01(seed, index); }
+
+// OpenMP threads of this library's parallel loops (a launcher may have exported
+// OMP_NUM_THREADS=1 to the process); returns the count now in force.
+int ref_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+}
 
 // Greedy generation through relay's own Engine (continuous batching scheduler) on the CPU
 // backend: the prompt, then `steps` tokens; writes the tokens and each step's logits.

@@ -7,6 +7,7 @@
 #include "relay_oracle.h"
 
 #include <math.h>
+#include <omp.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -416,4 +417,108 @@ int ro_forward(ro_model* m, int n_seqs, const int32_t* tokens, const int32_t* ch
   free(xr); free(act); free(gu); free(attn); free(qkv); free(xn); free(x);
   free(rows); free(toff); free(seq); free(pos);
   return R;
+}
+
+/* ---- the sampler (engine/src/sampler.cpp) ------------------------------------------------ */
+
+/* uniform01 (sampler.cpp:9-15): splitmix64 of (seed, index), 53 random bits. */
+double ro_uniform01(uint64_t seed, uint64_t index) {
+  uint64_t z = seed + 0x9E3779B97F4A7C15ULL * (index + 1);
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+  z ^= z >> 31;
+  return (double)(z >> 11) * (1.0 / 9007199254740992.0);
+}
+
+/* log_prob (sampler.cpp:24-31): log softmax(logits / t)[token] in double; t <= 0 means 1. */
+static double log_prob(const float* logits, int vocab, float temperature, int token) {
+  const double t = temperature > 0.0f ? temperature : 1.0;
+  double mx = logits[0];
+  for (int i = 1; i < vocab; ++i) mx = mx > (double)logits[i] ? mx : (double)logits[i];
+  double sum = 0;
+  for (int i = 0; i < vocab; ++i) sum += exp((logits[i] - mx) / t);
+  return (logits[token] - mx) / t - log(sum);
+}
+
+static const float* g_sort_logits; /* qsort has no context argument; sampling rows is not re-entrant here */
+#pragma omp threadprivate(g_sort_logits)
+static int by_logit(const void* a, const void* b) {
+  const int ia = *(const int*)a, ib = *(const int*)b;
+  if (g_sort_logits[ia] > g_sort_logits[ib]) return -1;
+  if (g_sort_logits[ia] < g_sort_logits[ib]) return 1;
+  return ia < ib ? -1 : (ia > ib ? 1 : 0); /* ties by id: the order is fully determined */
+}
+
+/* sample / sample_with_log_prob (sampler.cpp:33-105). lp_out may be NULL. */
+int ro_sample(const float* logits, int vocab, float temperature, float top_p, int top_k, uint64_t seed, uint64_t index,
+              double* lp_out) {
+  int tok;
+  if (!(temperature > 0.0f)) {
+    tok = ro_argmax(logits, vocab);
+    if (lp_out) *lp_out = log_prob(logits, vocab, temperature, tok);
+    return tok;
+  }
+  if ((top_k <= 0 || top_k >= vocab) && top_p >= 1.0f) {
+    /* no truncation: inverse CDF in id order, float terms, double sum (sampler.cpp:35-59) */
+    const float inv_t = 1.0f / temperature;
+    float mx = logits[0];
+    for (int i = 1; i < vocab; ++i) mx = mx > logits[i] ? mx : logits[i];
+    float* e = (float*)malloc(sizeof(float) * (size_t)vocab);
+    double total = 0;
+    for (int i = 0; i < vocab; ++i) total += e[i] = expf((logits[i] - mx) * inv_t);
+    double r = ro_uniform01(seed, index) * total;
+    tok = vocab - 1;
+    for (int i = 0; i < vocab; ++i) {
+      r -= e[i];
+      if (r < 0) {
+        tok = i;
+        break;
+      }
+    }
+    if (r >= 0)
+      while (tok > 0 && e[tok] == 0.0f) --tok;
+    if (lp_out) *lp_out = ((double)logits[tok] - mx) * inv_t - log(total);
+    free(e);
+    return tok;
+  }
+  /* candidates in order of decreasing logit, the k best kept (sampler.cpp:77-104) */
+  int* ids = (int*)malloc(sizeof(int) * (size_t)vocab);
+  for (int i = 0; i < vocab; ++i) ids[i] = i;
+  const int k = (top_k > 0 && top_k < vocab) ? top_k : vocab;
+  g_sort_logits = logits;
+  qsort(ids, (size_t)vocab, sizeof(int), by_logit);
+  double* prob = (double*)malloc(sizeof(double) * (size_t)k);
+  double mx = logits[ids[0]] / temperature, total = 0;
+  for (int i = 0; i < k; ++i) total += prob[i] = exp(logits[ids[i]] / temperature - mx);
+  int keep = k;
+  if (top_p < 1.0f) {
+    double cum = 0;
+    for (int i = 0; i < k; ++i) {
+      cum += prob[i] / total;
+      if (cum >= top_p) {
+        keep = i + 1;
+        break;
+      }
+    }
+  }
+  double kept = 0;
+  for (int i = 0; i < keep; ++i) kept += prob[i];
+  double r = ro_uniform01(seed, index) * kept;
+  tok = ids[keep - 1];
+  for (int i = 0; i < keep; ++i) {
+    r -= prob[i];
+    if (r < 0) {
+      tok = ids[i];
+      break;
+    }
+  }
+  free(prob);
+  free(ids);
+  if (lp_out) *lp_out = log_prob(logits, vocab, temperature, tok);
+  return tok;
+}
+
+int ro_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
 }

@@ -99,6 +99,17 @@ size_t ro_kv_block_bytes(const ro_model* m);
 void ro_read_kv_block(const ro_model* m, int layer, int block, float* k_out, float* v_out);
 void ro_write_kv_block(ro_model* m, int layer, int block, const float* k_in, const float* v_in);
 
+/* engine/src/sampler.cpp:9-15 and :33-105: the random number of (seed, index); the token
+ * sample() picks from one row and, in *lp_out when not NULL, the log-probability
+ * sample_with_log_prob() / log_prob() report for it. */
+double ro_uniform01(uint64_t seed, uint64_t index);
+int ro_sample(const float* logits, int vocab, float temperature, float top_p, int top_k, uint64_t seed, uint64_t index,
+              double* lp_out);
+
+/* OpenMP threads of this library's parallel loops (a launcher may have exported
+ * OMP_NUM_THREADS=1 to the process); returns the count now in force. */
+int ro_set_threads(int n);
+
 #ifdef __cplusplus
 }
 #endif

@@ -31,6 +31,11 @@ class CAttnShape(C.Structure):
                 ("q_stride", C.c_int32), ("o_stride", C.c_int32)]
 
 
+class CSamplingParams(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("top_k", C.c_int32), ("reserved", C.c_int32),
+                ("seed", C.c_uint64), ("index", C.c_uint64)]
+
+
 class CProfile(C.Structure):
     _fields_ = [("total_ms", C.c_double), ("decode_attn_ms", C.c_double), ("prefill_attn_ms", C.c_double),
                 ("forwards", C.c_uint64), ("decode_attn_calls", C.c_uint64), ("prefill_attn_calls", C.c_uint64)]
@@ -52,6 +57,11 @@ SIGNATURES = {
     "rb200_get_kv_layout": (I, [P, P]),
     "rb200_forward": (I, [P, I, P, P, P, P, P, P, I, LAYER_CB, P, P, SZ]),
     "rb200_forward_greedy": (I, [P, I, P, P, P, P, P, P, I, LAYER_CB, P, P, P, SZ]),
+    "rb200_forward_sample": (I, [P, I, P, P, P, P, P, P, I, LAYER_CB, P, P, P, P, SZ]),
+    "rb200_decode_open": (I, [P, I, P, P, P]),
+    "rb200_decode_set_slot": (I, [P, I, I, I, P]),
+    "rb200_decode_step": (I, [P, P, I, P, P, P, P, P, P, SZ]),
+    "rb200_decode_close": (I, [P]),
     "rb200_kv_block_bytes": (SZ, [P]),
     "rb200_read_kv_layer": (I, [P, I, P, I, P, P]),
     "rb200_write_kv_layer": (I, [P, I, P, I, P, P]),
@@ -69,6 +79,7 @@ SIGNATURES = {
     "rb200_recv_kv_layer": (I, [P, I, I, P, I]),
     "rb200_kv_hop_sync": (I, [P, I]),
     "rb200_decode_scratch_bytes": (SZ, [C.POINTER(CAttnShape), I, I]),
+    "rb200_decode_plan": (SZ, [C.POINTER(CAttnShape), I, I, P, P]),
     "rb200_decode_attention": (I, [C.POINTER(CAttnShape), P, C.POINTER(CTokenMeta), P, I, I, P, P, P, SZ, P, P]),
     "rb200_decode_attention_static": (I, [C.POINTER(CAttnShape), P, C.POINTER(CTokenMeta), P, I, I, P, P, P, P]),
     "rb200_prefill_attention": (I, [C.POINTER(CAttnShape), P, C.POINTER(CTokenMeta), P, I, P, P, P, P]),
@@ -86,6 +97,7 @@ SIGNATURES = {
     "rb200_kv_gather": (I, [P, P, P, I, SZ, P, P]),
     "rb200_kv_scatter": (I, [P, P, P, I, SZ, P, P]),
     "rb200_argmax_rows": (I, [P, I, I, P, P, P]),
+    "rb200_sample_rows": (I, [P, I, I, P, P, P, P]),
 }
 
 _lib = None

@@ -79,11 +79,28 @@ class Backend:
         return self._L.rb200_name(self._h).decode()
 
     def _cb(self, observer):
+        """The C callback for `observer`. An exception raised inside it cannot cross the C frames
+        of the forward pass: it is kept (the first one) and re-raised by _reraise() once the
+        call has returned."""
+        self._cb_error = None
         if observer is None:
             return _lib.LAYER_CB(), None
         fn = observer.kv_written if hasattr(observer, "kv_written") else observer
-        cb = _lib.LAYER_CB(lambda _ctx, layer: fn(layer))
+
+        def call(_ctx, layer):
+            if self._cb_error is None:
+                try:
+                    fn(layer)
+                except BaseException as e:  # noqa: BLE001 - re-raised after the C call returns
+                    self._cb_error = e
+
+        cb = _lib.LAYER_CB(call)
         return cb, cb
+
+    def _reraise(self):
+        e, self._cb_error = getattr(self, "_cb_error", None), None
+        if e is not None:
+            raise e
 
     def forward_flat(self, fb: FlatBatch, observer=None, out: Optional[np.ndarray] = None) -> np.ndarray:
         """forward() on an already flattened batch; `out` may be a caller-owned (for example
@@ -94,9 +111,11 @@ class Backend:
             out = np.empty((max(rows, 1), V), np.float32)
         cb, keep = self._cb(observer)
         want = fb.want_logits.astype(np.uint8)
-        r = _lib.check(self._L.rb200_forward(
+        r = self._L.rb200_forward(
             self._h, fb.n_seqs, ptr(fb.tokens), ptr(fb.chunk_len), ptr(fb.start_pos), ptr(fb.table_len), ptr(fb.tables),
-            ptr(want), int(fb.all_logits), cb, None, out.ctypes.data_as(C.c_void_p), out.size))
+            ptr(want), int(fb.all_logits), cb, None, out.ctypes.data_as(C.c_void_p), out.size)
+        self._reraise()
+        r = _lib.check(r)
         return out.reshape(-1)[: r * V].reshape(r, V)
 
     def forward(self, batch: ForwardBatch, observer=None) -> np.ndarray:
@@ -112,10 +131,86 @@ class Backend:
         tok, val = np.empty(rows, np.int32), np.empty(rows, np.float32)
         cb, keep = self._cb(observer)
         want = fb.want_logits.astype(np.uint8)
-        r = _lib.check(self._L.rb200_forward_greedy(
+        r = self._L.rb200_forward_greedy(
             self._h, fb.n_seqs, ptr(fb.tokens), ptr(fb.chunk_len), ptr(fb.start_pos), ptr(fb.table_len), ptr(fb.tables),
-            ptr(want), int(fb.all_logits), cb, None, ptr(tok), ptr(val), rows))
+            ptr(want), int(fb.all_logits), cb, None, ptr(tok), ptr(val), rows)
+        self._reraise()
+        r = _lib.check(r)
         return tok[:r], val[:r]
+
+    @staticmethod
+    def _sampling_array(sampling, rows: int):
+        """`sampling`: one (temperature, top_p, top_k, seed, index) tuple per logits row."""
+        arr = (_lib.CSamplingParams * max(rows, 1))()
+        if len(sampling) != rows:
+            raise ValueError(f"sampling: {len(sampling)} entries for {rows} logits rows")
+        for i, (t, top_p, top_k, seed, index) in enumerate(sampling):
+            arr[i] = _lib.CSamplingParams(float(t), float(top_p), int(top_k), 0, int(seed), int(index))
+        return arr
+
+    def forward_sample(self, batch: ForwardBatch, sampling, logprobs: bool = False, observer=None):
+        """The token relay's sampler picks from each logits row, sampled on the device, and (with
+        `logprobs`) its log-probability. `sampling`: one (temperature, top_p, top_k, seed, index)
+        per row; rows asking for top-k / top-p truncation raise ValueError (host path)."""
+        fb = flatten(batch)
+        rows = fb.n_rows
+        arr = self._sampling_array(sampling, rows)
+        tok = np.empty(max(rows, 1), np.int32)
+        lp = np.empty(max(rows, 1), np.float64) if logprobs else None
+        cb, keep = self._cb(observer)
+        want = fb.want_logits.astype(np.uint8)
+        r = self._L.rb200_forward_sample(
+            self._h, fb.n_seqs, ptr(fb.tokens), ptr(fb.chunk_len), ptr(fb.start_pos), ptr(fb.table_len), ptr(fb.tables),
+            ptr(want), int(fb.all_logits), cb, None, arr, ptr(tok), ptr(lp) if logprobs else None, rows)
+        self._reraise()
+        r = _lib.check(r)
+        return (tok[:r], lp[:r]) if logprobs else tok[:r]
+
+    # -- decode sessions (no counterpart in relay::Backend; see include/relay_b200.h) -------------
+    def decode_open(self, context_lens: Sequence[int], tables: Sequence[Sequence[int]]) -> None:
+        """A session over len(tables) sequences: slot s has context_lens[s] keys in the cache and the
+        block ids tables[s] (spare ids allowed)."""
+        ctx, tl = i32(context_lens), i32([len(t) for t in tables])
+        flat = i32([b for t in tables for b in t]) if tl.sum() else i32([0])
+        self._session_slots = len(tables)
+        _lib.check(self._L.rb200_decode_open(self._h, len(tables), ptr(ctx), ptr(tl), ptr(flat)))
+
+    def decode_set_slot(self, slot: int, context_len: int, table: Sequence[int]) -> None:
+        t = i32(table) if len(table) else i32([0])
+        _lib.check(self._L.rb200_decode_set_slot(self._h, slot, context_len, len(table), ptr(t)))
+
+    def decode_step(self, tokens=None, new_blocks: Sequence[Tuple[int, int]] = (), sampling=None, want_tokens: bool = True,
+                    logprobs: bool = False, want_logits: bool = False, logits_out: Optional[np.ndarray] = None):
+        """One step of the open session. tokens: one id per slot, or None to feed the tokens the
+        previous step picked on the device. new_blocks: (slot, block id) pairs appended since the
+        last step. Returns a dict with the outputs asked for: "tokens", "logprobs", "logits"."""
+        S, V = self._session_slots, self._config.vocab
+        tok_in = i32(tokens) if tokens is not None else None
+        if tok_in is not None and tok_in.size != S:
+            raise ValueError("decode_step: one token per slot")
+        nb_seq, nb_id = i32([s for s, _ in new_blocks]), i32([b for _, b in new_blocks])
+        arr = self._sampling_array(sampling, S) if sampling is not None else None
+        tok = np.empty(S, np.int32) if (want_tokens or sampling is not None or logprobs) else None
+        lp = np.empty(S, np.float64) if logprobs else None
+        lg = None
+        if want_logits:
+            lg = logits_out if logits_out is not None else np.empty((S, V), np.float32)
+        _lib.check(self._L.rb200_decode_step(
+            self._h, ptr(tok_in) if tok_in is not None else None, len(new_blocks), ptr(nb_seq) if len(new_blocks) else None,
+            ptr(nb_id) if len(new_blocks) else None, arr, ptr(tok) if tok is not None else None,
+            ptr(lp) if lp is not None else None, lg.ctypes.data_as(C.c_void_p) if lg is not None else None,
+            lg.size if lg is not None else 0))
+        out = {}
+        if tok is not None:
+            out["tokens"] = tok
+        if lp is not None:
+            out["logprobs"] = lp
+        if lg is not None:
+            out["logits"] = lg.reshape(-1)[: S * V].reshape(S, V)
+        return out
+
+    def decode_close(self) -> None:
+        _lib.check(self._L.rb200_decode_close(self._h))
 
     def forward_greedy_flat(self, fb: FlatBatch) -> Tuple[np.ndarray, np.ndarray]:
         """forward_greedy() on an already flattened batch."""

@@ -612,7 +612,7 @@ int shift_of(int bs) {
 
 template <class K>
 void raise_smem(K kernel, size_t bytes) {
-  // The attribute belongs to the kernel for the whole process; it is only ever raised.
+  // The attribute belongs to the (kernel, device) pair; it is only ever raised.
   RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
 }
 
@@ -620,12 +620,9 @@ template <int D, bool CONTIG, bool WIDE>
 void launch_decode_t(const AttnShape& s, const float* q, const TokenMeta& m, const int* decode_tokens, int n_decode,
                      int parts, int slice, const __half* kc, const __half* vc, float* part_o, float* part_ml, __half* out,
                      cudaStream_t st) {
-  static bool configured = false;  // benign race: the call is idempotent
+  static PerDeviceOnce once;
   auto kernel = decode_split_kernel<D, CONTIG, WIDE>;
-  if (!configured) {
-    raise_smem(kernel, decode_smem_bytes<D>());
-    configured = true;
-  }
+  if (once.first()) raise_smem(kernel, decode_smem_bytes<D>());
   const float scale_log2e = kLog2e / sqrtf(static_cast<float>(D));
   dim3 grid(n_decode, s.kv_heads, parts);
   count_launch();
@@ -647,12 +644,9 @@ void launch_decode_d(const AttnShape& s, const float* q, const TokenMeta& m, con
 template <int D>
 void launch_prefill_d(const AttnShape& s, const float* q, const TokenMeta& m, const int2* tiles, int n_tiles,
                       const __half* kc, const __half* vc, __half* out, cudaStream_t st) {
-  static bool configured = false;
+  static PerDeviceOnce once;
   auto kernel = prefill_flash_kernel<D>;
-  if (!configured) {
-    raise_smem(kernel, prefill_smem_bytes<D>());
-    configured = true;
-  }
+  if (once.first()) raise_smem(kernel, prefill_smem_bytes<D>());
   const float scale_log2e = kLog2e / sqrtf(static_cast<float>(D));
   dim3 grid(n_tiles, s.heads);
   count_launch();
@@ -675,14 +669,11 @@ size_t decode_scratch_bytes(const AttnShape& s, int n_decode, int max_ctx) {
   return static_cast<size_t>(n_decode) * s.heads * parts * (s.D + 2) * sizeof(float);
 }
 
-void launch_decode_attention(const AttnShape& s, const float* q, const TokenMeta& m, const int* decode_tokens,
-                             int n_decode, int max_ctx, const __half* kc, const __half* vc, float* scratch,
-                             __half* out, cudaStream_t st) {
-  if (n_decode == 0) return;
-  // Slices are 512 keys when the batch alone would not fill the GPU; with many (token, KV
-  // head) pairs they grow (in steps of 512, up to 512 block-table entries) until a few waves
-  // of CTAs remain, which spares the partial results and, at one slice, the merge.
-  const long long pairs_kv = static_cast<long long>(n_decode) * s.kv_heads;
+// Slices are 512 keys when the batch alone would not fill the GPU; with many (token, KV
+// head) pairs they grow (in steps of 512, up to 512 block-table entries) until a few waves
+// of CTAs remain, which spares the partial results and, at one slice, the merge.
+DecodePlan plan_decode(const AttnShape& s, int n_decode, int max_ctx) {
+  const long long pairs_kv = std::max<long long>(1, static_cast<long long>(n_decode) * s.kv_heads);
   static const int waves = [] {
     const char* e = std::getenv("RB200_DECODE_WAVES");
     return e && std::atoi(e) > 0 ? std::atoi(e) : 8;
@@ -693,6 +684,20 @@ void launch_decode_attention(const AttnShape& s, const float* q, const TokenMeta
   slice = static_cast<int>(std::min<long long>(slice, static_cast<long long>(kDecodeSlice) * s.block_size));
   slice = std::max(kDecodeSlice, slice / kDecodeSlice * kDecodeSlice);
   const int parts = div_up(std::max(max_ctx, 1), slice);
+  DecodePlan p;
+  p.slice = slice;
+  p.parts = parts;
+  // one slice writes the output directly: no partial results, no merge
+  p.scratch_bytes = parts > 1 ? static_cast<size_t>(n_decode) * s.heads * parts * (s.D + 2) * sizeof(float) : 0;
+  return p;
+}
+
+void launch_decode_attention(const AttnShape& s, const float* q, const TokenMeta& m, const int* decode_tokens,
+                             int n_decode, int max_ctx, const __half* kc, const __half* vc, float* scratch,
+                             __half* out, cudaStream_t st) {
+  if (n_decode == 0) return;
+  const DecodePlan plan = plan_decode(s, n_decode, max_ctx);
+  const int parts = plan.parts, slice = plan.slice;
   RB_REQUIRE(parts <= 65535, "decode attention: context too long for one launch");
   float* part_o = scratch;
   float* part_ml = scratch + static_cast<size_t>(n_decode) * s.heads * parts * s.D;
@@ -790,6 +795,13 @@ size_t rb200_decode_scratch_bytes(const rb200_attn_shape* s, int n_decode, int m
   return decode_scratch_bytes(shape_of(s), n_decode, max_ctx);
 }
 
+size_t rb200_decode_plan(const rb200_attn_shape* s, int n_decode, int max_ctx, int32_t* slice_out, int32_t* parts_out) {
+  const DecodePlan p = plan_decode(shape_of(s), n_decode, max_ctx);
+  if (slice_out) *slice_out = p.slice;
+  if (parts_out) *parts_out = p.parts;
+  return p.scratch_bytes;
+}
+
 int rb200_decode_attention(const rb200_attn_shape* s, const float* q, const rb200_token_meta* m,
                            const int32_t* decode_tokens, int n_decode, int max_ctx, const void* k_pool,
                            const void* v_pool, void* scratch, size_t scratch_bytes, void* out, void* stream) {
@@ -798,8 +810,7 @@ int rb200_decode_attention(const rb200_attn_shape* s, const float* q, const rb20
     check_shape(sh);
     RB_REQUIRE(fast_attention_supported(sh), "decode attention: head_dim must be 16/32/64/128 and heads/kv_heads <= 16");
     RB_REQUIRE(n_decode >= 0 && max_ctx >= 1, "decode attention: bad batch");
-    RB_REQUIRE(scratch_bytes >= decode_scratch_bytes(sh, n_decode, max_ctx) || max_ctx <= kDecodeSlice,
-               "decode attention: scratch too small");
+    RB_REQUIRE(scratch_bytes >= plan_decode(sh, n_decode, max_ctx).scratch_bytes, "decode attention: scratch too small");
     launch_decode_attention(sh, q, meta_of(m), decode_tokens, n_decode, max_ctx, static_cast<const __half*>(k_pool),
                             static_cast<const __half*>(v_pool), static_cast<float*>(scratch), static_cast<__half*>(out),
                             as_stream(stream));
@@ -816,7 +827,9 @@ int rb200_decode_attention_static(const rb200_attn_shape* s, const float* q, con
     check_shape(sh);
     RB_REQUIRE(fast_attention_supported(sh), "decode attention: head_dim must be 16/32/64/128 and heads/kv_heads <= 16");
     RB_REQUIRE(n_decode >= 0 && max_ctx >= 1, "decode attention: bad batch");
-    const size_t need = decode_scratch_bytes(sh, n_decode, max_ctx);
+    // What this launch will really park: the slices the planner cuts, not the 512-key upper bound
+    // of rb200_decode_scratch_bytes (a batch that fills the GPU with one slice per pair parks nothing).
+    const size_t need = plan_decode(sh, n_decode, max_ctx).scratch_bytes;
     if (need > static_cast<size_t>(RB200_STATIC_DECODE_SCRATCH_BYTES))
       fail(RB200_ERR_INVALID_ARGUMENT, "decode attention (static scratch): this batch needs " + std::to_string(need) +
                                            " bytes of partial results, the built-in buffer holds " +

@@ -289,6 +289,8 @@ Backend::~Backend() {
   cudaSetDevice(device_);
   nccl_finalize_noexcept();
   cudaDeviceSynchronize();
+  session_.reset();
+  if (pass_done_) cudaEventDestroy(pass_done_);
   for (auto e : layer_done_) cudaEventDestroy(e);
   for (IdSlot& s : id_slots_)
     if (s.uploaded) cudaEventDestroy(s.uploaded);
@@ -298,10 +300,37 @@ Backend::~Backend() {
 
 // ---- forward ------------------------------------------------------------------------------
 
+Backend::PickSpec Backend::pick_of(const Outputs& out, int R) const {
+  PickSpec pick;
+  if (!out.tokens) return pick;
+  pick.kind = out.sampling ? Pick::Sample : Pick::Greedy;
+  pick.logprobs = out.logprobs != nullptr;
+  if (out.sampling)
+    for (int r = 0; r < R; ++r)
+      if (!sampling_on_device(out.sampling[r], c_.vocab))
+        fail(RB200_ERR_INVALID_ARGUMENT,
+             "sampling: top-k / top-p truncation is not done on the device; take the logits (rb200_forward) for such rows");
+  // greedy with log-probabilities runs the sampling kernel with temperature 0 rows
+  if (pick.kind == Pick::Greedy && pick.logprobs) pick.kind = Pick::Sample;
+  return pick;
+}
+
+// Copies of the pass's results to the host, enqueued behind its kernels.
+void Backend::fetch_outputs(const Outputs& out, int R, PickSpec pick) {
+  if (R == 0) return;
+  const size_t rows = static_cast<size_t>(R);
+  if (pick.kind != Pick::None) {
+    RB_CUDA(cudaMemcpyAsync(out.tokens, argmax_tok_.p, rows * 4, cudaMemcpyDeviceToHost, stream_));
+    if (pick.kind == Pick::Greedy && out.greedy_logit)
+      RB_CUDA(cudaMemcpyAsync(out.greedy_logit, argmax_val_.p, rows * 4, cudaMemcpyDeviceToHost, stream_));
+    if (pick.logprobs) RB_CUDA(cudaMemcpyAsync(out.logprobs, logprob_.p, rows * 8, cudaMemcpyDeviceToHost, stream_));
+  }
+  if (out.logits) RB_CUDA(cudaMemcpyAsync(out.logits, logits_.p, rows * c_.vocab * 4, cudaMemcpyDeviceToHost, stream_));
+}
+
 int Backend::forward(int n_seqs, const int32_t* tokens, const int32_t* chunk_len, const int32_t* start_pos,
                      const int32_t* table_len, const int32_t* tables, const uint8_t* want_logits, bool all_logits,
-                     rb200_layer_cb cb, void* cb_ctx, float* logits_out, size_t cap_floats, int32_t* token_out,
-                     float* logit_out, size_t cap_rows) {
+                     rb200_layer_cb cb, void* cb_ctx, const Outputs& out) {
   set_device();  // the caller's current device may be another GPU (engine/src/cuda_backend.cu:505)
   RB_REQUIRE(n_seqs >= 0, "forward: negative sequence count");
   const int H = c_.hidden, D = c_.head_dim, Q = c_.heads * D, KV = c_.kv_heads * D, QKV = Q + 2 * KV, I = c_.intermediate;
@@ -332,12 +361,13 @@ int Backend::forward(int n_seqs, const int32_t* tokens, const int32_t* chunk_len
   const int T = static_cast<int>(T_ll);
 
   // Pass 2: flatten into one pinned buffer -> one host-to-device copy.
-  // Layout (ints): tokens[T] pos[T] seq[T] rows[T] decode[T] tiles[2T] table_off[S4] tables[...]
+  // Layout (ints): tokens[T4] pos[T4] seq[T4] rows[T4] decode[T4] tiles[2 T4] table_off[S4] tables[...]
+  // and, when the device samples, the rows' sampling parameters (8 ints each) behind the tables.
   const size_t S4 = static_cast<size_t>(round_up(n_seqs, 4));
-  const size_t meta_ints = static_cast<size_t>(T) * 7 + S4 + static_cast<size_t>(table_ints);
   const size_t T4 = static_cast<size_t>(round_up(T, 4));
-  const size_t total_ints = T4 * 7 + S4 + static_cast<size_t>(table_ints);
-  (void)meta_ints;
+  const size_t sampling_off = T4 * 7 + S4 + static_cast<size_t>(table_ints);  // a multiple of 4 ints: 16-byte aligned
+  static_assert(sizeof(rb200_sampling_params) == 32, "sampling parameters are 8 ints");
+  const size_t total_ints = sampling_off + (out.tokens ? static_cast<size_t>(T) * 8 : 0);
   meta_host_.ensure(total_ints * 4);
   meta_dev_.ensure(total_ints * 4);
   int* hm = meta_host_.as<int>();
@@ -380,46 +410,62 @@ int Backend::forward(int n_seqs, const int32_t* tokens, const int32_t* chunk_len
       t += n;
     }
   }
-  if (logits_out && static_cast<size_t>(R) * V > cap_floats) fail(RB200_ERR_INVALID_ARGUMENT, "logits buffer too small");
-  if (token_out && static_cast<size_t>(R) > cap_rows) fail(RB200_ERR_INVALID_ARGUMENT, "token buffer too small");
+  if (out.logits && static_cast<size_t>(R) * V > out.cap_floats) fail(RB200_ERR_INVALID_ARGUMENT, "logits buffer too small");
+  if (out.tokens && static_cast<size_t>(R) > out.cap_rows) fail(RB200_ERR_INVALID_ARGUMENT, "token buffer too small");
+  const PickSpec pick = pick_of(out, R);
+  if (pick.kind == Pick::Sample) {
+    auto* sp = reinterpret_cast<rb200_sampling_params*>(hm + sampling_off);
+    for (int r = 0; r < R; ++r) sp[r] = out.sampling ? out.sampling[r] : rb200_sampling_params{0.0f, 1.0f, 0, 0, 0, 0};
+  }
 
   RB_CUDA(cudaMemcpyAsync(meta_dev_.p, hm, total_ints * 4, cudaMemcpyHostToDevice, stream_));
-  plan_ = Plan{T, R, n_decode, n_tiles, max_ctx, T4, S4};
+  plan_ = Plan{T, R, n_decode, n_tiles, max_ctx, T4, S4, pick.kind == Pick::Sample ? sampling_off : 0};
   const AttnShape shape{c_.heads, c_.kv_heads, D, bs, QKV, Qp_};
   if (fast_attention_ && n_decode > 0) decode_scratch_.ensure(decode_scratch_bytes(shape, n_decode, max_ctx));
-  if (R > 0) logits_.ensure(static_cast<size_t>(R) * V * 4);
-  if (R > 0 && token_out) {
-    argmax_tok_.ensure(static_cast<size_t>(R) * 4);
-    argmax_val_.ensure(static_cast<size_t>(R) * 4);
-  }
+  ensure_row_buffers(R, pick);
   (void)H; (void)I; (void)KV;
 
   Prof prof = begin_profile();
-  enqueue(plan_, cb, cb_ctx, token_out != nullptr, &prof);
-  if (R > 0) {
-    if (token_out) {
-      RB_CUDA(cudaMemcpyAsync(token_out, argmax_tok_.p, static_cast<size_t>(R) * 4, cudaMemcpyDeviceToHost, stream_));
-      if (logit_out)
-        RB_CUDA(cudaMemcpyAsync(logit_out, argmax_val_.p, static_cast<size_t>(R) * 4, cudaMemcpyDeviceToHost, stream_));
-    } else if (logits_out) {
-      RB_CUDA(cudaMemcpyAsync(logits_out, logits_.p, static_cast<size_t>(R) * V * 4, cudaMemcpyDeviceToHost, stream_));
-    }
-  }
+  enqueue(meta_dev_.as<int>(), plan_, cb, cb_ctx, pick, &prof);
+  layer_events_stale_ = false;
+  fetch_outputs(out, R, pick);
+  // Steps of every size run tcgen05 kernels (the few-token linear layers too), so the word their
+  // bounded pipeline waits leave a code in comes back with every pass, behind the results.
+  result_host_.ensure(sizeof(int));
+  RB_CUDA(cudaMemcpyAsync(result_host_.p, umma_status_word(), sizeof(int), cudaMemcpyDeviceToHost, stream_));
   RB_CUDA(cudaGetLastError());
   RB_CUDA(cudaStreamSynchronize(stream_));
   end_profile(prof);
-  if (T > 8 || R > 8 || n_tiles > 0) {  // a tcgen05 kernel ran: make sure none of its bounded waits gave up
-    const int code = umma_gemm_status();
-    if (code != 0) fail(RB200_ERR_RUNTIME, "a tcgen05 pipeline wait timed out (code " + std::to_string(code) + ")");
-  }
+  check_pipeline_status();
   return R;
 }
 
+// Reads the status word copied to result_host_ by the pass that just completed. A pass in which
+// a wait gave up produced no valid output: it fails, and the word is cleared so that the next
+// pass is judged on its own.
+void Backend::check_pipeline_status() {
+  const int code = *result_host_.as<int>();
+  if (code == 0) return;
+  umma_status_clear(stream_);
+  RB_CUDA(cudaStreamSynchronize(stream_));
+  fail(RB200_ERR_RUNTIME, "a tcgen05 pipeline wait timed out (code " + std::to_string(code) + ")");
+}
+
 // One forward pass's kernels, from metadata that is already on the device.
-void Backend::enqueue(const Plan& p, rb200_layer_cb cb, void* cb_ctx, bool argmax, Prof* prof) {
+void Backend::ensure_row_buffers(int R, PickSpec pick) {
+  if (R <= 0) return;
+  logits_.ensure(static_cast<size_t>(R) * c_.vocab * 4);
+  if (pick.kind != Pick::None) {
+    argmax_tok_.ensure(static_cast<size_t>(R) * 4);
+    argmax_val_.ensure(static_cast<size_t>(R) * 4);
+  }
+  if (pick.logprobs) logprob_.ensure(static_cast<size_t>(R) * 8);
+}
+
+void Backend::enqueue(const int* dm, const Plan& p, rb200_layer_cb cb, void* cb_ctx, PickSpec pick, Prof* prof,
+                      bool layer_events) {
   const int H = c_.hidden, D = c_.head_dim, Q = c_.heads * D, KV = c_.kv_heads * D, QKV = Q + 2 * KV, I = c_.intermediate;
   const int V = c_.vocab, bs = block_size_, T = p.T, R = p.R;
-  const int* dm = meta_dev_.as<int>();
   const size_t T4 = p.T4;
   const int *d_tok = dm, *d_pos = dm + T4, *d_seq = dm + 2 * T4, *d_rows = dm + 3 * T4, *d_dec = dm + 4 * T4;
   const int2* d_tiles = reinterpret_cast<const int2*>(dm + 5 * T4);
@@ -452,7 +498,7 @@ void Backend::enqueue(const Plan& p, rb200_layer_cb cb, void* cb_ctx, bool argma
                     c_.kv_heads, D, bs, stream_);
     // This layer's K and V are enqueued; a transfer thread may wait on the event and read
     // them while later layers run (engine/src/cuda_backend.cu:580-581).
-    RB_CUDA(cudaEventRecord(layer_done_[l], stream_));
+    if (layer_events) RB_CUDA(cudaEventRecord(layer_done_[l], stream_));
     if (cb) cb(cb_ctx, l);
     if (fast_attention_) {
       if (p.n_tiles > 0) {
@@ -480,7 +526,11 @@ void Backend::enqueue(const Plan& p, rb200_layer_cb cb, void* cb_ctx, bool argma
     launch_rmsnorm(x, d_rows, final_norm_.as<float>(), xn, R, H, Hp_, eps, stream_);
     const Matrix& head = c_.tie_embeddings ? embed_ : lm_head_;
     launch_linear(head.view(), xn, Hp_, logits_.as<float>(), R, 0.0f, gs, gsb, stream_);
-    if (argmax) launch_argmax_rows(logits_.as<float>(), R, c_.vocab, argmax_tok_.as<int>(), argmax_val_.as<float>(), stream_);
+    if (pick.kind == Pick::Greedy)
+      launch_argmax_rows(logits_.as<float>(), R, c_.vocab, argmax_tok_.as<int>(), argmax_val_.as<float>(), stream_);
+    else if (pick.kind == Pick::Sample)
+      launch_sample_rows(logits_.as<float>(), R, c_.vocab, reinterpret_cast<const rb200_sampling_params*>(dm + p.sampling_off),
+                         argmax_tok_.as<int>(), pick.logprobs ? logprob_.as<double>() : nullptr, stream_);
   }
   if (prof) mark(*prof, kMarkEnd);
   RB_CUDA(cudaGetLastError());
@@ -549,14 +599,19 @@ float Backend::replay(int iters) {
     RB_CUDA(cudaEventRecord(a, stream_));
     for (int i = 0; i < iters; ++i) {
       Prof prof = begin_profile();
-      enqueue(plan_, nullptr, nullptr, (flags_ & RB200_GPU_ARGMAX) != 0 && argmax_tok_.bytes >= static_cast<size_t>(plan_.R) * 4, &prof);
+      PickSpec pick;
+      if ((flags_ & RB200_GPU_ARGMAX) != 0 && argmax_tok_.bytes >= static_cast<size_t>(plan_.R) * 4) pick.kind = Pick::Greedy;
+      enqueue(meta_dev_.as<int>(), plan_, nullptr, nullptr, pick, &prof);
       if (prof.on) {  // per-pass marks are read back before the next pass reuses the events
         RB_CUDA(cudaStreamSynchronize(stream_));
         end_profile(prof);
       }
     }
     RB_CUDA(cudaEventRecord(b, stream_));
+    result_host_.ensure(sizeof(int));
+    RB_CUDA(cudaMemcpyAsync(result_host_.p, umma_status_word(), sizeof(int), cudaMemcpyDeviceToHost, stream_));
     RB_CUDA(cudaStreamSynchronize(stream_));
+    check_pipeline_status();
     RB_CUDA(cudaEventElapsedTime(&total, a, b));
   } catch (...) {
     cudaEventDestroy(a);
@@ -672,7 +727,9 @@ void Backend::write_kv_layer(int layer, const int32_t* blocks, int n, const void
 
 void Backend::wait_kv_written(int layer) {
   check_layer(layer);
-  RB_CUDA(cudaEventSynchronize(layer_done_[layer]));
+  // A pass replayed as a CUDA graph records no per-layer events: wait for the whole pass.
+  if (layer_events_stale_ && pass_done_) RB_CUDA(cudaEventSynchronize(pass_done_));
+  else RB_CUDA(cudaEventSynchronize(layer_done_[layer]));
 }
 
 // ---- weight update (engine/src/cuda_backend.cu:429-477) -------------------------------------
@@ -822,8 +879,11 @@ int rb200_forward(rb200_backend* b, int n_seqs, const int32_t* tokens, const int
                   rb200_layer_cb cb, void* cb_ctx, float* logits_out, size_t cap_floats) {
   return guarded([&] {
     RB_REQUIRE(b != nullptr, "forward: null backend");
+    Backend::Outputs out;
+    out.logits = logits_out;
+    out.cap_floats = cap_floats;
     return b->impl->forward(n_seqs, tokens, chunk_len, start_pos, table_len, tables, want_logits, all_logits != 0, cb,
-                            cb_ctx, logits_out, cap_floats, nullptr, nullptr, 0);
+                            cb_ctx, out);
   });
 }
 
@@ -833,8 +893,68 @@ int rb200_forward_greedy(rb200_backend* b, int n_seqs, const int32_t* tokens, co
                          float* logit_out, size_t cap_rows) {
   return guarded([&] {
     RB_REQUIRE(b != nullptr && token_out != nullptr, "forward_greedy: null argument");
+    Backend::Outputs out;
+    out.tokens = token_out;
+    out.greedy_logit = logit_out;
+    out.cap_rows = cap_rows;
     return b->impl->forward(n_seqs, tokens, chunk_len, start_pos, table_len, tables, want_logits, all_logits != 0, cb,
-                            cb_ctx, nullptr, 0, token_out, logit_out, cap_rows);
+                            cb_ctx, out);
+  });
+}
+
+int rb200_forward_sample(rb200_backend* b, int n_seqs, const int32_t* tokens, const int32_t* chunk_len,
+                         const int32_t* start_pos, const int32_t* table_len, const int32_t* tables,
+                         const uint8_t* want_logits, int all_logits, rb200_layer_cb cb, void* cb_ctx,
+                         const rb200_sampling_params* sampling, int32_t* token_out, double* logprob_out, size_t cap_rows) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr && token_out != nullptr && sampling != nullptr, "forward_sample: null argument");
+    Backend::Outputs out;
+    out.tokens = token_out;
+    out.sampling = sampling;
+    out.logprobs = logprob_out;
+    out.cap_rows = cap_rows;
+    return b->impl->forward(n_seqs, tokens, chunk_len, start_pos, table_len, tables, want_logits, all_logits != 0, cb,
+                            cb_ctx, out);
+  });
+}
+
+int rb200_decode_open(rb200_backend* b, int n_seqs, const int32_t* context_len, const int32_t* table_len,
+                      const int32_t* tables) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "decode_open: null backend");
+    b->impl->decode_open(n_seqs, context_len, table_len, tables);
+    return 0;
+  });
+}
+
+int rb200_decode_set_slot(rb200_backend* b, int slot, int context_len, int table_len, const int32_t* table) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "decode_set_slot: null backend");
+    b->impl->decode_set_slot(slot, context_len, table_len, table);
+    return 0;
+  });
+}
+
+int rb200_decode_step(rb200_backend* b, const int32_t* tokens, int n_new_blocks, const int32_t* new_block_seq,
+                      const int32_t* new_block_id, const rb200_sampling_params* sampling, int32_t* token_out,
+                      double* logprob_out, float* logits_out, size_t cap_floats) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "decode_step: null backend");
+    Backend::Outputs out;
+    out.tokens = token_out;
+    out.sampling = sampling;
+    out.logprobs = logprob_out;
+    out.logits = logits_out;
+    out.cap_floats = cap_floats;
+    return b->impl->decode_step(tokens, n_new_blocks, new_block_seq, new_block_id, out);
+  });
+}
+
+int rb200_decode_close(rb200_backend* b) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "decode_close: null backend");
+    b->impl->decode_close();
+    return 0;
   });
 }
 

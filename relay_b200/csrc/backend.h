@@ -5,6 +5,7 @@
 // time and run on their own stream under copy_mu_.
 #pragma once
 
+#include <map>
 #include <memory>
 #include <mutex>
 #include <string>
@@ -58,6 +59,27 @@ struct NcclState {
   int nranks = 0, rank = -1;
 };
 
+struct DecodeSession {
+  int S = 0;    // slots
+  int cap = 0;  // block-table entries per slot (a multiple of 4: tables stay 16-byte aligned)
+  size_t T4 = 0, S4 = 0;
+  std::vector<int> ctx, tlen;  // host mirror: keys in the cache and table entries in use, per slot
+  // forward()'s metadata layout with tables `cap` apart, then the per-step delta:
+  //   header[4] = {new blocks, 1 if the device feeds its own tokens, 0, 0}
+  //   tokens[S4], (slot, table index, block id)[S] padded to 4 ints, sampling parameters[S]
+  DeviceBuf meta;
+  PinnedBuf delta_host;
+  size_t delta_off = 0, tokens_off = 0, blocks_off = 0, sampling_off = 0, delta_ints = 0;  // in ints from meta
+  bool have_picked = false;  // the previous step left one picked token per slot on the device
+  // captured steps by launch geometry; `seen` holds geometries that have run once uncaptured
+  std::map<uint64_t, cudaGraphExec_t> graphs;
+  std::map<uint64_t, int> seen;
+  uintptr_t buffers_sig = 0;
+  ~DecodeSession() {
+    for (auto& g : graphs) cudaGraphExecDestroy(g.second);
+  }
+};
+
 class Backend {
  public:
   Backend(const rb200_model_config& cfg, const rb200_weights* w, int num_blocks, int block_size, int device,
@@ -70,11 +92,29 @@ class Backend {
   size_t kv_block_bytes() const { return static_cast<size_t>(c_.kv_heads) * block_size_ * c_.head_dim * 2; }
   long long layer_elems() const { return static_cast<long long>(c_.kv_heads) * block_size_ * c_.head_dim * num_blocks_; }
 
-  // Returns the number of logit rows. Exactly one of logits_out / token_out is used.
+  // What a pass hands back to the host, per logits row: the float32 logits, or the token the
+  // device picked (greedy with its logit, or sampled per `sampling` with its log-probability).
+  struct Outputs {
+    float* logits = nullptr;
+    size_t cap_floats = 0;
+    int32_t* tokens = nullptr;
+    float* greedy_logit = nullptr;
+    const rb200_sampling_params* sampling = nullptr;  // host, one per logits row; null: greedy
+    double* logprobs = nullptr;
+    size_t cap_rows = 0;
+  };
+  // Returns the number of logit rows.
   int forward(int n_seqs, const int32_t* tokens, const int32_t* chunk_len, const int32_t* start_pos,
               const int32_t* table_len, const int32_t* tables, const uint8_t* want_logits, bool all_logits,
-              rb200_layer_cb cb, void* cb_ctx, float* logits_out, size_t cap_floats, int32_t* token_out,
-              float* logit_out, size_t cap_rows);
+              rb200_layer_cb cb, void* cb_ctx, const Outputs& out);
+
+  // Decode session: a batch of single-token sequences whose positions and block tables stay on
+  // the device between steps (session.cu).
+  void decode_open(int n_seqs, const int32_t* context_len, const int32_t* table_len, const int32_t* tables);
+  void decode_set_slot(int slot, int context_len, int table_len, const int32_t* table);
+  int decode_step(const int32_t* tokens, int n_new_blocks, const int32_t* new_block_seq, const int32_t* new_block_id,
+                  const Outputs& out);
+  void decode_close();
 
   void read_kv_layer(int layer, const int32_t* blocks, int n, void* k_out, void* v_out);
   void write_kv_layer(int layer, const int32_t* blocks, int n, const void* k_in, const void* v_in);
@@ -113,6 +153,13 @@ class Backend {
   struct Plan {
     int T = 0, R = 0, n_decode = 0, n_tiles = 0, max_ctx = 0;
     size_t T4 = 0, S4 = 0;
+    size_t sampling_off = 0;  // ints from the start of the metadata to the rows' sampling parameters (0: none)
+  };
+  // How the logits rows are reduced on the device at the end of a pass.
+  enum class Pick { None, Greedy, Sample };
+  struct PickSpec {
+    Pick kind = Pick::None;
+    bool logprobs = false;
   };
   // Event marks of one pass while profiling is on.
   struct Prof {
@@ -120,7 +167,15 @@ class Backend {
     int first = 0, n = 0;
   };
   enum { kMarkStart, kMarkEnd, kMarkDecodeBegin, kMarkDecodeEnd, kMarkPrefillBegin, kMarkPrefillEnd };
-  void enqueue(const Plan& p, rb200_layer_cb cb, void* cb_ctx, bool argmax, Prof* prof);
+  // `meta`: the packed metadata on the device (the layout forward() documents); `layer_events`:
+  // record layer_done_[l] behind each layer's K/V append (not while the stream is being captured).
+  void enqueue(const int* meta, const Plan& p, rb200_layer_cb cb, void* cb_ctx, PickSpec pick, Prof* prof,
+               bool layer_events = true);
+  void check_pipeline_status();
+  void ensure_row_buffers(int R, PickSpec pick);
+  // Validates the sampling parameters of R rows and says how the device will pick.
+  PickSpec pick_of(const Outputs& out, int R) const;
+  void fetch_outputs(const Outputs& out, int R, PickSpec pick);
   Prof begin_profile();
   void mark(Prof& p, int kind);
   void end_profile(Prof& p);
@@ -144,7 +199,7 @@ class Backend {
   std::vector<Layer> layers_;
   DeviceBuf kc_, vc_;
 
-  DeviceBuf x_, xn_, qkv_, attn_, gu_, act_, logits_, argmax_tok_, argmax_val_;
+  DeviceBuf x_, xn_, qkv_, attn_, gu_, act_, logits_, argmax_tok_, argmax_val_, logprob_;
   DeviceBuf meta_dev_, decode_scratch_, gemv_scratch_, stage_;
   PinnedBuf meta_host_, result_host_;
 
@@ -163,6 +218,10 @@ class Backend {
   int id_next_ = 0;
 
   std::unique_ptr<NcclState> nccl_;
+
+  std::unique_ptr<DecodeSession> session_;
+  cudaEvent_t pass_done_ = nullptr;  // recorded behind a pass that ran as a graph (no per-layer events)
+  bool layer_events_stale_ = false;
 };
 
 }  // namespace rb200

@@ -67,6 +67,24 @@ inline void count_launch(int n = 1) { launch_counter().fetch_add(static_cast<uin
 // Number of SMs of the current device (148 on B200), cached per device.
 int sm_count();
 
+// A kernel attribute (cudaFuncSetAttribute) belongs to the device that is current when it is
+// set, so a process that drives several GPUs has to set it once on each. One of these, as a
+// function-local static next to the launch, remembers the devices already done; first() is
+// true once per device (two threads racing on it both set the attribute, which is harmless:
+// the call is idempotent and only ever raises the limit).
+struct PerDeviceOnce {
+  static constexpr int kMaxDevices = 64;
+  std::atomic<bool> done[kMaxDevices] = {};
+  bool first() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+      cudaGetLastError();
+      return true;  // unknown device: set the attribute every time
+    }
+    return !done[dev].exchange(true, std::memory_order_acq_rel);
+  }
+};
+
 // ---- device primitives ----------------------------------------------------------------
 
 #ifdef __CUDACC__

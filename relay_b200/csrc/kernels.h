@@ -50,11 +50,26 @@ void launch_kv_scatter(void* k, void* v, const int* blocks, int n, size_t block_
                        cudaStream_t st);
 void launch_argmax_rows(const float* logits, int R, int V, int* token_out, float* logit_out, cudaStream_t st);
 
+// ---- sampler.cu ----
+// True when the device sampler covers these parameters (greedy, or temperature sampling without
+// top-k / top-p truncation); `params` of launch_sample_rows is a device array, one per row.
+bool sampling_on_device(const rb200_sampling_params& p, int V);
+void launch_sample_rows(const float* logits, int R, int V, const rb200_sampling_params* params, int* token_out,
+                        double* logprob_out, cudaStream_t st);
+
 // ---- attention.cu ----
 // True when the tensor-core decode / prefill kernels cover this head layout; otherwise the
 // backend routes every token through launch_reference_attention.
 bool fast_attention_supported(const AttnShape& s);
+// Upper bound of the split decode's partial results (512-key slices), for sizing a buffer once.
 size_t decode_scratch_bytes(const AttnShape& s, int n_decode, int max_ctx);
+// What launch_decode_attention does with a batch: keys per slice, slices per context, and the
+// bytes of partial results it parks in its scratch (0 with one slice).
+struct DecodePlan {
+  int slice = 0, parts = 0;
+  size_t scratch_bytes = 0;
+};
+DecodePlan plan_decode(const AttnShape& s, int n_decode, int max_ctx);
 void launch_decode_attention(const AttnShape& s, const float* q, const TokenMeta& m, const int* decode_tokens,
                              int n_decode, int max_ctx, const __half* kc, const __half* vc, float* scratch,
                              __half* out, cudaStream_t st);
@@ -102,8 +117,13 @@ void launch_umma_prefill(const AttnShape& s, const float* q, const TokenMeta& m,
 // ---- umma_gemm.cu ----
 bool umma_gemm_usable(const WeightView& W, const __half* x, int ldx);
 void launch_umma_gemm(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st);
-// 0, or the code a bounded pipeline wait of the tcgen05 GEMM left on the current device.
+// 0, or the code a bounded pipeline wait of a tcgen05 kernel left on the current device. The
+// word is sticky: it keeps the code until umma_status_clear() zeroes it.
 int umma_gemm_status();
+// The status word's device address (one int per device), for callers that read it back in a
+// copy of their own, and its reset, enqueued on `st`.
+const int* umma_status_word();
+void umma_status_clear(cudaStream_t st);
 
 // ---- umma_i8_gemm.cu ----
 // int8 weights x up to 64 tokens on the integer tensor cores: the activations are rewritten

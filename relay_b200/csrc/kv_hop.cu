@@ -69,6 +69,9 @@ void nccl_check(ncclResult_t r, const char* what) {
 
 static ncclComm_t comm_of(const NcclState& s) { return static_cast<ncclComm_t>(s.comm); }
 
+constexpr int kDefaultSyncTimeoutMs = 60000;  // kv_hop_sync(timeout_ms <= 0)
+constexpr int kFinalizeTimeoutMs = 10000;     // finalize / destructor
+
 void Backend::nccl_init(const void* id, int nranks, int rank) {
   set_device();
   RB_REQUIRE(nranks >= 2 && rank >= 0 && rank < nranks, "nccl_init: bad rank");
@@ -89,7 +92,10 @@ void Backend::nccl_init(const void* id, int nranks, int rank) {
 void Backend::nccl_finalize() {
   if (!nccl_) return;
   set_device();
-  RB_CUDA(cudaStreamSynchronize(copy_stream_));
+  // A send or receive the peer never matched would keep the copy stream busy for ever: wait with
+  // the deadline of kv_hop_sync, which aborts the communicator when it runs out.
+  kv_hop_sync(kFinalizeTimeoutMs);
+  if (!nccl_) return;  // aborted
   nccl_check(api().CommDestroy(comm_of(*nccl_)), "ncclCommDestroy");
   nccl_.reset();
 }
@@ -141,7 +147,8 @@ void Backend::recv_kv_layer(int peer, int layer, const int32_t* blocks, int n) {
 
 void Backend::kv_hop_sync(int timeout_ms) {
   set_device();
-  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms > 0 ? timeout_ms : 0);
+  if (timeout_ms <= 0) timeout_ms = kDefaultSyncTimeoutMs;  // never wait without a limit
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
   for (;;) {
     const cudaError_t q = cudaStreamQuery(copy_stream_);
     if (q == cudaSuccess) return;

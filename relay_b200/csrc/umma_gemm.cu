@@ -483,12 +483,10 @@ template <int BN, bool INT8, int MT>
 void launch_umma_cfg(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st, int rows,
                      int splits) {
   using S = UmmaSmem<BN, INT8, MT>;
-  static bool configured = false;
+  static PerDeviceOnce once;
   auto kernel = umma_gemm_kernel<BN, INT8, MT>;
-  if (!configured) {
+  if (once.first())
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
-    configured = true;
-  }
   const CUtensorMap mw = INT8 ? make_map(W.i8, 1, W.N, W.K, W.ld, rows, S::kKB, S::kKB == 128, S::kKB == 64)
                               : make_map(W.f16, 2, W.N, W.K, W.ld, rows, kBlockK, true);
   const CUtensorMap mx = make_map(x, 2, T, W.K, ldx, BN, kBlockK, true);
@@ -623,5 +621,9 @@ int umma_gemm_status() {
   RB_CUDA(cudaMemcpy(&v, status_word(), sizeof(int), cudaMemcpyDeviceToHost));
   return v;
 }
+
+const int* umma_status_word() { return status_word(); }
+
+void umma_status_clear(cudaStream_t st) { RB_CUDA(cudaMemsetAsync(status_word(), 0, sizeof(int), st)); }
 
 }  // namespace rb200

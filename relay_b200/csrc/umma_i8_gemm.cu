@@ -415,12 +415,10 @@ template <int BN, bool FUSED>
 void launch_i8_t(const WeightView& W, const int8_t* digits, const float* tscale, const __half* x, int ldx, float* y, int T,
                  float beta, cudaStream_t st) {
   using S = I8Smem<BN>;
-  static bool configured = false;
+  static PerDeviceOnce once;
   auto kernel = umma_i8_kernel<BN, FUSED>;
-  if (!configured) {
+  if (once.first())
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
-    configured = true;
-  }
   // Rows per CTA and the K split: the pair that needs the fewest (waves x bytes per CTA), where a
   // CTA's fixed cost (prologue, pipeline fill, epilogue) counts like 48 KB of weights. A cluster
   // needs its CTAs on SMs of one GPC at the same time, so fewer clusters than SMs / size are

@@ -436,12 +436,10 @@ template <int D>
 void launch_umma_prefill_d(const AttnShape& s, const float* q, const TokenMeta& m, const int2* tiles, int n_tiles,
                            const __half* kc, const __half* vc, __half* out, cudaStream_t st) {
   using S = PfSmem<D>;
-  static bool configured = false;
+  static PerDeviceOnce once;
   auto kernel = umma_prefill_kernel<D>;
-  if (!configured) {
+  if (once.first())
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
-    configured = true;
-  }
   // The layer's pool as rows of D halves, box = one 16-key page x 64 dims; the row count only
   // bounds coordinates (the kernel never asks for a row the block table does not name).
   const long long rows = 1LL << 31;

@@ -55,6 +55,13 @@ def decode_scratch_bytes(shape: CAttnShape, n_decode: int, max_ctx: int) -> int:
     return _lib.lib().rb200_decode_scratch_bytes(C.byref(shape), n_decode, max_ctx)
 
 
+def decode_plan(shape: CAttnShape, n_decode: int, max_ctx: int):
+    """(keys per slice, slices per context, bytes of partial results) of such a decode launch."""
+    sl, parts = C.c_int32(0), C.c_int32(0)
+    nbytes = _lib.lib().rb200_decode_plan(C.byref(shape), n_decode, max_ctx, C.byref(sl), C.byref(parts))
+    return sl.value, parts.value, nbytes
+
+
 def decode_attention(shape: CAttnShape, q: torch.Tensor, meta: TokenMeta, decode_tokens: torch.Tensor, max_ctx: int,
                      k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                      scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -172,4 +179,12 @@ def kv_scatter(k_pool, v_pool, blocks, block_bytes, staging) -> None:
 def argmax_rows(logits, token_out, logit_out=None):
     R, V = logits.shape
     _lib.check(_lib.lib().rb200_argmax_rows(_p(logits), R, V, _p(token_out), _p(logit_out), _stream()))
+    return token_out
+
+
+def sample_rows(logits, params: torch.Tensor, token_out, logprob_out=None):
+    """The device sampler on logits [R][V]; `params`: a device uint8 tensor holding R
+    rb200_sampling_params (32 bytes each); logprob_out: float64 [R] or None."""
+    R, V = logits.shape
+    _lib.check(_lib.lib().rb200_sample_rows(_p(logits), R, V, _p(params), _p(token_out), _p(logprob_out), _stream()))
     return token_out

@@ -88,10 +88,29 @@ def f16() -> None:
     print("f16", sample.size, "cases")
 
 
+def sampler() -> None:
+    """relay's sampler (engine/src/sampler.cpp, compiled) on the seeded rows of
+    tests/workloads.sampler_cases: the token and log-probability of every row."""
+    from tests.workloads import sampler_cases
+    R = oracle.ref_lib()
+    toks, lps = [], []
+    for lg, t, top_p, top_k, seed, index in sampler_cases():
+        tok, lp = oracle.sample(lg, t, top_p, top_k, seed, index, prefer_reference=True)
+        toks.append(tok)
+        lps.append(lp)
+    u = [R.ref_uniform01(s, i) for s, i in ((0, 0), (1, 0), (0, 1), (2 ** 63, 12345), (987654321, 2 ** 40))]
+    np.savez_compressed(os.path.join(HERE, "sampler_reference.npz"), tokens=np.asarray(toks, np.int32),
+                        logprobs=np.asarray(lps, np.float64), uniform01=np.asarray(u, np.float64))
+    print("sampler", len(toks), "rows")
+
+
 if __name__ == "__main__":
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else oracle.reference_root()
+    if not ref_root:
+        sys.exit("usage: python tests/golden/make_golden.py <root of the relay checkout>")
     oracle.build()
     for name in ("llama-mha", "llama-gqa-tied-bf16", "llama3-rope", "qwen2-bias", "chat-tiny"):
         fixture(ref_root, name)
     c1()
     f16()
+    sampler()

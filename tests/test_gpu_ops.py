@@ -8,7 +8,7 @@ torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
 from oracle import oracle  # noqa: E402
-from tests.workloads import c2_contexts, paged_attention_case, round_f16  # noqa: E402
+from tests.workloads import WideDecodeCase, c2_contexts, paged_attention_case, round_f16  # noqa: E402
 
 
 @pytest.fixture(scope="module")
@@ -224,6 +224,29 @@ def test_decode_attention_full_size_c2_shape(ops):
     assert row_err(got, want) < ATTN_TOL
 
 
+@pytest.mark.parametrize("n_seqs,why", [
+    (256, "2048 (token, KV head) pairs: one 4096-key slice per pair, written straight to the output, no merge"),
+    (64, "512 pairs: the planner cuts each context into a few slices of more than 512 keys and merges them"),
+])
+def test_decode_attention_at_the_decode_step_benchmark_size(ops, n_seqs, why):
+    # The launch the headline decode step makes per layer: every sequence at context 4096, 32 q /
+    # 8 kv heads of 128, block 16. With this many (token, KV head) pairs the slice rule grows the
+    # 512-key slices (launch_decode_attention), a path the small cases above never take.
+    heads, kv_heads, D, bs, ctx = 32, 8, 128, 16, 4096
+    case = WideDecodeCase(5, n_seqs, ctx, heads, kv_heads, D, bs)
+    k16, v16 = case.pools16()
+    shape = ops.attn_shape(heads, kv_heads, D, bs)
+    meta = ops.TokenMeta.from_host(case.pos, case.seq, case.table_off, case.tables)
+    out = torch.zeros((n_seqs, heads * D), dtype=torch.float16, device="cuda")
+    ops.decode_attention(shape, dev(case.q), meta, dev(np.arange(n_seqs, dtype=np.int32)), ctx, dev(k16), dev(v16), out)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy().astype(np.float32)
+    del k16, v16
+    for g in range(n_seqs // case.group):  # the CPU checker, one group of sequences at a time
+        want = oracle_attention(case.group_case(g))
+        assert row_err(got[g * case.group:(g + 1) * case.group], want) < ATTN_TOL, (g, why)
+
+
 PREFILL_CASES = [
     (16, 4, 2, 16, [37, 1, 64, 65, 200], [37, 1, 64, 65, 130]),   # whole prompts, a 1-row chunk, a late chunk
     (32, 8, 4, 16, [300, 129], [192, 129]),
@@ -337,7 +360,7 @@ def test_gemv_matches_oracle(ops, K, N, int8):
             assert row_err(y.cpu().numpy(), want) < LINEAR_TOL
 
 
-@pytest.mark.parametrize("K,N", [(64, 256), (192, 64), (4096, 4096), (4096, 1024), (14336, 4096), (4096, 1000)])
+@pytest.mark.parametrize("K,N", [(64, 256), (192, 64), (4096, 4096), (4096, 1024), (14336, 4096), (4096, 14336), (4096, 1000)])
 @pytest.mark.parametrize("int8", [True, False])
 def test_gemm_matches_oracle(ops, K, N, int8):
     for T, beta in [(9, 0.0), (64, 1.0), (100, 0.0), (256, 1.0)]:
@@ -420,3 +443,20 @@ def test_linear_rejects_bad_shapes(ops):
     with pytest.raises(ValueError, match="at most 8"):
         ops.gemv_int8(w, torch.ones(64, device="cuda"), torch.zeros((9, 128), dtype=torch.float16, device="cuda"),
                       torch.zeros((9, 64), device="cuda"))
+
+
+@pytest.mark.parametrize("splits", [2, 4, 8])
+def test_linear_layers_with_a_forced_cluster_k_split(splits):
+    # RB200_GEMM_SPLITS is read once per process, so each split factor gets a process of its own:
+    # the tcgen05 GEMMs (fp16, int8 widening, int8 few-token) then split K over a cluster of that
+    # size on every shape that allows it, and must still match the CPU checker.
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, RB200_GEMM_SPLITS=str(splits))
+    sel = "(test_gemm_matches_oracle or test_gemv_matches_oracle or test_int8_few_tokens) and (4096-4096 or 14336-4096 or 4160-1024)"
+    r = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-m", "gpu", os.path.abspath(__file__), "-k", sel,
+                        "-p", "no:cacheprovider"], env=env, capture_output=True, text=True, timeout=1200,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout and "no tests ran" not in r.stdout

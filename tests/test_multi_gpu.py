@@ -144,3 +144,31 @@ def test_sequence_sharded_replicas_equal_one_gpu():
     prompts = [rng.integers(0, 256, int(n)).tolist() for n in rng.integers(5, 40, 7)]
     want = [int(np.argmax(be.forward(ForwardBatch([SeqChunk(p, 0, [0, 1, 2])]))[0])) for p in prompts]
     assert got[0][1] == want and got[1][1] == want
+
+
+def test_one_process_drives_backends_on_two_devices():
+    # Kernel attributes (the dynamic shared-memory limit) belong to the device that was current
+    # when they were set: a process with a backend on each of two GPUs must raise them on both.
+    # Every kernel family runs on each device: tcgen05 prefill and GEMMs (D 128, 300-token
+    # prompt), the split decode, the int8 few-token GEMM.
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from relay_b200.backend import make_cuda_backend
+    from relay_b200.types import CudaOptions, ForwardBatch, SeqChunk
+    from tests.test_gpu_model import WIDE_CONFIGS, synthetic
+    cfg = WIDE_CONFIGS["d128_g4"]
+    w = synthetic(cfg, 12)
+    rng = np.random.Generator(np.random.PCG64(2))
+    prompt = rng.integers(0, cfg.vocab, 300).tolist()
+    table = list(range(20))
+    for int8 in (False, True):
+        rows = []
+        for dev in (1, 0):  # the second device first: nothing has configured it yet
+            be = make_cuda_backend(w, 64, 16, device=dev, max_batch_tokens=512, options=CudaOptions(int8_weights=int8))
+            first = be.forward(ForwardBatch([SeqChunk(prompt, 0, table)]))
+            step = be.forward(ForwardBatch([SeqChunk([int(np.argmax(first[0]))], 300, table)]))
+            rows.append((first, step))
+            be.close()
+        assert np.array_equal(rows[0][0], rows[1][0]) and np.array_equal(rows[0][1], rows[1][1])

@@ -203,3 +203,24 @@ def test_kv_gather_scatter_layout():
     k2, v2 = np.zeros_like(k), np.zeros_like(v)
     oracle.kv_scatter(k2, v2, [1, 0, 4], bb, st)
     assert np.array_equal(k2[bb:2 * bb], k[7 * bb:8 * bb]) and np.array_equal(v2[4 * bb:5 * bb], v[9 * bb:10 * bb])
+
+
+def test_sampler_restatement_matches_the_reference_golden_rows():
+    # tokens and log-probabilities relay's compiled sampler gave on these seeded rows (committed)
+    from tests.workloads import sampler_cases
+    z = np.load(f"{GOLDEN}/sampler_reference.npz")
+    for i, (lg, t, top_p, top_k, seed, index) in enumerate(sampler_cases()):
+        tok, lp = oracle.sample(lg, t, top_p, top_k, seed, index, prefer_reference=False)
+        assert tok == int(z["tokens"][i]), (i, t, top_p, top_k)
+        assert abs(lp - float(z["logprobs"][i])) <= 1e-12 * max(1.0, abs(lp))
+    pairs = ((0, 0), (1, 0), (0, 1), (2 ** 63, 12345), (987654321, 2 ** 40))
+    assert [oracle.uniform01(s, i) for s, i in pairs] == z["uniform01"].tolist()
+
+
+@needs_ref
+def test_sampler_restatement_equals_the_compiled_reference():
+    from tests.workloads import sampler_cases
+    for lg, t, top_p, top_k, seed, index in sampler_cases(seed=77, n=120):
+        a = oracle.sample(lg, t, top_p, top_k, seed, index, prefer_reference=True)
+        b = oracle.sample(lg, t, top_p, top_k, seed, index, prefer_reference=False)
+        assert a[0] == b[0] and abs(a[1] - b[1]) <= 1e-12 * max(1.0, abs(a[1]))
