@@ -109,12 +109,16 @@ def prefill_pass(be, fb, cfg, bs, out) -> dict:
 
 
 def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
-    """Disaggregated prefill -> decode hop between GPU pairs (even rank = prefill side, odd rank =
-    decode side): the K/V pages of a 2048-token prompt cross NVLink layer by layer with NCCL
-    send/recv (rb200_send_kv_layer / rb200_recv_kv_layer). Measured twice: all layers back to back
-    (the hop's own bandwidth), and issued from the layer observer while the prompt is prefilled
-    (what the hop adds to the prefill time). Times are the host clock up to rb200_kv_hop_sync, max
-    over ranks."""
+    """The disaggregated variant: GPU 0 prefills 2048-token prompts and streams every layer's K/V
+    pages over NVLink to the decode GPUs (ranks 1 .. N-1, prompts dealt round robin), which land
+    them in their own block ids. Two transports carry the same payload: NCCL send/recv
+    (rb200_send_kv_layer / rb200_recv_kv_layer) and the K/V links (copy engines + counters,
+    rb200_kv_link_*). For each: the hop alone, all layers of a prompt back to back (one pair, and
+    one prompt to every decode GPU at once), and the hop issued from the layer observer while the
+    prompts are prefilled (what it adds to the prefill time). The received pages of three layers
+    are compared byte for byte with the sender's inside the run. Times are the host clock up to
+    rb200_kv_hop_sync, max over ranks."""
+    import hashlib
     from relay_b200.backend import Backend
     uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
     if rank == 0:
@@ -122,10 +126,31 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
     dist.broadcast(uid, src=0)
     be.nccl_init(bytes(uid.cpu().numpy().tobytes()), world, rank)
     per = PREFILL_PROMPT // bs
-    table = [int(b) for b in fb.tables[: int(fb.table_len[0])][:per]]
-    peer = rank ^ 1
-    paired = peer < world
-    sender = rank % 2 == 0
+    n_dec = world - 1
+    n_prompts = 2 * n_dec
+    # prompt p lives in the blocks of decode sequence p on both sides (same ids, different pools)
+    tables = [[int(b) for b in fb.tables[p * (fb.table_len[0]):p * (fb.table_len[0]) + per]] for p in range(n_prompts)]
+    layer_bytes = 2 * be.kv_block_bytes() * per
+    hop_bytes = layer_bytes * cfg.layers
+
+    # one link per decode GPU: a ring of 4 slots, each as large as one layer of a whole prompt
+    slot = (layer_bytes + 255) // 256 * 256
+    links = {}
+    if rank == 0:
+        mine = [be.kv_link_create(4, slot) for _ in range(n_dec)]
+        handles = [h for _, h in mine]
+    else:
+        mine = [be.kv_link_create(4, slot)]
+        handles = [mine[0][1]]
+    gathered = [None] * world
+    dist.all_gather_object(gathered, handles)
+    if rank == 0:
+        for d in range(n_dec):
+            be.kv_link_connect(mine[d][0], gathered[d + 1][0])
+            links[d + 1] = mine[d][0]
+    else:
+        be.kv_link_connect(mine[0][0], gathered[0][rank - 1])
+        links[0] = mine[0][0]
 
     def mx(x):
         t = torch.tensor([x], dtype=torch.float64, device="cuda")
@@ -136,48 +161,111 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
         torch.cuda.synchronize()
         dist.barrier()
 
-    block_bytes = 2 * be.kv_block_bytes()  # K and V
-    raw = float("inf")
-    for _ in range(3):
-        sync_all()
-        t0 = time.perf_counter()
-        if paired:
-            for layer in range(cfg.layers):
-                (be.send_kv_layer if sender else be.recv_kv_layer)(peer, layer, table)
-            be.kv_hop_sync(30000)
-        raw = min(raw, mx(time.perf_counter() - t0))
-    hop_bytes = block_bytes * per * cfg.layers
+    def send(transport, peer, layer, blocks):
+        if transport == "nccl":
+            be.send_kv_layer(peer, layer, blocks)
+        else:
+            be.kv_link_send_layer(links[peer], layer, blocks)
+
+    def recv(transport, layer, blocks):
+        if transport == "nccl":
+            be.recv_kv_layer(0, layer, blocks)
+        else:
+            be.kv_link_recv_layer(links[0], layer, blocks)
+
+    def best_of(fn, n=3):
+        best = float("inf")
+        for _ in range(n):
+            sync_all()
+            t0 = time.perf_counter()
+            fn()
+            best = min(best, mx(time.perf_counter() - t0))
+        return best
 
     rng = np.random.Generator(np.random.PCG64(11))
     toks = rng.integers(0, cfg.vocab, PREFILL_PROMPT)
-    chunks = [(c, flatten(ForwardBatch([SeqChunk([int(t) for t in toks[c:c + PREFILL_CHUNK]], c, table,
-                                                 want_logits=(c + PREFILL_CHUNK == PREFILL_PROMPT))])))
-              for c in range(0, PREFILL_PROMPT, PREFILL_CHUNK)]
-    times = {}
-    for mode in ("plain", "streamed"):
-        best = float("inf")
-        for _ in range(3):
-            sync_all()
-            t0 = time.perf_counter()
-            if sender or not paired:
-                for c, ch in chunks:
-                    blocks = table[c // bs:(c + PREFILL_CHUNK) // bs]
-                    obs = (lambda layer, blocks=blocks: be.send_kv_layer(peer, layer, blocks)) if (mode == "streamed" and paired) else None
-                    be.forward_flat(ch, observer=obs, out=out)
-            elif mode == "streamed":
-                for c, ch in chunks:
-                    for layer in range(cfg.layers):
-                        be.recv_kv_layer(peer, layer, table[c // bs:(c + PREFILL_CHUNK) // bs])
-            if mode == "streamed" and paired:
-                be.kv_hop_sync(30000)
-            best = min(best, mx(time.perf_counter() - t0))
-        times[mode] = best
+
+    def prefill(p, transport):
+        """Chunked prefill of prompt p on GPU 0; with a transport, every layer of every chunk is
+        handed to it from the layer observer."""
+        peer = 1 + p % n_dec
+        for c in range(0, PREFILL_PROMPT, PREFILL_CHUNK):
+            blocks = tables[p][c // bs:(c + PREFILL_CHUNK) // bs]
+            ch = flatten(ForwardBatch([SeqChunk([int(t) for t in toks[c:c + PREFILL_CHUNK]], c, tables[p],
+                                                want_logits=(c + PREFILL_CHUNK == PREFILL_PROMPT))]))
+            obs = (lambda layer, blocks=blocks: send(transport, peer, layer, blocks)) if transport else None
+            be.forward_flat(ch, observer=obs, out=out)
+
+    def receive_all(transport):
+        for p in range(n_prompts):
+            if 1 + p % n_dec != rank:
+                continue
+            for c in range(0, PREFILL_PROMPT, PREFILL_CHUNK):
+                for layer in range(cfg.layers):
+                    recv(transport, layer, tables[p][c // bs:(c + PREFILL_CHUNK) // bs])
+
+    res = {"workload": f"GPU 0 prefills {n_prompts} prompts of {PREFILL_PROMPT} tokens ({PREFILL_PROMPT // PREFILL_CHUNK} chunks each) and streams "
+                       f"{hop_bytes / 1e6:.0f} MB of K/V per prompt, layer by layer, to {n_dec} decode GPU(s)",
+           "bytes_per_prompt": hop_bytes}
+    # the prompts' K/V on GPU 0 (untimed), so that the hops below move real pages
+    if rank == 0:
+        for p in range(n_prompts):
+            prefill(p, None)
+    plain = best_of(lambda: [prefill(p, None) for p in range(n_prompts)] if rank == 0 else None)
+    res["prefill_ms_per_prompt"] = plain / n_prompts * 1e3
+    for transport in ("nccl", "link"):
+        def pair():  # one prompt, all layers back to back, GPU 0 -> GPU 1
+            if rank == 0:
+                for layer in range(cfg.layers):
+                    send(transport, 1, layer, tables[0])
+            elif rank == 1:
+                for layer in range(cfg.layers):
+                    recv(transport, layer, tables[0])
+            be.kv_hop_sync(30000)
+
+        def fan():  # one prompt to every decode GPU at once
+            if rank == 0:
+                for layer in range(cfg.layers):
+                    for d in range(1, world):
+                        send(transport, d, layer, tables[d - 1])
+            else:
+                for layer in range(cfg.layers):
+                    recv(transport, layer, tables[rank - 1])
+            be.kv_hop_sync(30000)
+
+        def streamed():
+            if rank == 0:
+                for p in range(n_prompts):
+                    prefill(p, transport)
+            else:
+                receive_all(transport)
+            be.kv_hop_sync(60000)
+
+        t_pair, t_fan, t_str = best_of(pair), best_of(fan), best_of(streamed)
+        # byte compare of what arrived: three layers of the last prompt each decode GPU received
+        digests = []
+        for p in range(n_prompts - n_dec, n_prompts):
+            if rank == 0 or 1 + p % n_dec == rank:
+                h = hashlib.sha256()
+                for layer in (0, cfg.layers // 2, cfg.layers - 1):
+                    h.update(be.read_kv_layer(layer, tables[p]).tobytes())
+                digests.append((p, h.hexdigest()))
+        allg = [None] * world
+        dist.all_gather_object(allg, digests)
+        want = dict(allg[0])
+        identical = all(want[p] == d for r in range(1, world) for p, d in allg[r])
+        res[transport] = {"pair_ms": t_pair * 1e3, "pair_gbs": hop_bytes / t_pair / 1e9,
+                          "fan_out_ms": t_fan * 1e3, "fan_out_gbs_from_gpu0": hop_bytes * n_dec / t_fan / 1e9,
+                          "streamed_prefill_ms_per_prompt": t_str / n_prompts * 1e3,
+                          "exposed_ms_per_prompt": (t_str - plain) / n_prompts * 1e3,
+                          "received_pages_identical": bool(identical)}
+    res["gbs_per_pair"] = res["link"]["pair_gbs"]
+    res["transport_note"] = ("nccl: page gather -> ncclSend / ncclRecv -> scatter on one copy stream; link: gather -> copy-engine "
+                             "peer copy into the receiver's ring -> scatter, ordered by two counters (no SM held during the copy)")
+    for l in links.values():
+        be.kv_link_close(l)
     be.nccl_finalize()
-    return {"workload": f"K/V of a {PREFILL_PROMPT}-token prompt, {cfg.layers} layers, {hop_bytes / 1e6:.0f} MB per pair, "
-                        f"{world // 2} pair(s) at once (even rank -> odd rank)",
-            "bytes_per_pair": hop_bytes, "back_to_back_ms": raw * 1e3, "gbs_per_pair": hop_bytes / raw / 1e9,
-            "prefill_ms": times["plain"] * 1e3, "prefill_streaming_kv_ms": times["streamed"] * 1e3,
-            "transport": "NCCL send/recv over NVLink, page gather/scatter kernels on the copy stream"}
+    return res
 
 
 class ClockSampler:

@@ -253,6 +253,30 @@ int rb200_recv_kv_layer(rb200_backend* b, int peer, int layer, const int32_t* bl
  * wait the same way with a 10 s limit, so an unmatched send or receive cannot block them. */
 int rb200_kv_hop_sync(rb200_backend* b, int timeout_ms);
 
+/* ---- the same hop over a K/V link: copy engines and two counters, no library kernel -------
+ * A link joins one backend in each of two processes on one box. Each end creates its side (a
+ * ring of n_slots landing slots of slot_bytes each in its own device memory) and gets a
+ * handle; the ends swap handles out of band (the host connection that carries the transfer
+ * engine's Hello frame, engine/src/kv_transfer.cpp:185-200) and connect. The k-th
+ * rb200_kv_link_send_layer on one end pairs with the k-th rb200_kv_link_recv_layer on the
+ * other: same payload and order as the Layer frames (engine/include/relay/kv_transfer.h:14-18;
+ * sender engine/src/kv_transfer.cpp:107-128, receiver :269-301). The sender gathers the pages
+ * into its slot, a copy engine moves the slot across NVLink, the receiver scatters it into its
+ * own block ids; slots are reused once the receiver has acknowledged them. Both calls only
+ * enqueue (the send is ordered behind the layer's K/V append on the device);
+ * rb200_kv_hop_sync waits for the links too, and on its deadline releases every wait the peer
+ * has not satisfied and marks those links broken. A layer with more blocks than a slot holds
+ * travels as several messages, cut the same way on both ends. */
+#define RB200_KV_LINK_HANDLE_BYTES 128
+/* Returns the link's id (>= 0) on this backend and fills handle_out (RB200_KV_LINK_HANDLE_BYTES). */
+int rb200_kv_link_create(rb200_backend* b, int n_slots, size_t slot_bytes, void* handle_out);
+/* Maps the other end's region; both ends must have been created with the same ring. */
+int rb200_kv_link_connect(rb200_backend* b, int link, const void* peer_handle);
+int rb200_kv_link_send_layer(rb200_backend* b, int link, int layer, const int32_t* blocks, int n);
+int rb200_kv_link_recv_layer(rb200_backend* b, int link, int layer, const int32_t* blocks, int n);
+/* After rb200_kv_hop_sync; unmaps the peer's region and frees this end's. */
+int rb200_kv_link_close(rb200_backend* b, int link);
+
 /* ---- operators on device buffers ----------------------------------------------------- */
 /* All pointers below are DEVICE pointers on the current device unless said otherwise;
  * `stream` is a cudaStream_t (NULL: the default stream). Calls return once enqueued. */

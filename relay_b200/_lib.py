@@ -17,6 +17,7 @@ ERR_INVALID_ARGUMENT, ERR_OUT_OF_RANGE, ERR_RUNTIME, ERR_LOGIC = 1, 2, 3, 4
 DECODE_SLICE = 512
 PREFILL_ROWS = 64
 NCCL_ID_BYTES = 128
+KV_LINK_HANDLE_BYTES = 128
 STATIC_DECODE_SCRATCH_BYTES = 8 << 20
 
 LAYER_CB = C.CFUNCTYPE(None, C.c_void_p, C.c_int)
@@ -78,6 +79,11 @@ SIGNATURES = {
     "rb200_send_kv_layer": (I, [P, I, I, P, I]),
     "rb200_recv_kv_layer": (I, [P, I, I, P, I]),
     "rb200_kv_hop_sync": (I, [P, I]),
+    "rb200_kv_link_create": (I, [P, I, SZ, P]),
+    "rb200_kv_link_connect": (I, [P, I, P]),
+    "rb200_kv_link_send_layer": (I, [P, I, I, P, I]),
+    "rb200_kv_link_recv_layer": (I, [P, I, I, P, I]),
+    "rb200_kv_link_close": (I, [P, I]),
     "rb200_decode_scratch_bytes": (SZ, [C.POINTER(CAttnShape), I, I]),
     "rb200_decode_plan": (SZ, [C.POINTER(CAttnShape), I, I, P, P]),
     "rb200_decode_attention": (I, [C.POINTER(CAttnShape), P, C.POINTER(CTokenMeta), P, I, I, P, P, P, SZ, P, P]),

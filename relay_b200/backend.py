@@ -308,6 +308,27 @@ class Backend:
         b = i32(blocks)
         _lib.check(self._L.rb200_recv_kv_layer(self._h, peer, layer, ptr(b), b.size))
 
+    # -- K/V links (copy engines + counters; include/relay_b200.h) -----------------------------
+    def kv_link_create(self, n_slots: int, slot_bytes: int) -> Tuple[int, bytes]:
+        """(link id, handle to give to the other end)."""
+        buf = C.create_string_buffer(_lib.KV_LINK_HANDLE_BYTES)
+        link = _lib.check(self._L.rb200_kv_link_create(self._h, n_slots, slot_bytes, buf))
+        return link, buf.raw
+
+    def kv_link_connect(self, link: int, peer_handle: bytes) -> None:
+        _lib.check(self._L.rb200_kv_link_connect(self._h, link, C.c_char_p(peer_handle)))
+
+    def kv_link_send_layer(self, link: int, layer: int, blocks: Sequence[int]) -> None:
+        b = i32(blocks)
+        _lib.check(self._L.rb200_kv_link_send_layer(self._h, link, layer, ptr(b), b.size))
+
+    def kv_link_recv_layer(self, link: int, layer: int, blocks: Sequence[int]) -> None:
+        b = i32(blocks)
+        _lib.check(self._L.rb200_kv_link_recv_layer(self._h, link, layer, ptr(b), b.size))
+
+    def kv_link_close(self, link: int) -> None:
+        _lib.check(self._L.rb200_kv_link_close(self._h, link))
+
     def kv_hop_sync(self, timeout_ms: int = 0) -> None:
         _lib.check(self._L.rb200_kv_hop_sync(self._h, timeout_ms))
 

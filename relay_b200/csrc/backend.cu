@@ -5,9 +5,11 @@
 // drive it unchanged through the adapter; the kernels are this repository's own.
 #include "backend.h"
 
+#include <chrono>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <thread>
 
 namespace rb200 {
 
@@ -290,6 +292,16 @@ Backend::~Backend() {
   nccl_finalize_noexcept();
   cudaDeviceSynchronize();
   session_.reset();
+  try {  // a link wait the peer never satisfied must not block the destructor
+    bool idle = links_idle();
+    for (int i = 0; i < 50 && !idle; ++i) {  // work in flight gets half a second to drain
+      std::this_thread::sleep_for(std::chrono::milliseconds(10));
+      idle = links_idle();
+    }
+    if (!idle) links_release();
+  } catch (...) {
+  }
+  links_.clear();
   if (pass_done_) cudaEventDestroy(pass_done_);
   for (auto e : layer_done_) cudaEventDestroy(e);
   for (IdSlot& s : id_slots_)
@@ -1054,6 +1066,45 @@ int rb200_recv_kv_layer(rb200_backend* b, int peer, int layer, const int32_t* bl
   return guarded([&] {
     RB_REQUIRE(b != nullptr, "recv_kv_layer: null backend");
     b->impl->recv_kv_layer(peer, layer, blocks, n);
+    return 0;
+  });
+}
+
+int rb200_kv_link_create(rb200_backend* b, int n_slots, size_t slot_bytes, void* handle_out) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "kv_link_create: null backend");
+    return b->impl->kv_link_create(n_slots, slot_bytes, handle_out);
+  });
+}
+
+int rb200_kv_link_connect(rb200_backend* b, int link, const void* peer_handle) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "kv_link_connect: null backend");
+    b->impl->kv_link_connect(link, peer_handle);
+    return 0;
+  });
+}
+
+int rb200_kv_link_send_layer(rb200_backend* b, int link, int layer, const int32_t* blocks, int n) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "kv_link_send_layer: null backend");
+    b->impl->kv_link_send_layer(link, layer, blocks, n);
+    return 0;
+  });
+}
+
+int rb200_kv_link_recv_layer(rb200_backend* b, int link, int layer, const int32_t* blocks, int n) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "kv_link_recv_layer: null backend");
+    b->impl->kv_link_recv_layer(link, layer, blocks, n);
+    return 0;
+  });
+}
+
+int rb200_kv_link_close(rb200_backend* b, int link) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "kv_link_close: null backend");
+    b->impl->kv_link_close(link);
     return 0;
   });
 }

@@ -59,6 +59,19 @@ struct NcclState {
   int nranks = 0, rank = -1;
 };
 
+// One end of a K/V link (kv_link.cu): this end's region (a ring of landing slots with two
+// counters each), the peer's region mapped through CUDA IPC, and the streams the link's work runs on.
+struct KvLink {
+  int n_slots = 0;
+  size_t slot_bytes = 0;
+  DeviceBuf region;
+  void* peer = nullptr;
+  cudaStream_t streams[2] = {nullptr, nullptr};  // consecutive messages alternate between them
+  uint32_t sent = 0, received = 0;  // messages enqueued so far in each direction
+  bool broken = false;
+  ~KvLink();
+};
+
 struct DecodeSession {
   int S = 0;    // slots
   int cap = 0;  // block-table entries per slot (a multiple of 4: tables stay 16-byte aligned)
@@ -134,6 +147,13 @@ class Backend {
   void recv_kv_layer(int peer, int layer, const int32_t* blocks, int n);
   void kv_hop_sync(int timeout_ms);
   void nccl_finalize_noexcept() noexcept;
+
+  // kv_link.cu
+  int kv_link_create(int n_slots, size_t slot_bytes, void* handle_out);
+  void kv_link_connect(int link, const void* peer_handle);
+  void kv_link_send_layer(int link, int layer, const int32_t* blocks, int n);
+  void kv_link_recv_layer(int link, int layer, const int32_t* blocks, int n);
+  void kv_link_close(int link);
 
  private:
   void set_device() const;
@@ -218,6 +238,10 @@ class Backend {
   int id_next_ = 0;
 
   std::unique_ptr<NcclState> nccl_;
+  std::vector<std::unique_ptr<KvLink>> links_;  // under copy_mu_
+  KvLink& link_of(int link);
+  bool links_idle();
+  void links_release();
 
   std::unique_ptr<DecodeSession> session_;
   cudaEvent_t pass_done_ = nullptr;  // recorded behind a pass that ran as a graph (no per-layer events)

@@ -26,6 +26,7 @@ struct NcclApi {
   void* lib = nullptr;
   ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
   ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
@@ -46,6 +47,7 @@ NcclApi& api() {
     auto sym = [&](const char* n) { return dlsym(a.lib, n); };
     a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(sym("ncclGetUniqueId"));
     a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(sym("ncclCommInitRank"));
+    a.CommInitRankConfig = reinterpret_cast<decltype(a.CommInitRankConfig)>(sym("ncclCommInitRankConfig"));
     a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(sym("ncclCommDestroy"));
     a.CommAbort = reinterpret_cast<decltype(a.CommAbort)>(sym("ncclCommAbort"));
     a.CommGetAsyncError = reinterpret_cast<decltype(a.CommGetAsyncError)>(sym("ncclCommGetAsyncError"));
@@ -69,6 +71,32 @@ void nccl_check(ncclResult_t r, const char* what) {
 
 static ncclComm_t comm_of(const NcclState& s) { return static_cast<ncclComm_t>(s.comm); }
 
+constexpr int kInitTimeoutMs = 120000;  // communicator set-up
+constexpr int kCallTimeoutMs = 60000;   // a send / receive call that has to connect the two ranks first
+
+// The communicator is non-blocking: a call may return ncclInProgress while NCCL still works on
+// it in the background (rendezvous, the first connection between two ranks). The next call on the
+// communicator has to wait for that; this polls with a host deadline and aborts the communicator
+// when it runs out, so no call of this file can block for ever on a peer that never shows up.
+static void wait_ready(ncclComm_t comm, ncclResult_t r, int timeout_ms, const char* what) {
+  const NcclApi& a = api();
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  while (r == ncclInProgress) {
+    if (!a.CommGetAsyncError) return;  // a library too old to poll: it is blocking anyway
+    if (a.CommGetAsyncError(comm, &r) != ncclSuccess) break;
+    if (r != ncclInProgress) break;
+    if (std::chrono::steady_clock::now() > deadline) {
+      a.CommAbort(comm);
+      fail(RB200_ERR_RUNTIME, std::string(what) + ": timed out; communicator aborted");
+    }
+    std::this_thread::sleep_for(std::chrono::microseconds(100));
+  }
+  if (r != ncclSuccess) {
+    a.CommAbort(comm);
+    fail(RB200_ERR_RUNTIME, std::string("NCCL error in ") + what + ": " + (a.GetErrorString ? a.GetErrorString(r) : "?"));
+  }
+}
+
 constexpr int kDefaultSyncTimeoutMs = 60000;  // kv_hop_sync(timeout_ms <= 0)
 constexpr int kFinalizeTimeoutMs = 10000;     // finalize / destructor
 
@@ -82,7 +110,16 @@ void Backend::nccl_init(const void* id, int nranks, int rank) {
   std::memcpy(&uid, id, sizeof(uid));
   auto st = std::make_unique<NcclState>();
   ncclComm_t comm = nullptr;
-  nccl_check(a.CommInitRank(&comm, nranks, uid, rank), "ncclCommInitRank");
+  if (a.CommInitRankConfig && a.CommGetAsyncError) {
+    ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+    cfg.blocking = 0;
+    const ncclResult_t r = a.CommInitRankConfig(&comm, nranks, uid, rank, &cfg);
+    if (r != ncclSuccess && r != ncclInProgress) nccl_check(r, "ncclCommInitRankConfig");
+    RB_REQUIRE(comm != nullptr, "nccl_init: no communicator");
+    wait_ready(comm, ncclInProgress, kInitTimeoutMs, "ncclCommInitRankConfig");
+  } else {
+    nccl_check(a.CommInitRank(&comm, nranks, uid, rank), "ncclCommInitRank");
+  }
   st->comm = comm;
   st->nranks = nranks;
   st->rank = rank;
@@ -96,8 +133,10 @@ void Backend::nccl_finalize() {
   // the deadline of kv_hop_sync, which aborts the communicator when it runs out.
   kv_hop_sync(kFinalizeTimeoutMs);
   if (!nccl_) return;  // aborted
-  nccl_check(api().CommDestroy(comm_of(*nccl_)), "ncclCommDestroy");
+  ncclComm_t comm = comm_of(*nccl_);
   nccl_.reset();
+  const ncclResult_t r = api().CommDestroy(comm);
+  if (r != ncclSuccess && r != ncclInProgress) nccl_check(r, "ncclCommDestroy");
 }
 
 void Backend::nccl_finalize_noexcept() noexcept {
@@ -125,7 +164,13 @@ void Backend::send_kv_layer(int peer, int layer, const int32_t* blocks, int n) {
   const size_t off = static_cast<size_t>(layer) * layer_elems();
   launch_kv_gather(kc_.as<__half>() + off, vc_.as<__half>() + off, ids, n, bb, kv_staging_.p, copy_stream_);
   RB_CUDA(cudaGetLastError());
-  nccl_check(api().Send(kv_staging_.p, 2 * static_cast<size_t>(n) * bb, ncclInt8, peer, comm_of(*nccl_), copy_stream_), "ncclSend");
+  try {
+    wait_ready(comm_of(*nccl_), api().Send(kv_staging_.p, 2 * static_cast<size_t>(n) * bb, ncclInt8, peer, comm_of(*nccl_), copy_stream_),
+               kCallTimeoutMs, "ncclSend");
+  } catch (...) {
+    nccl_.reset();  // wait_ready aborted the communicator
+    throw;
+  }
 }
 
 void Backend::recv_kv_layer(int peer, int layer, const int32_t* blocks, int n) {
@@ -139,7 +184,13 @@ void Backend::recv_kv_layer(int peer, int layer, const int32_t* blocks, int n) {
   const size_t bb = kv_block_bytes();
   ensure_kv_staging(n);
   const int* ids = static_cast<const int*>(staging_ids(blocks, n));
-  nccl_check(api().Recv(kv_staging_.p, 2 * static_cast<size_t>(n) * bb, ncclInt8, peer, comm_of(*nccl_), copy_stream_), "ncclRecv");
+  try {
+    wait_ready(comm_of(*nccl_), api().Recv(kv_staging_.p, 2 * static_cast<size_t>(n) * bb, ncclInt8, peer, comm_of(*nccl_), copy_stream_),
+               kCallTimeoutMs, "ncclRecv");
+  } catch (...) {
+    nccl_.reset();
+    throw;
+  }
   const size_t off = static_cast<size_t>(layer) * layer_elems();
   launch_kv_scatter(kc_.as<__half>() + off, vc_.as<__half>() + off, ids, n, bb, kv_staging_.p, copy_stream_);
   RB_CUDA(cudaGetLastError());
@@ -151,8 +202,12 @@ void Backend::kv_hop_sync(int timeout_ms) {
   const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
   for (;;) {
     const cudaError_t q = cudaStreamQuery(copy_stream_);
-    if (q == cudaSuccess) return;
-    if (q != cudaErrorNotReady) RB_CUDA(q);
+    if (q == cudaSuccess) {
+      std::lock_guard<std::mutex> lock(copy_mu_);
+      if (links_idle()) return;
+    } else if (q != cudaErrorNotReady) {
+      RB_CUDA(q);
+    }
     if (nccl_ && api().CommGetAsyncError) {
       ncclResult_t async = ncclSuccess;
       api().CommGetAsyncError(comm_of(*nccl_), &async);
@@ -162,11 +217,16 @@ void Backend::kv_hop_sync(int timeout_ms) {
         fail(RB200_ERR_RUNTIME, "NCCL reported an asynchronous error; communicator aborted");
       }
     }
-    if (timeout_ms > 0 && std::chrono::steady_clock::now() > deadline) {
-      if (nccl_) {
+    if (std::chrono::steady_clock::now() > deadline) {
+      if (nccl_ && cudaStreamQuery(copy_stream_) == cudaErrorNotReady) {
         api().CommAbort(comm_of(*nccl_));
         nccl_.reset();
       }
+      {
+        std::lock_guard<std::mutex> lock(copy_mu_);
+        links_release();
+      }
+      cudaGetLastError();
       fail(RB200_ERR_RUNTIME, "kv_hop_sync: timed out; communicator aborted");
     }
     std::this_thread::sleep_for(std::chrono::microseconds(50));

@@ -1,0 +1,285 @@
+// K/V links: the prefill -> decode hop between two GPUs of one box without a library kernel in
+// the way. It carries the same payload as the NCCL hop of kv_hop.cu and the Layer frames of
+// relay's transfer engine (engine/include/relay/kv_transfer.h:14-18: all K blocks of a layer,
+// then all V blocks, request-relative order; sender engine/src/kv_transfer.cpp:107-128,
+// receiver :269-301), but moves it with the copy engines and orders it with two counters, so
+// that no SM is held while the bytes cross NVLink and no per-operation library latency is paid.
+//
+// Each end of a link owns one device region: a ring of `n_slots` landing slots and, per slot,
+// two 32-bit counters. The ends exchange CUDA IPC handles of their regions out of band (the host
+// connection that already carries relay's Hello frame) and map each other's region.
+//
+//   sender, message k (slot s = k % n_slots):
+//                        wait until its own ack[s] says the message that last used s was scattered;
+//                        gather the layer's pages into its own slot (one kernel, HBM speed);
+//                        copy the slot into the peer's slot (copy engine over NVLink);
+//                        store k + 1 into the peer's arrived[s] (one-thread kernel);
+//   receiver, message k: stream-wait until its own arrived[s] reaches k + 1;
+//                        scatter its slot into the pages of its own block ids;
+//                        store k + 1 into the peer's ack[s].
+// Consecutive messages alternate between two streams on each end, so the gather of message
+// k + 1 runs while the copy engine moves message k; the per-slot counters keep that safe.
+//
+// The waits are stream memory operations (cuStreamWaitValue32) on the waiting GPU's own memory:
+// no kernel spins, and a wait the peer never satisfies is released from the host when
+// rb200_kv_hop_sync's deadline runs out (the link is then marked broken). Only plain stores from
+// this library's own one-thread kernels and copy-engine copies touch the peer's memory; no TMA
+// and no library kernel ever sees a peer pointer. Messages pair up by order on the link, which
+// the host connection's ordered frames already guarantee.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <cstring>
+#include <string>
+
+#include "backend.h"
+
+namespace rb200 {
+
+namespace {
+
+constexpr uint32_t kLinkMagic = 0x4b4c3230u;  // "02LK"
+constexpr int kMaxSlots = 64;
+constexpr size_t kControlBytes = 512;         // arrived[64] @0, ack[64] @256; the ring starts behind
+constexpr int kMaxIds = 960;                  // block ids handed to a kernel by value (3.8 KB of parameters)
+
+struct LinkHandle {  // what crosses the host connection: RB200_KV_LINK_HANDLE_BYTES
+  uint32_t magic;
+  int32_t n_slots;
+  uint64_t slot_bytes;
+  cudaIpcMemHandle_t mem;
+  unsigned char pad[RB200_KV_LINK_HANDLE_BYTES - 16 - sizeof(cudaIpcMemHandle_t)];
+};
+static_assert(sizeof(LinkHandle) == RB200_KV_LINK_HANDLE_BYTES, "link handle size");
+
+struct IdList {
+  int n;
+  int ids[kMaxIds];
+};
+
+// Pages of one layer into / out of a contiguous [K of each block][V of each block] slot; the
+// block ids ride in the kernel's parameters, so no upload precedes the launch.
+__global__ void link_gather_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, const __grid_constant__ IdList ids,
+                                   long long block_vec, uint4* __restrict__ out) {
+  const int i = blockIdx.x, which = blockIdx.y;
+  const uint4* src = (which ? v : k) + static_cast<long long>(ids.ids[i]) * block_vec;
+  uint4* dst = out + (static_cast<long long>(which) * ids.n + i) * block_vec;
+  for (long long e = blockIdx.z * blockDim.x + threadIdx.x; e < block_vec; e += static_cast<long long>(gridDim.z) * blockDim.x)
+    dst[e] = src[e];
+}
+
+__global__ void link_scatter_kernel(uint4* __restrict__ k, uint4* __restrict__ v, const __grid_constant__ IdList ids,
+                                    long long block_vec, const uint4* __restrict__ in) {
+  const int i = blockIdx.x, which = blockIdx.y;
+  uint4* dst = (which ? v : k) + static_cast<long long>(ids.ids[i]) * block_vec;
+  const uint4* src = in + (static_cast<long long>(which) * ids.n + i) * block_vec;
+  for (long long e = blockIdx.z * blockDim.x + threadIdx.x; e < block_vec; e += static_cast<long long>(gridDim.z) * blockDim.x)
+    dst[e] = src[e];
+}
+
+// One store of `value` to a counter in the peer's region, behind everything this stream has
+// written there (the copy ahead of it has completed in stream order; the fence orders this
+// thread's store behind it system-wide).
+__global__ void link_signal_kernel(uint32_t* counter, uint32_t value) {
+  __threadfence_system();
+  *reinterpret_cast<volatile uint32_t*>(counter) = value;
+  __threadfence_system();
+}
+
+using WaitValueFn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+
+WaitValueFn wait_value_fn() {
+  static WaitValueFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<WaitValueFn>(p);
+    else
+      cudaGetLastError();
+  });
+  if (!fn) fail(RB200_ERR_RUNTIME, "cuStreamWaitValue32 is not available from this driver");
+  return fn;
+}
+
+void stream_wait_geq(cudaStream_t st, uint32_t* addr, uint32_t value) {
+  const CUresult r = wait_value_fn()(st, reinterpret_cast<CUdeviceptr>(addr), value, CU_STREAM_WAIT_VALUE_GEQ);
+  if (r != CUDA_SUCCESS) fail(RB200_ERR_RUNTIME, "cuStreamWaitValue32 failed with code " + std::to_string(static_cast<int>(r)));
+}
+
+uint32_t* arrived_of(void* region, const KvLink& l, uint32_t k) {
+  return static_cast<uint32_t*>(region) + k % static_cast<uint32_t>(l.n_slots);
+}
+uint32_t* ack_of(void* region, const KvLink& l, uint32_t k) {
+  return reinterpret_cast<uint32_t*>(static_cast<char*>(region) + 256) + k % static_cast<uint32_t>(l.n_slots);
+}
+char* slot_of(void* region, const KvLink& l, uint32_t k) {
+  return static_cast<char*>(region) + kControlBytes + static_cast<size_t>(k % static_cast<uint32_t>(l.n_slots)) * l.slot_bytes;
+}
+
+bool sm_copy() {  // RB200_KV_LINK=sm: the gather kernel stores straight into the peer's slot (no copy engine)
+  static const bool on = [] {
+    const char* e = std::getenv("RB200_KV_LINK");
+    return e && std::string(e) == "sm";
+  }();
+  return on;
+}
+
+}  // namespace
+
+KvLink::~KvLink() {
+  if (peer) cudaIpcCloseMemHandle(peer);
+  for (cudaStream_t s : streams)
+    if (s) cudaStreamDestroy(s);
+}
+
+KvLink& Backend::link_of(int link) {
+  RB_REQUIRE(link >= 0 && link < static_cast<int>(links_.size()) && links_[link], "kv link: no such link");
+  return *links_[link];
+}
+
+int Backend::kv_link_create(int n_slots, size_t slot_bytes, void* handle_out) {
+  set_device();
+  RB_REQUIRE(n_slots >= 1 && n_slots <= kMaxSlots && handle_out, "kv_link_create: bad arguments");
+  const size_t bb = kv_block_bytes();
+  RB_REQUIRE(slot_bytes >= 2 * bb && slot_bytes % 256 == 0, "kv_link_create: a slot holds at least one K and one V block and is a multiple of 256 bytes");
+  auto l = std::make_unique<KvLink>();
+  l->n_slots = n_slots;
+  l->slot_bytes = slot_bytes;
+  l->region = DeviceBuf(kControlBytes + static_cast<size_t>(n_slots) * slot_bytes);
+  RB_CUDA(cudaMemset(l->region.p, 0, kControlBytes));
+  for (cudaStream_t& s : l->streams) RB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  LinkHandle h{};
+  h.magic = kLinkMagic;
+  h.n_slots = n_slots;
+  h.slot_bytes = slot_bytes;
+  RB_CUDA(cudaIpcGetMemHandle(&h.mem, l->region.p));
+  std::memcpy(handle_out, &h, sizeof(h));
+  wait_value_fn();  // fail now rather than at the first message
+  std::lock_guard<std::mutex> lock(copy_mu_);
+  links_.push_back(std::move(l));
+  return static_cast<int>(links_.size()) - 1;
+}
+
+void Backend::kv_link_connect(int link, const void* peer_handle) {
+  set_device();
+  RB_REQUIRE(peer_handle != nullptr, "kv_link_connect: null handle");
+  std::lock_guard<std::mutex> lock(copy_mu_);
+  KvLink& l = link_of(link);
+  RB_REQUIRE(l.peer == nullptr, "kv_link_connect: already connected");
+  LinkHandle h;
+  std::memcpy(&h, peer_handle, sizeof(h));
+  RB_REQUIRE(h.magic == kLinkMagic, "kv_link_connect: not a link handle");
+  RB_REQUIRE(h.n_slots == l.n_slots && h.slot_bytes == l.slot_bytes, "kv_link_connect: the two ends were created with different rings");
+  void* p = nullptr;
+  RB_CUDA(cudaIpcOpenMemHandle(&p, h.mem, cudaIpcMemLazyEnablePeerAccess));
+  l.peer = p;
+}
+
+void Backend::kv_link_close(int link) {
+  set_device();
+  std::lock_guard<std::mutex> lock(copy_mu_);
+  KvLink& l = link_of(link);
+  // The caller has synchronised the hop (rb200_kv_hop_sync) before closing; a link that is
+  // still busy here is waiting for a peer that will not come.
+  if (cudaStreamQuery(l.streams[0]) == cudaErrorNotReady || cudaStreamQuery(l.streams[1]) == cudaErrorNotReady) links_release();
+  cudaGetLastError();
+  links_[link].reset();
+}
+
+void Backend::kv_link_send_layer(int link, int layer, const int32_t* blocks, int n) {
+  set_device();
+  check_layer(layer);
+  check_blocks(blocks, n);
+  if (n == 0) return;
+  std::lock_guard<std::mutex> lock(copy_mu_);
+  KvLink& l = link_of(link);
+  RB_REQUIRE(l.peer != nullptr, "kv_link_send_layer: the link is not connected");
+  if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
+  const size_t bb = kv_block_bytes();
+  const int per_msg = static_cast<int>(std::min<size_t>(kMaxIds, l.slot_bytes / (2 * bb)));
+  const long long vec = static_cast<long long>(bb / 16);
+  const size_t off = static_cast<size_t>(layer) * layer_elems();
+  // The gather must see this layer's appends of the latest forward pass.
+  for (cudaStream_t s : l.streams) RB_CUDA(cudaStreamWaitEvent(s, layer_done_[layer], 0));
+  for (int b0 = 0; b0 < n; b0 += per_msg) {
+    const int m = std::min(per_msg, n - b0);
+    const uint32_t k = l.sent++;
+    cudaStream_t st = l.streams[k & 1];
+    if (k >= static_cast<uint32_t>(l.n_slots)) stream_wait_geq(st, ack_of(l.region.p, l, k), k - l.n_slots + 1);
+    IdList ids;
+    ids.n = m;
+    std::memcpy(ids.ids, blocks + b0, static_cast<size_t>(m) * 4);
+    const size_t bytes = 2 * static_cast<size_t>(m) * bb;
+    char* mine = slot_of(l.region.p, l, k);
+    char* theirs = slot_of(l.peer, l, k);
+    dim3 grid(m, 2, static_cast<unsigned>(std::max<long long>(1, std::min<long long>(8, vec / 256))));
+    count_launch(2);
+    link_gather_kernel<<<grid, 256, 0, st>>>(kc_.as<uint4>() + off / 8, vc_.as<uint4>() + off / 8, ids, vec,
+                                             reinterpret_cast<uint4*>(sm_copy() ? theirs : mine));
+    if (!sm_copy()) RB_CUDA(cudaMemcpyAsync(theirs, mine, bytes, cudaMemcpyDefault, st));  // peer copy, by address
+    link_signal_kernel<<<1, 1, 0, st>>>(arrived_of(l.peer, l, k), k + 1);
+    RB_CUDA(cudaGetLastError());
+  }
+}
+
+void Backend::kv_link_recv_layer(int link, int layer, const int32_t* blocks, int n) {
+  set_device();
+  check_layer(layer);
+  check_blocks(blocks, n);
+  if (n == 0) return;
+  std::lock_guard<std::mutex> lock(copy_mu_);
+  KvLink& l = link_of(link);
+  RB_REQUIRE(l.peer != nullptr, "kv_link_recv_layer: the link is not connected");
+  if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
+  const size_t bb = kv_block_bytes();
+  const int per_msg = static_cast<int>(std::min<size_t>(kMaxIds, l.slot_bytes / (2 * bb)));
+  const long long vec = static_cast<long long>(bb / 16);
+  const size_t off = static_cast<size_t>(layer) * layer_elems();
+  for (int b0 = 0; b0 < n; b0 += per_msg) {
+    const int m = std::min(per_msg, n - b0);
+    const uint32_t k = l.received++;
+    cudaStream_t st = l.streams[k & 1];
+    stream_wait_geq(st, arrived_of(l.region.p, l, k), k + 1);
+    IdList ids;
+    ids.n = m;
+    std::memcpy(ids.ids, blocks + b0, static_cast<size_t>(m) * 4);
+    dim3 grid(m, 2, static_cast<unsigned>(std::max<long long>(1, std::min<long long>(8, vec / 256))));
+    count_launch(2);
+    link_scatter_kernel<<<grid, 256, 0, st>>>(kc_.as<uint4>() + off / 8, vc_.as<uint4>() + off / 8, ids, vec,
+                                              reinterpret_cast<const uint4*>(slot_of(l.region.p, l, k)));
+    link_signal_kernel<<<1, 1, 0, st>>>(ack_of(l.peer, l, k), k + 1);
+    RB_CUDA(cudaGetLastError());
+  }
+}
+
+// True when every link stream is idle. On `deadline` (links_sync gave up), every wait a peer has
+// not satisfied is released from the host by writing the awaited counters, and the links are
+// marked broken: what their last messages scattered is not to be used.
+bool Backend::links_idle() {
+  for (auto& l : links_) {
+    if (!l) continue;
+    for (cudaStream_t s : l->streams) {
+      const cudaError_t q = cudaStreamQuery(s);
+      if (q == cudaErrorNotReady) return false;
+      if (q != cudaSuccess) RB_CUDA(q);
+    }
+  }
+  return true;
+}
+
+void Backend::links_release() {
+  for (auto& l : links_) {
+    if (!l) continue;
+    if (cudaStreamQuery(l->streams[0]) != cudaErrorNotReady && cudaStreamQuery(l->streams[1]) != cudaErrorNotReady) continue;
+    l->broken = true;
+    uint32_t big[kControlBytes / 4];
+    for (uint32_t& w : big) w = 0x7fffffffu;  // satisfies every pending >= wait on this end
+    cudaMemcpy(l->region.p, big, kControlBytes, cudaMemcpyHostToDevice);
+    for (cudaStream_t s : l->streams) cudaStreamSynchronize(s);
+  }
+  cudaGetLastError();
+}
+
+}  // namespace rb200

@@ -172,3 +172,95 @@ def test_one_process_drives_backends_on_two_devices():
             rows.append((first, step))
             be.close()
         assert np.array_equal(rows[0][0], rows[1][0]) and np.array_equal(rows[0][1], rows[1][1])
+
+
+def _link_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+    from relay_b200 import _lib
+    from relay_b200.backend import make_cuda_backend
+    from relay_b200.types import ForwardBatch, SeqChunk
+    from tests.test_gpu_model import WIDE_CONFIGS, synthetic
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.cuda.set_device(rank)
+        cfg = WIDE_CONFIGS["d128_g4"]
+        w = synthetic(cfg, 12)
+        be = make_cuda_backend(w, 64, 16, device=rank, max_batch_tokens=512)
+        # a ring of 3 slots of 4 blocks each: the 19-block layers travel as 5 messages, and the
+        # 2 layers x 5 messages wrap the ring, so slot reuse behind the receiver's acknowledgements runs
+        slot = 4 * 2 * be.kv_block_bytes()
+        link, handle = be.kv_link_create(3, slot)
+        handles = [None, None]
+        dist.all_gather_object(handles, handle)
+        be.kv_link_connect(link, handles[1 - rank])
+        rng = np.random.Generator(np.random.PCG64(21))
+        prompt = rng.integers(0, cfg.vocab, 300).tolist()
+        src_blocks = list(range(3, 3 + 19))
+        dst_blocks = list(range(40, 40 + 19))[::-1]
+        if rank == 0:
+            first = be.forward(ForwardBatch([SeqChunk(prompt, 0, src_blocks + [30])]),
+                               observer=lambda layer: be.kv_link_send_layer(link, layer, src_blocks))
+            be.kv_hop_sync(20000)
+            tok = int(np.argmax(first[0]))
+            dist.broadcast_object_list([tok], src=0)
+            table = src_blocks + [30]
+        else:
+            for layer in range(cfg.layers):
+                be.kv_link_recv_layer(link, layer, dst_blocks)
+            be.kv_hop_sync(20000)
+            box = [None]
+            dist.broadcast_object_list(box, src=0)
+            tok = box[0]
+            table = dst_blocks + [33]
+        toks, rows = [], []
+        for s in range(6):
+            row = be.forward(ForwardBatch([SeqChunk([tok], 300 + s, table)]))[0]
+            rows.append(row)
+            tok = int(np.argmax(row))
+            toks.append(tok)
+        pages = [be.read_kv_layer(l, table[:19]) for l in range(cfg.layers)]
+        # A receive nothing sends: the wait must run out on the host, the link is then refused,
+        # and the backend goes on working (no GPU wait is left spinning).
+        timed_out = refused = False
+        if rank == 1:
+            be.kv_link_recv_layer(link, 0, [60, 61])  # blocks no sequence uses
+            try:
+                be.kv_hop_sync(1500)
+            except _lib.B200Error as e:
+                timed_out = "timed out" in str(e)
+            try:
+                be.kv_link_recv_layer(link, 0, [60, 61])
+            except _lib.B200Error as e:
+                refused = "broken" in str(e)
+        after = be.forward(ForwardBatch([SeqChunk([toks[-1]], 306, table)]))[0]
+        dist.barrier()
+        q.put((rank, toks, np.stack(rows), [p.tobytes() for p in pages], timed_out, refused, bool(np.isfinite(after).all())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_kv_link_hop_equals_colocated_decode_and_its_waits_are_bounded():
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_link_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(2):
+        item = q.get(timeout=300)
+        got[item[0]] = item[1:]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert got[0][0] == got[1][0]                    # same greedy tokens
+    assert np.array_equal(got[0][1], got[1][1])      # same logits, bit for bit
+    assert got[0][2] == got[1][2]                    # the pages that crossed NVLink are byte-identical
+    assert got[1][3] and got[1][4]                   # the unmatched receive timed out; the link is then refused
+    assert got[0][5] and got[1][5]                   # both backends still compute
