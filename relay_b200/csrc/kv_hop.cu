@@ -13,6 +13,7 @@
 #include <nccl.h>
 
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <thread>
 
@@ -80,16 +81,19 @@ constexpr int kCallTimeoutMs = 60000;   // a send / receive call that has to con
 // when it runs out, so no call of this file can block for ever on a peer that never shows up.
 static void wait_ready(ncclComm_t comm, ncclResult_t r, int timeout_ms, const char* what) {
   const NcclApi& a = api();
-  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  const auto start = std::chrono::steady_clock::now();
+  const auto deadline = start + std::chrono::milliseconds(timeout_ms);
   while (r == ncclInProgress) {
     if (!a.CommGetAsyncError) return;  // a library too old to poll: it is blocking anyway
     if (a.CommGetAsyncError(comm, &r) != ncclSuccess) break;
     if (r != ncclInProgress) break;
-    if (std::chrono::steady_clock::now() > deadline) {
+    const auto now = std::chrono::steady_clock::now();
+    if (now > deadline) {
       a.CommAbort(comm);
       fail(RB200_ERR_RUNTIME, std::string(what) + ": timed out; communicator aborted");
     }
-    std::this_thread::sleep_for(std::chrono::microseconds(100));
+    // an enqueue completes within microseconds: spin for the first millisecond, then back off
+    if (now - start > std::chrono::milliseconds(1)) std::this_thread::sleep_for(std::chrono::microseconds(50));
   }
   if (r != ncclSuccess) {
     a.CommAbort(comm);
@@ -110,7 +114,13 @@ void Backend::nccl_init(const void* id, int nranks, int rank) {
   std::memcpy(&uid, id, sizeof(uid));
   auto st = std::make_unique<NcclState>();
   ncclComm_t comm = nullptr;
-  if (a.CommInitRankConfig && a.CommGetAsyncError) {
+  // RB200_NCCL_BLOCKING=1: a blocking communicator (each send / receive call then costs less host
+  // time, but set-up and the first connection to a peer wait without a deadline).
+  static const bool blocking = [] {
+    const char* e = std::getenv("RB200_NCCL_BLOCKING");
+    return e && e[0] == '1';
+  }();
+  if (!blocking && a.CommInitRankConfig && a.CommGetAsyncError) {
     ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
     cfg.blocking = 0;
     const ncclResult_t r = a.CommInitRankConfig(&comm, nranks, uid, rank, &cfg);

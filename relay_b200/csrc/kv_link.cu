@@ -41,7 +41,7 @@ namespace {
 constexpr uint32_t kLinkMagic = 0x4b4c3230u;  // "02LK"
 constexpr int kMaxSlots = 64;
 constexpr size_t kControlBytes = 512;         // arrived[64] @0, ack[64] @256; the ring starts behind
-constexpr int kMaxIds = 960;                  // block ids handed to a kernel by value (3.8 KB of parameters)
+constexpr int kMaxIds = 480;                  // block ids handed to a kernel by value (1.9 KB of parameters)
 
 struct LinkHandle {  // what crosses the host connection: RB200_KV_LINK_HANDLE_BYTES
   uint32_t magic;
@@ -201,12 +201,19 @@ void Backend::kv_link_send_layer(int link, int layer, const int32_t* blocks, int
   const int per_msg = static_cast<int>(std::min<size_t>(kMaxIds, l.slot_bytes / (2 * bb)));
   const long long vec = static_cast<long long>(bb / 16);
   const size_t off = static_cast<size_t>(layer) * layer_elems();
-  // The gather must see this layer's appends of the latest forward pass.
-  for (cudaStream_t s : l.streams) RB_CUDA(cudaStreamWaitEvent(s, layer_done_[layer], 0));
+  // The gather must see this layer's appends of the latest forward pass: the streams this call
+  // uses wait for the layer's event, unless it has completed already.
+  const bool layer_pending = cudaEventQuery(layer_done_[layer]) != cudaSuccess;
+  cudaGetLastError();
+  bool waited[2] = {false, false};
   for (int b0 = 0; b0 < n; b0 += per_msg) {
     const int m = std::min(per_msg, n - b0);
     const uint32_t k = l.sent++;
     cudaStream_t st = l.streams[k & 1];
+    if (layer_pending && !waited[k & 1]) {
+      RB_CUDA(cudaStreamWaitEvent(st, layer_done_[layer], 0));
+      waited[k & 1] = true;
+    }
     if (k >= static_cast<uint32_t>(l.n_slots)) stream_wait_geq(st, ack_of(l.region.p, l, k), k - l.n_slots + 1);
     IdList ids;
     ids.n = m;
@@ -215,6 +222,10 @@ void Backend::kv_link_send_layer(int link, int layer, const int32_t* blocks, int
     char* mine = slot_of(l.region.p, l, k);
     char* theirs = slot_of(l.peer, l, k);
     dim3 grid(m, 2, static_cast<unsigned>(std::max<long long>(1, std::min<long long>(8, vec / 256))));
+    // RB200_KV_LINK=sm: the gather stores straight into the peer's slot (measured about 10 % faster
+    // back to back, but its CTAs then hold SMs for the whole NVLink transfer); default: copy engine.
+    // Folding the signal into that kernel (last CTA done stores the counter) measured slower: every
+    // thread then pays a system-wide fence behind its peer stores.
     count_launch(2);
     link_gather_kernel<<<grid, 256, 0, st>>>(kc_.as<uint4>() + off / 8, vc_.as<uint4>() + off / 8, ids, vec,
                                              reinterpret_cast<uint4*>(sm_copy() ? theirs : mine));
@@ -274,9 +285,9 @@ void Backend::links_release() {
     if (!l) continue;
     if (cudaStreamQuery(l->streams[0]) != cudaErrorNotReady && cudaStreamQuery(l->streams[1]) != cudaErrorNotReady) continue;
     l->broken = true;
-    uint32_t big[kControlBytes / 4];
-    for (uint32_t& w : big) w = 0x7fffffffu;  // satisfies every pending >= wait on this end
-    cudaMemcpy(l->region.p, big, kControlBytes, cudaMemcpyHostToDevice);
+    uint32_t big[128];
+    for (uint32_t& w : big) w = 0x7fffffffu;  // satisfies every pending >= wait on this end (arrived and ack)
+    cudaMemcpy(l->region.p, big, sizeof(big), cudaMemcpyHostToDevice);
     for (cudaStream_t s : l->streams) cudaStreamSynchronize(s);
   }
   cudaGetLastError();
