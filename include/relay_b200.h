@@ -272,8 +272,25 @@ int rb200_kv_hop_sync(rb200_backend* b, int timeout_ms);
 int rb200_kv_link_create(rb200_backend* b, int n_slots, size_t slot_bytes, void* handle_out);
 /* Maps the other end's region; both ends must have been created with the same ring. */
 int rb200_kv_link_connect(rb200_backend* b, int link, const void* peer_handle);
+/* The same for two backends of one process (a process cannot open its own IPC handle): each end
+ * takes the other's region by address; backends on different devices get peer access first. */
+int rb200_kv_link_connect_local(rb200_backend* a, int link_a, rb200_backend* b, int link_b);
 int rb200_kv_link_send_layer(rb200_backend* b, int link, int layer, const int32_t* blocks, int n);
 int rb200_kv_link_recv_layer(rb200_backend* b, int link, int layer, const int32_t* blocks, int n);
+/* Sender: waits until every layer sent so far has been read out of the cache (its gather has
+ * run; the copy may still be under way), after which the sender's blocks may be rewritten. The
+ * reference frees a request's blocks once its last frame is written
+ * (engine/src/kv_transfer.cpp:139-160); its read_kv_layer is synchronous, this call restores
+ * that guarantee. At most timeout_ms (<= 0: 60 s); on the deadline the link is broken, -1. */
+int rb200_kv_link_wait_gathered(rb200_backend* b, int link, int timeout_ms);
+/* Receiver: consumes a layer of n blocks from the link without landing it anywhere, the
+ * counterpart of the transfer engine reading and dropping a Layer frame it has no room for
+ * (engine/src/kv_transfer.cpp:284-288). */
+int rb200_kv_link_skip_layer(rb200_backend* b, int link, int n);
+/* Waits until everything enqueued on this link has run (write_kv_layer's contract is that the
+ * pages are in the cache when it returns: engine/src/cuda_backend.cu:649-664), at most
+ * timeout_ms (<= 0: 60 s); on the deadline the link is released, marked broken, and -1 returned. */
+int rb200_kv_link_wait(rb200_backend* b, int link, int timeout_ms);
 /* After rb200_kv_hop_sync; unmaps the peer's region and frees this end's. */
 int rb200_kv_link_close(rb200_backend* b, int link);
 

@@ -83,6 +83,10 @@ SIGNATURES = {
     "rb200_kv_link_connect": (I, [P, I, P]),
     "rb200_kv_link_send_layer": (I, [P, I, I, P, I]),
     "rb200_kv_link_recv_layer": (I, [P, I, I, P, I]),
+    "rb200_kv_link_connect_local": (I, [P, I, P, I]),
+    "rb200_kv_link_skip_layer": (I, [P, I, I]),
+    "rb200_kv_link_wait": (I, [P, I, I]),
+    "rb200_kv_link_wait_gathered": (I, [P, I, I]),
     "rb200_kv_link_close": (I, [P, I]),
     "rb200_decode_scratch_bytes": (SZ, [C.POINTER(CAttnShape), I, I]),
     "rb200_decode_plan": (SZ, [C.POINTER(CAttnShape), I, I, P, P]),

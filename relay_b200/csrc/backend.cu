@@ -1101,6 +1101,38 @@ int rb200_kv_link_recv_layer(rb200_backend* b, int link, int layer, const int32_
   });
 }
 
+int rb200_kv_link_connect_local(rb200_backend* a, int link_a, rb200_backend* b, int link_b) {
+  return guarded([&] {
+    RB_REQUIRE(a != nullptr && b != nullptr, "kv_link_connect_local: null backend");
+    a->impl->kv_link_connect_local(link_a, *b->impl, link_b);
+    return 0;
+  });
+}
+
+int rb200_kv_link_skip_layer(rb200_backend* b, int link, int n) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "kv_link_skip_layer: null backend");
+    b->impl->kv_link_skip_layer(link, n);
+    return 0;
+  });
+}
+
+int rb200_kv_link_wait(rb200_backend* b, int link, int timeout_ms) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "kv_link_wait: null backend");
+    b->impl->kv_link_wait(link, timeout_ms);
+    return 0;
+  });
+}
+
+int rb200_kv_link_wait_gathered(rb200_backend* b, int link, int timeout_ms) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "kv_link_wait_gathered: null backend");
+    b->impl->kv_link_wait_gathered(link, timeout_ms);
+    return 0;
+  });
+}
+
 int rb200_kv_link_close(rb200_backend* b, int link) {
   return guarded([&] {
     RB_REQUIRE(b != nullptr, "kv_link_close: null backend");

@@ -66,7 +66,9 @@ struct KvLink {
   size_t slot_bytes = 0;
   DeviceBuf region;
   void* peer = nullptr;
+  bool peer_is_ipc = false;  // mapped with cudaIpcOpenMemHandle (another process) rather than taken by address
   cudaStream_t streams[2] = {nullptr, nullptr};  // consecutive messages alternate between them
+  cudaEvent_t gathered[2] = {nullptr, nullptr};  // behind the latest gather on each stream
   uint32_t sent = 0, received = 0;  // messages enqueued so far in each direction
   bool broken = false;
   ~KvLink();
@@ -153,6 +155,10 @@ class Backend {
   void kv_link_connect(int link, const void* peer_handle);
   void kv_link_send_layer(int link, int layer, const int32_t* blocks, int n);
   void kv_link_recv_layer(int link, int layer, const int32_t* blocks, int n);
+  void kv_link_connect_local(int link, Backend& other, int other_link);
+  void kv_link_skip_layer(int link, int n);
+  void kv_link_wait(int link, int timeout_ms);
+  void kv_link_wait_gathered(int link, int timeout_ms);
   void kv_link_close(int link);
 
  private:

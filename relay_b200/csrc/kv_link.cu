@@ -28,9 +28,11 @@
 // the host connection's ordered frames already guarantee.
 #include <cuda.h>
 
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <thread>
 
 #include "backend.h"
 
@@ -129,9 +131,11 @@ bool sm_copy() {  // RB200_KV_LINK=sm: the gather kernel stores straight into th
 }  // namespace
 
 KvLink::~KvLink() {
-  if (peer) cudaIpcCloseMemHandle(peer);
+  if (peer && peer_is_ipc) cudaIpcCloseMemHandle(peer);
   for (cudaStream_t s : streams)
     if (s) cudaStreamDestroy(s);
+  for (cudaEvent_t e : gathered)
+    if (e) cudaEventDestroy(e);
 }
 
 KvLink& Backend::link_of(int link) {
@@ -150,6 +154,7 @@ int Backend::kv_link_create(int n_slots, size_t slot_bytes, void* handle_out) {
   l->region = DeviceBuf(kControlBytes + static_cast<size_t>(n_slots) * slot_bytes);
   RB_CUDA(cudaMemset(l->region.p, 0, kControlBytes));
   for (cudaStream_t& s : l->streams) RB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  for (cudaEvent_t& e : l->gathered) RB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   LinkHandle h{};
   h.magic = kLinkMagic;
   h.n_slots = n_slots;
@@ -175,6 +180,34 @@ void Backend::kv_link_connect(int link, const void* peer_handle) {
   void* p = nullptr;
   RB_CUDA(cudaIpcOpenMemHandle(&p, h.mem, cudaIpcMemLazyEnablePeerAccess));
   l.peer = p;
+  l.peer_is_ipc = true;
+}
+
+// The two ends live in one process (an IPC handle cannot be opened by the process that made it):
+// each end takes the other's region by its address. Backends on different devices get peer
+// access to each other first.
+void Backend::kv_link_connect_local(int link, Backend& other, int other_link) {
+  RB_REQUIRE(&other != this, "kv_link_connect_local: a link joins two backends");
+  if (other.device_ != device_) {
+    for (int pass = 0; pass < 2; ++pass) {
+      RB_CUDA(cudaSetDevice(pass == 0 ? device_ : other.device_));
+      const cudaError_t e = cudaDeviceEnablePeerAccess(pass == 0 ? other.device_ : device_, 0);
+      if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) RB_CUDA(e);
+      cudaGetLastError();
+    }
+  }
+  set_device();
+  // lock the two backends in address order
+  Backend* first = this < &other ? this : &other;
+  Backend* second = this < &other ? &other : this;
+  std::lock_guard<std::mutex> la(first->copy_mu_);
+  std::lock_guard<std::mutex> lb(second->copy_mu_);
+  KvLink& a = link_of(link);
+  KvLink& b = other.link_of(other_link);
+  RB_REQUIRE(a.peer == nullptr && b.peer == nullptr, "kv_link_connect_local: already connected");
+  RB_REQUIRE(a.n_slots == b.n_slots && a.slot_bytes == b.slot_bytes, "kv_link_connect_local: the two ends were created with different rings");
+  a.peer = b.region.p;
+  b.peer = a.region.p;
 }
 
 void Backend::kv_link_close(int link) {
@@ -229,6 +262,7 @@ void Backend::kv_link_send_layer(int link, int layer, const int32_t* blocks, int
     count_launch(2);
     link_gather_kernel<<<grid, 256, 0, st>>>(kc_.as<uint4>() + off / 8, vc_.as<uint4>() + off / 8, ids, vec,
                                              reinterpret_cast<uint4*>(sm_copy() ? theirs : mine));
+    RB_CUDA(cudaEventRecord(l.gathered[k & 1], st));  // from here on the message no longer reads the pages
     if (!sm_copy()) RB_CUDA(cudaMemcpyAsync(theirs, mine, bytes, cudaMemcpyDefault, st));  // peer copy, by address
     link_signal_kernel<<<1, 1, 0, st>>>(arrived_of(l.peer, l, k), k + 1);
     RB_CUDA(cudaGetLastError());
@@ -262,6 +296,82 @@ void Backend::kv_link_recv_layer(int link, int layer, const int32_t* blocks, int
                                               reinterpret_cast<const uint4*>(slot_of(l.region.p, l, k)));
     link_signal_kernel<<<1, 1, 0, st>>>(ack_of(l.peer, l, k), k + 1);
     RB_CUDA(cudaGetLastError());
+  }
+}
+
+// Consumes the messages of a layer of n blocks the peer has sent (or will send) without landing
+// them anywhere: the receiver had no room for the request and drops the frame
+// (engine/src/kv_transfer.cpp:284-288), but the ring must move on.
+void Backend::kv_link_skip_layer(int link, int n) {
+  set_device();
+  RB_REQUIRE(n >= 0, "kv_link_skip_layer: negative block count");
+  if (n == 0) return;
+  std::lock_guard<std::mutex> lock(copy_mu_);
+  KvLink& l = link_of(link);
+  RB_REQUIRE(l.peer != nullptr, "kv_link_skip_layer: the link is not connected");
+  if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
+  const int per_msg = static_cast<int>(std::min<size_t>(kMaxIds, l.slot_bytes / (2 * kv_block_bytes())));
+  for (int b0 = 0; b0 < n; b0 += per_msg) {
+    const uint32_t k = l.received++;
+    cudaStream_t st = l.streams[k & 1];
+    stream_wait_geq(st, arrived_of(l.region.p, l, k), k + 1);
+    count_launch();
+    link_signal_kernel<<<1, 1, 0, st>>>(ack_of(l.peer, l, k), k + 1);
+    RB_CUDA(cudaGetLastError());
+  }
+}
+
+// Waits until everything enqueued on one link has run, at most timeout_ms; on the deadline the
+// link's waits are released, it is marked broken and the call fails.
+void Backend::kv_link_wait(int link, int timeout_ms) {
+  set_device();
+  if (timeout_ms <= 0) timeout_ms = 60000;
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  for (;;) {
+    {
+      std::lock_guard<std::mutex> lock(copy_mu_);
+      KvLink& l = link_of(link);
+      const cudaError_t a = cudaStreamQuery(l.streams[0]), b = cudaStreamQuery(l.streams[1]);
+      if (a != cudaErrorNotReady && a != cudaSuccess) RB_CUDA(a);
+      if (b != cudaErrorNotReady && b != cudaSuccess) RB_CUDA(b);
+      if (a == cudaSuccess && b == cudaSuccess) {
+        if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
+        return;
+      }
+      if (std::chrono::steady_clock::now() > deadline) {
+        links_release();
+        fail(RB200_ERR_RUNTIME, "kv_link_wait: timed out; the link is broken");
+      }
+    }
+    std::this_thread::yield();
+  }
+}
+
+// Waits until every message sent so far has read its pages out of the cache (its gather has run;
+// the bytes may still be on their way): from then on the sender's blocks may be reused. relay frees
+// a request's blocks once its last frame is written (engine/src/kv_transfer.cpp:139-160), which
+// read_kv_layer's synchronous copy made safe; a sender over a link calls this instead.
+void Backend::kv_link_wait_gathered(int link, int timeout_ms) {
+  set_device();
+  if (timeout_ms <= 0) timeout_ms = 60000;
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  for (;;) {
+    {
+      std::lock_guard<std::mutex> lock(copy_mu_);
+      KvLink& l = link_of(link);
+      const cudaError_t a = cudaEventQuery(l.gathered[0]), b = cudaEventQuery(l.gathered[1]);
+      if (a != cudaErrorNotReady && a != cudaSuccess) RB_CUDA(a);
+      if (b != cudaErrorNotReady && b != cudaSuccess) RB_CUDA(b);
+      if (a == cudaSuccess && b == cudaSuccess) {
+        if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
+        return;
+      }
+      if (std::chrono::steady_clock::now() > deadline) {
+        links_release();
+        fail(RB200_ERR_RUNTIME, "kv_link_wait_gathered: timed out (the receiver does not free ring slots); the link is broken");
+      }
+    }
+    std::this_thread::yield();
   }
 }
 

@@ -37,3 +37,23 @@ def test_reference_program_passes_on_the_b200_backend(prog):
     tail = (r.stdout + r.stderr)[-3000:]
     assert r.returncode == 0, tail
     assert "0 failed" in tail, tail
+
+
+@pytest.mark.parametrize("devices", ["0,0", "0,1"])
+def test_relays_transfer_engine_over_a_kv_link(devices):
+    """tests/cpp/test_kv_link_transfer.cpp: relay's KVSender / KVReceiver / PrefillWorker / Engine,
+    unmodified, with the Layer payloads on a K/V link (include/relay_b200_transfer.h): tokens equal
+    one engine's, dropped frames, host-injected connection cuts. "0,0": both backends on one GPU;
+    "0,1": prefill on GPU 0, decode on GPU 1 (skipped on a one-GPU box)."""
+    exe = os.path.join(BIN, "test_kv_link_transfer")
+    if not os.path.exists(exe):
+        pytest.skip("not built here (needs the reference checkout: make -C oracle reftests)")
+    if devices == "0,1":
+        import torch
+        if torch.cuda.device_count() < 2:
+            pytest.skip("needs two GPUs")
+    env = dict(os.environ, RB200_LINK_DEVICES=devices)
+    r = subprocess.run([exe], cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    tail = (r.stdout + r.stderr)[-3000:]
+    assert r.returncode == 0, tail
+    assert "\n0 failed" in tail, tail
