@@ -437,6 +437,15 @@ def op_suite(peak_gbs: float, peak_tflops: float, only=None, int8_case=None, cpu
         from oracle import oracle
         oracle.set_threads()  # all the cores this process may use, whatever OMP_NUM_THREADS says
     want = lambda name: only is None or name in only  # --ops: a subset, for profiler captures of one kernel
+    if want("int8") or want("prefill") or want("floor"):
+        # What one launch costs when it does next to nothing: a 256-element conversion kernel in the
+        # same harness (a CUDA graph of back-to-back programmatic dependent launches, each waiting
+        # for the one ahead before it touches memory). No kernel of the path that depends on its
+        # predecessor can take less; the small int8 shapes and the first prefill chunk sit close to it.
+        tiny_in = torch.zeros(256, device=dev)
+        tiny_out = torch.zeros(256, device=dev, dtype=torch.float16)
+        out["dependent_launch_floor"] = {"us": time_in_graph(lambda i: ops.f32_to_f16(tiny_in, tiny_out), 1) * 1e3,
+                                         "what": "a 256-element kernel, same graph of dependent launches as the operators below"}
     if want("decode"):
         out.update(_op_decode(ops, torch, np, c2_contexts, peak_gbs, cpu))
     if want("int8"):

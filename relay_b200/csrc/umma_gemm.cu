@@ -68,7 +68,8 @@ __device__ __forceinline__ void cvt_s8x4(uint32_t w, uint32_t& lo, uint32_t& hi)
 // MT = 128-row M tiles per CTA (1 or 2). Two tiles share every activation tile a CTA loads and let
 // a grid of up to 256-row tiles fit the SMs in one wave where 128-row tiles need two (the
 // gate/up projection at 256 tokens: 144 CTAs of 200 rows, tensor pipe active 76 %).
-// fp16 weights, no K split (the partial tile would not fit shared memory).
+// fp16 weights only. With a K split the two partial tiles are exchanged one after the other (one
+// alone fills the shared memory of the idle operand stages).
 template <int BN, bool INT8, int MT = 1>
 struct UmmaSmem {
   // Elements of K per block. int8 weights with up to 128 tokens take 128 (two swizzle atoms of
@@ -270,9 +271,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     tc_fence_after();
     const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
     const int row = quarter * 32 + lane;
-    const int n = m0 + row;
-    const bool live = row < rows && n < N;
-    const float sc = (INT8 && live) ? scale[n] : 1.0f;
     if (warp >= 6) {
       // nothing: only widening warps
     } else if (splits == 1) {
@@ -306,34 +304,37 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           }
         }
       }
-    } else {
+    }
+  }
+#pragma unroll 1
+  for (int a = 0; a < (splits > 1 ? MT : 0); ++a) {  // the CTA's M tiles, one exchange each
+    if (warp >= 2 && warp < 6) {
       // Park this CTA's partial tile as red[token][row] in the (now idle) operand stages.
+      const int quarter = warp & 3, row = quarter * 32 + lane;
       float* red = reinterpret_cast<float*>(gen_base);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t v[32];
-        tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN + c0, v);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) red[(c0 + j) * kTileM + row] = __uint_as_float(v[j]);
       }
     }
-  }
-  if (splits > 1) {
     cluster_sync_all();  // every member's partial tile is in its shared memory
     if (warp >= 2 && warp < 6) {
       // This CTA finishes `per` token columns of the tile: a thread takes four consecutive weight
       // rows of one column (16-byte DSMEM loads; the rows are contiguous in red[token][row]), the
       // four warps take the columns round-robin, the members are added in rank order.
       const int tid = threadIdx.x - 64, r4 = (tid & 31) * 4, cg = tid >> 5;
-      const int n4 = m0 + r4;
+      const int n4 = m0 + a * kTileM + r4;
       const int per = (BN + splits - 1) / splits;
       const int c_begin = split * per, c_end = min(min(BN, c_begin + per), T - tok0);
       bool live[4];
       float sc[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        live[k] = r4 + k < rows && n4 + k < N;
+        live[k] = a * kTileM + r4 + k < rows && n4 + k < N;
         sc[k] = (INT8 && live[k]) ? scale[n4 + k] : 1.0f;
       }
       const bool vec = (N & 3) == 0 && live[3];  // the four outputs form one aligned float4 of y
@@ -397,7 +398,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
       }
     }
-    cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
+    cluster_sync_all();  // nobody leaves (or parks its next tile) while a peer may still read its shared memory
   }
   tc_fence_before();
   __syncthreads();
@@ -544,7 +545,9 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
     }
   }
   const bool can_split = static_cast<size_t>(BN) * kTileM * 4 <= static_cast<size_t>(S::kStages) * S::kStageBytes;
-  constexpr bool kTwoTiles = !INT8 && BN >= 128;  // two M tiles per CTA: fp16, wide token tiles, no K split
+  using S2 = UmmaSmem<BN, INT8, INT8 ? 1 : 2>;
+  const bool can_split2 = static_cast<size_t>(BN) * kTileM * 4 <= static_cast<size_t>(S2::kStages) * S2::kStageBytes;
+  constexpr bool kTwoTiles = !INT8 && BN >= 128;  // two M tiles per CTA: fp16, wide token tiles
   static const bool two_off = [] {
     const char* e = std::getenv("RB200_GEMM_MT");
     return e && std::atoi(e) == 1;
@@ -556,6 +559,12 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
   // same however few of its rows count (176-row tiles measured slower than 128-row ones).
   for (int m = 1; m <= ((kTwoTiles && !two_off) ? 2 : 1); ++m) {
     for (int r = kTileM * m; r >= (m == 1 ? 64 : 200); r -= 8) {
+      // Two M tiles are planned without a K split only: with one (the kernel can do it, and the
+      // forced-split tests run it) the projections with few row tiles measured slower at 256
+      // tokens (QKV 31 us, attention output 28 us, down 48 us against 22.5, 17.7 and 36 us with
+      // 128-row tiles in clusters of four): their time is pipeline fill and the partial-tile
+      // exchange, which two exchanges and shorter k ranges make worse, not the L2 traffic of the
+      // shared activation tile.
       for (int sp = 1; sp <= (m == 1 ? 8 : 1); ++sp) {
         if (sp > 1 && (!can_split || nk / sp < 4)) break;
         const long long clusters = static_cast<long long>(div_up(W.N, r)) * ttiles;
@@ -577,8 +586,10 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
   }();
   if (forced > 0 && can_split) {
     splits = std::min({forced, 8, std::max(1, nk)});
-    if (mt == 2) rows = kTileM;
-    mt = 1;
+    if (mt == 2 && !can_split2) {
+      rows = kTileM;
+      mt = 1;
+    }
   }
   static const bool debug = std::getenv("RB200_GEMM_DEBUG") != nullptr;
   if (debug)
@@ -587,7 +598,7 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
                  W.N, W.K, T, INT8 ? 1 : 0, BN, rows, mt, splits, div_up(W.N, rows), ttiles, splits, capacity[1], capacity[2],
                  capacity[3], capacity[4], capacity[5], capacity[6], capacity[7], capacity[8]);
   if constexpr (kTwoTiles) {
-    if (mt == 2) return launch_umma_cfg<BN, INT8, 2>(W, x, ldx, y, T, beta, st, rows, 1);
+    if (mt == 2) return launch_umma_cfg<BN, INT8, 2>(W, x, ldx, y, T, beta, st, rows, splits);
   }
   launch_umma_cfg<BN, INT8, 1>(W, x, ldx, y, T, beta, st, rows, splits);
 }

@@ -364,8 +364,8 @@ def test_gemv_matches_oracle(ops, K, N, int8):
 @pytest.mark.parametrize("int8", [True, False])
 def test_gemm_matches_oracle(ops, K, N, int8):
     for T, beta in [(9, 0.0), (64, 1.0), (100, 0.0), (256, 1.0)]:
-        if K * N * T > 4096 * 4096 * 64 and T > 64:
-            continue  # keep the CPU oracle in seconds
+        if int8 and K * N * T > 4096 * 4096 * 64 and T > 64:
+            continue  # keep the CPU restatement of the int8 product in seconds (fp16 is checked by a float64 matmul)
         x, y0, w, scale = linear_case(K + N + T, T, K, N, int8)
         want = linear_oracle(x, y0, w, scale, beta)
         y = dev(y0)
