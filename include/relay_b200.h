@@ -152,10 +152,9 @@ typedef struct rb200_sampling_params {
  * sample() / sample_with_log_prob() pick from that row (engine/src/sampler.cpp:33-72, called
  * per row by engine/src/engine.cpp:270-282) and, when logprob_out is not NULL, the
  * log-probability Engine reports with it (float64; relay narrows it to float). `sampling` is a
- * host array, one entry per logits row. Covered on the device: greedy rows (lowest id on ties)
- * and temperature sampling without truncation (inverse CDF in id order). A row with top_k in
- * (0, vocab) or top_p < 1 is refused with an invalid-argument error: such rows need the
- * vocabulary in sorted order and stay on the host path (rb200_forward + relay's sampler). */
+ * host array, one entry per logits row. All of relay's sampler runs on the device: greedy rows
+ * (lowest id on ties), temperature sampling without truncation (inverse CDF in id order), and
+ * top-k / nucleus truncation (candidates by decreasing logit, ties by id; sampler.cpp:77-104). */
 int rb200_forward_sample(rb200_backend* b, int n_seqs, const int32_t* tokens, const int32_t* chunk_len,
                          const int32_t* start_pos, const int32_t* table_len, const int32_t* tables,
                          const uint8_t* want_logits, int all_logits, rb200_layer_cb cb, void* cb_ctx,
@@ -423,9 +422,8 @@ int rb200_kv_scatter(void* k_pool, void* v_pool, const int32_t* blocks, int n, s
                      const void* staging, void* stream);
 /* Greedy token of each row of logits [R][V] (lowest id wins ties, engine/src/sampler.cpp:17-22). */
 int rb200_argmax_rows(const float* logits, int R, int V, int32_t* token_out, float* logit_out, void* stream);
-/* The device sampler on rows of logits [R][V] (engine/src/sampler.cpp:33-72): `params` is a
- * DEVICE array of R entries, each greedy or untruncated (see rb200_forward_sample; the caller
- * checks, the kernel does not); logprob_out may be NULL. */
+/* The device sampler on rows of logits [R][V] (engine/src/sampler.cpp:33-105): `params` is a
+ * DEVICE array of R entries (see rb200_forward_sample); logprob_out (float64 [R]) may be NULL. */
 int rb200_sample_rows(const float* logits, int R, int V, const rb200_sampling_params* params, int32_t* token_out,
                       double* logprob_out, void* stream);
 

@@ -151,7 +151,7 @@ class Backend:
     def forward_sample(self, batch: ForwardBatch, sampling, logprobs: bool = False, observer=None):
         """The token relay's sampler picks from each logits row, sampled on the device, and (with
         `logprobs`) its log-probability. `sampling`: one (temperature, top_p, top_k, seed, index)
-        per row; rows asking for top-k / top-p truncation raise ValueError (host path)."""
+        per row."""
         fb = flatten(batch)
         rows = fb.n_rows
         arr = self._sampling_array(sampling, rows)

@@ -318,10 +318,11 @@ Backend::PickSpec Backend::pick_of(const Outputs& out, int R) const {
   pick.kind = out.sampling ? Pick::Sample : Pick::Greedy;
   pick.logprobs = out.logprobs != nullptr;
   if (out.sampling)
-    for (int r = 0; r < R; ++r)
-      if (!sampling_on_device(out.sampling[r], c_.vocab))
-        fail(RB200_ERR_INVALID_ARGUMENT,
-             "sampling: top-k / top-p truncation is not done on the device; take the logits (rb200_forward) for such rows");
+    for (int r = 0; r < R; ++r) {
+      const rb200_sampling_params& sp = out.sampling[r];
+      if (sp.temperature > 0.0f && !(sp.top_p > 0.0f)) fail(RB200_ERR_INVALID_ARGUMENT, "sampling: top_p must be positive");
+      pick.truncated = pick.truncated || sampling_truncated(sp, c_.vocab);
+    }
   // greedy with log-probabilities runs the sampling kernel with temperature 0 rows
   if (pick.kind == Pick::Greedy && pick.logprobs) pick.kind = Pick::Sample;
   return pick;
@@ -542,7 +543,7 @@ void Backend::enqueue(const int* dm, const Plan& p, rb200_layer_cb cb, void* cb_
       launch_argmax_rows(logits_.as<float>(), R, c_.vocab, argmax_tok_.as<int>(), argmax_val_.as<float>(), stream_);
     else if (pick.kind == Pick::Sample)
       launch_sample_rows(logits_.as<float>(), R, c_.vocab, reinterpret_cast<const rb200_sampling_params*>(dm + p.sampling_off),
-                         argmax_tok_.as<int>(), pick.logprobs ? logprob_.as<double>() : nullptr, stream_);
+                         argmax_tok_.as<int>(), pick.logprobs ? logprob_.as<double>() : nullptr, stream_, pick.truncated);
   }
   if (prof) mark(*prof, kMarkEnd);
   RB_CUDA(cudaGetLastError());

@@ -186,6 +186,7 @@ class Backend {
   struct PickSpec {
     Pick kind = Pick::None;
     bool logprobs = false;
+    bool truncated = false;  // some row asks for top-k / nucleus truncation
   };
   // Event marks of one pass while profiling is on.
   struct Prof {

@@ -51,11 +51,13 @@ void launch_kv_scatter(void* k, void* v, const int* blocks, int n, size_t block_
 void launch_argmax_rows(const float* logits, int R, int V, int* token_out, float* logit_out, cudaStream_t st);
 
 // ---- sampler.cu ----
-// True when the device sampler covers these parameters (greedy, or temperature sampling without
-// top-k / top-p truncation); `params` of launch_sample_rows is a device array, one per row.
-bool sampling_on_device(const rb200_sampling_params& p, int V);
+// True when these parameters ask for top-k or nucleus truncation (temperature > 0 and top_k in
+// (0, V) or top_p < 1). `params` of launch_sample_rows is a device array, one per row;
+// `any_truncated`: some row may be truncated, so the second kernel (which takes those rows) is
+// launched behind the first.
+bool sampling_truncated(const rb200_sampling_params& p, int V);
 void launch_sample_rows(const float* logits, int R, int V, const rb200_sampling_params* params, int* token_out,
-                        double* logprob_out, cudaStream_t st);
+                        double* logprob_out, cudaStream_t st, bool any_truncated);
 
 // ---- attention.cu ----
 // True when the tensor-core decode / prefill kernels cover this head layout; otherwise the

@@ -210,7 +210,7 @@ int Backend::decode_step(const int32_t* tokens, int n_new, const int32_t* new_se
 
   const DecodePlan dp = plan_decode(shape, S, max_ctx);
   const uint64_t key = (static_cast<uint64_t>(dp.parts) << 40) ^ (static_cast<uint64_t>(dp.slice) << 8) ^
-                       (static_cast<uint64_t>(pick.kind) << 2) ^ (pick.logprobs ? 1u : 0u);
+                       (static_cast<uint64_t>(pick.kind) << 2) ^ (pick.truncated ? 2u : 0u) ^ (pick.logprobs ? 1u : 0u);
   bool as_graph = false;
   if (graphs_enabled()) {
     auto it = s.graphs.find(key);

@@ -71,6 +71,33 @@ def test_sample_rows_picks_what_relays_sampler_picks(gpu, V, R, spread):
     assert np.array_equal(tok, tok2)
 
 
+TRUNCATED_CASES = [
+    # (V, spread of the logits, [(temperature, top_p, top_k)])
+    (128256, 3.0, [(0.8, 1.0, 50), (1.0, 0.9, 0), (0.7, 0.95, 1000), (1.3, 1.0, 1), (1.0, 0.5, 40), (1.0, 1.0, 5000),
+                   (2.0, 0.999, 0), (1.0, 0.3, 2048), (0.9, 0.99, 2049)]),
+    (128256, 0.02, [(1.0, 0.2, 0), (1.0, 1.0, 7000), (1.0, 0.05, 9000)]),  # nearly flat: nuclei of many thousand tokens
+    (3000, 2.0, [(0.8, 0.9, 0), (1.0, 1.0, 10), (1.5, 0.7, 2999), (1.0, 0.999999, 0)]),
+    (37, 1.0, [(1.0, 0.5, 3), (0.7, 0.9, 36), (1.0, 0.1, 0)]),
+]
+
+
+@pytest.mark.parametrize("V,spread,settings", TRUNCATED_CASES)
+def test_truncated_sampling_picks_what_relays_sampler_picks(gpu, V, spread, settings):
+    _lib, ops, _ = gpu
+    rng = np.random.Generator(np.random.PCG64(V + len(settings)))
+    R = 2 * len(settings)
+    logits = (rng.standard_normal((R, V)) * spread).astype(np.float32)
+    # equal logits at the top and in the body: candidates are then ordered by id
+    logits[0, [V // 3, 2, V - 1]] = logits[0].max()
+    logits[1] = np.round(logits[1] * 2) / 2
+    rows = [settings[r % len(settings)] + (int(rng.integers(0, 2 ** 62)), int(rng.integers(0, 4096))) for r in range(R)]
+    tok, lp = run_sampler(_lib, ops, logits, rows)
+    for r in range(R):
+        want_tok, want_lp = oracle.sample(logits[r], *rows[r])
+        assert tok[r] == want_tok, (r, rows[r])
+        assert abs(lp[r] - want_lp) <= LOGPROB_TOL * max(1.0, abs(want_lp)), (r, rows[r])
+
+
 def test_sampled_tokens_follow_the_distribution_and_depend_only_on_seed_and_index(gpu):
     _lib, ops, _ = gpu
     V = 50
@@ -106,10 +133,13 @@ def test_forward_sample_equals_host_sampling_of_the_forward_logits(gpu):
     # greedy rows agree with the greedy entry point
     g_tok, _ = be.forward_greedy(batch)
     assert np.array_equal(be.forward_sample(batch, [(0.0, 1.0, 0, 0, 0)] * len(prompt)), g_tok)
-    # truncation stays on the host path
-    for bad in ((1.0, 0.9, 0, 1, 0), (1.0, 1.0, 40, 1, 0)):
-        with pytest.raises(ValueError, match="truncation"):
-            be.forward_sample(batch, [bad] * len(prompt))
+    # rows with top-k / nucleus truncation mixed among the others
+    mixed = [(0.9, [1.0, 0.9, 0.5][i % 3], [0, 5, 40, 300][i % 4], 7 + i, i) for i in range(len(prompt))]
+    tok, lp = be.forward_sample(batch, mixed, logprobs=True)
+    for i, row in enumerate(mixed):
+        want_tok, want_lp = oracle.sample(logits[i], *row)
+        assert tok[i] == want_tok, (i, row)
+        assert abs(lp[i] - want_lp) <= LOGPROB_TOL * max(1.0, abs(want_lp))
 
 
 # ---- decode sessions ---------------------------------------------------------------------------
