@@ -214,7 +214,7 @@ Backend::Backend(const rb200_model_config& cfg, const rb200_weights* w, int num_
   Hp_ = round_up(H, kPad);
   Qp_ = round_up(Q, kPad);
   Ip_ = round_up(I, kPad);
-  const AttnShape shape{c_.heads, c_.kv_heads, D, block_size_, QKV, Qp_};
+  const AttnShape shape{c_.heads, c_.kv_heads, D, block_size_, QKV, Qp_, pool_rows()};
   fast_attention_ = !(flags_ & RB200_REFERENCE_ATTENTION) && fast_attention_supported(shape);
 
   const bool q8 = flags_ & RB200_INT8_WEIGHTS;
@@ -433,7 +433,7 @@ int Backend::forward(int n_seqs, const int32_t* tokens, const int32_t* chunk_len
 
   RB_CUDA(cudaMemcpyAsync(meta_dev_.p, hm, total_ints * 4, cudaMemcpyHostToDevice, stream_));
   plan_ = Plan{T, R, n_decode, n_tiles, max_ctx, T4, S4, pick.kind == Pick::Sample ? sampling_off : 0};
-  const AttnShape shape{c_.heads, c_.kv_heads, D, bs, QKV, Qp_};
+  const AttnShape shape{c_.heads, c_.kv_heads, D, bs, QKV, Qp_, pool_rows()};
   if (fast_attention_ && n_decode > 0) decode_scratch_.ensure(decode_scratch_bytes(shape, n_decode, max_ctx));
   ensure_row_buffers(R, pick);
   (void)H; (void)I; (void)KV;
@@ -485,7 +485,7 @@ void Backend::enqueue(const int* dm, const Plan& p, rb200_layer_cb cb, void* cb_
   const int* d_toff = dm + 7 * T4;
   const int* d_tables = d_toff + p.S4;
   const TokenMeta meta{d_pos, d_seq, d_toff, d_tables};
-  const AttnShape shape{c_.heads, c_.kv_heads, D, bs, QKV, Qp_};
+  const AttnShape shape{c_.heads, c_.kv_heads, D, bs, QKV, Qp_, pool_rows()};
   const float eps = static_cast<float>(c_.rms_eps);
   float* x = x_.as<float>();
   __half* xn = xn_.as<__half>();

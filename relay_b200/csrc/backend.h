@@ -105,6 +105,7 @@ class Backend {
   int num_blocks() const { return num_blocks_; }
   int block_size() const { return block_size_; }
   size_t kv_block_bytes() const { return static_cast<size_t>(c_.kv_heads) * block_size_ * c_.head_dim * 2; }
+  long long pool_rows() const { return static_cast<long long>(num_blocks_) * c_.kv_heads * block_size_; }
   long long layer_elems() const { return static_cast<long long>(c_.kv_heads) * block_size_ * c_.head_dim * num_blocks_; }
 
   // What a pass hands back to the host, per logits row: the float32 logits, or the token the

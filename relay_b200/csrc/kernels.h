@@ -22,6 +22,11 @@ struct AttnShape {
   int heads, kv_heads, D, block_size;
   int q_stride;  // floats between tokens' q rows
   int o_stride;  // halves between tokens' output rows
+  // Rows ([block][kv head][slot]) of one layer's pool, when the caller knows them (the backend
+  // does; the operator entry points do not): the TMA descriptors of the tcgen05 prefill kernel
+  // then end where the pool ends, so a page the block table should not name reads as zeros
+  // instead of memory behind the pool. 0: unknown.
+  long long pool_rows = 0;
 };
 
 constexpr int kDecodeSlice = RB200_DECODE_SLICE;  // keys per split-context CTA

@@ -182,7 +182,7 @@ int Backend::decode_step(const int32_t* tokens, int n_new, const int32_t* new_se
   }
 
   const int D = c_.head_dim, QKV = (c_.heads + 2 * c_.kv_heads) * D;
-  const AttnShape shape{c_.heads, c_.kv_heads, D, bs, QKV, Qp_};
+  const AttnShape shape{c_.heads, c_.kv_heads, D, bs, QKV, Qp_, pool_rows()};
   decode_scratch_.ensure(decode_scratch_bytes(shape, S, max_ctx));
   ensure_row_buffers(S, PickSpec{pick.kind == Pick::None ? Pick::Greedy : pick.kind, pick.logprobs});  // picked tokens always have a home
   const uintptr_t sig = reinterpret_cast<uintptr_t>(decode_scratch_.p) ^ (reinterpret_cast<uintptr_t>(logits_.p) << 1) ^

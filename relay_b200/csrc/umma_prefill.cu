@@ -440,9 +440,10 @@ void launch_umma_prefill_d(const AttnShape& s, const float* q, const TokenMeta& 
   auto kernel = umma_prefill_kernel<D>;
   if (once.first())
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
-  // The layer's pool as rows of D halves, box = one 16-key page x 64 dims; the row count only
-  // bounds coordinates (the kernel never asks for a row the block table does not name).
-  const long long rows = 1LL << 31;
+  // The layer's pool as rows of D halves, box = one 16-key page x 64 dims. With the pool's real
+  // row count a page outside it reads as zeros; callers that do not know it get a bound that only
+  // limits the coordinates (the kernel never asks for a row the block table does not name).
+  const long long rows = s.pool_rows > 0 ? s.pool_rows : (1LL << 31);
   const CUtensorMap mk = make_map(kc, 2, rows, D, D, 16, 64, true);
   const CUtensorMap mv = make_map(vc, 2, rows, D, D, 16, 64, true);
   const float scale_log2e = kLog2e / sqrtf(static_cast<float>(D));
