@@ -502,7 +502,9 @@ def _op_decode(ops, torch, np, c2_contexts, peak_gbs, cpu=False):
 def _op_int8(ops, torch, peak_gbs, case=None, cpu=False):
     """case = (K, N, T) restricts the sweep to one point."""
     lin, dev = {}, "cuda"
-    for (K, N) in ((4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)):
+    # the four projection shapes of the workload definition, and 4096 -> 6144: what the model really
+    # runs for Q, K and V (one fused matrix)
+    for (K, N) in ((4096, 4096), (4096, 1024), (4096, 6144), (4096, 14336), (14336, 4096)):
         if case and (K, N) != tuple(case[:2]):
             continue
         R = max(2, int(300e6 // (N * K)) + 1)

@@ -287,6 +287,113 @@ gemv_kernel(const void* __restrict__ wv, const float* __restrict__ scale, const 
   gemv_finish<INT8>(acc, rb, split, splits, warp, g, t4, T, N, scale, y, beta, counters, partials, &s_last);
 }
 
+// ---- GEMV for small int8 matrices (T <= 8) ---------------------------------------------------
+//
+// A matrix of a few megabytes is read in about a microsecond; what a kernel for it has to avoid
+// is everything else: a K split across CTAs (partials through global memory, a counter, a last
+// CTA), staging the activations through shared memory behind block barriers, set-up of tensor
+// memory and descriptors. Here a CTA owns 16 output rows for the whole of K: its eight warps
+// take an eighth of K each, load their weight bytes (32 bytes per lane and row, four blocks in
+// flight) BEFORE waiting for the kernel ahead (weights are never written by a forward pass), read
+// the activation fragments straight from global memory (a few KB per warp, L1 / L2 resident),
+// multiply on m16n8k16 with the tokens on N as gemv_kernel does, and add the partial
+// accumulators in warp order through 4 KB of shared memory: one block barrier, no atomics,
+// the same sum on every run. WPG = warps that share a group of 16 rows (8, 4 or 2: a CTA then
+// owns 16, 32 or 64 rows, and a warp an eighth, a quarter or half of K); the host picks the
+// largest WPG whose grid still fits the SMs in one wave of two CTAs each, so that no second
+// wave trails behind.
+constexpr int kRowsWarps = 8;
+
+template <int WPG>
+__global__ void __launch_bounds__(kRowsWarps * 32)
+gemv_rows_i8_kernel(const int8_t* __restrict__ w, const float* __restrict__ scale, const __half* __restrict__ x,
+                    float* __restrict__ y, int T, int K, int N, int ldw, int ldx, float beta) {
+  pdl_trigger();
+  __shared__ float red[kRowsWarps][32][4];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  constexpr int U = 4;          // 32-byte loads in flight per lane and row
+  constexpr int kGroups = kRowsWarps / WPG;
+  const int group = warp / WPG, part = warp % WPG;
+  const int kw = K / WPG;  // this warp's k range: a multiple of 128
+  const int k0 = part * kw, nblk = kw / 128;
+  const int n_a = (blockIdx.x * kGroups + group) * 16 + g, n_b = n_a + 8;
+  const unsigned char* wa = reinterpret_cast<const unsigned char*>(w) + static_cast<size_t>(min(n_a, N - 1)) * ldw + k0 + 32 * t4;
+  const unsigned char* wb = reinterpret_cast<const unsigned char*>(w) + static_cast<size_t>(min(n_b, N - 1)) * ldw + k0 + 32 * t4;
+  uint32_t ra[U][8], rbv[U][8];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    if (u < nblk) {
+      ld_global_256(ra[u], wa + u * 128, true);
+      ld_global_256(rbv[u], wb + u * 128, true);
+    }
+  }
+  pdl_wait();  // x and y belong to the kernels ahead until they complete
+  // token g's 32 activations of a block, at the same k as this lane's 32 weight bytes
+  const __half* xg = x + static_cast<long long>(min(g, T - 1)) * ldx + k0 + 32 * t4;
+  const bool tok_live = g < T;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int b0 = 0; b0 < nblk; b0 += U) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int b = b0 + u;
+      if (b < nblk) {
+        uint32_t wra[8], wrb[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          wra[i] = ra[u][i];
+          wrb[i] = rbv[u][i];
+        }
+        if (b + U < nblk) {
+          ld_global_256(ra[u], wa + (b + U) * 128, true);
+          ld_global_256(rbv[u], wb + (b + U) * 128, true);
+        }
+        uint32_t xb[16];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+          if (tok_live) xv = __ldg(reinterpret_cast<const uint4*>(xg + b * 128 + 8 * c));
+          xb[4 * c] = xv.x;
+          xb[4 * c + 1] = xv.y;
+          xb[4 * c + 2] = xv.z;
+          xb[4 * c + 3] = xv.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          uint32_t a[4];
+          cvt_s8x4_f16x4(wra[i], a[0], a[2]);
+          cvt_s8x4_f16x4(wrb[i], a[1], a[3]);
+          mma_f16(acc, a, xb[2 * i], xb[2 * i + 1]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) red[warp][lane][i] = acc[i];
+  __syncthreads();
+  if (part != 0) return;
+  float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int wv = 0; wv < WPG; ++wv)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[i] += red[group * WPG + wv][lane][i];
+  // s[0], s[1]: row n_a, tokens 2 t4 and 2 t4 + 1; s[2], s[3]: row n_b
+  const int tok = 2 * t4;
+  auto finish = [&](int n, float v0, float v1) {
+    if (n >= N) return;
+    const float sc = scale[n];
+    if (tok < T) {
+      float* d = y + static_cast<long long>(tok) * N + n;
+      *d = beta != 0.f ? v0 * sc + beta * *d : v0 * sc;
+    }
+    if (tok + 1 < T) {
+      float* d = y + static_cast<long long>(tok + 1) * N + n;
+      *d = beta != 0.f ? v1 * sc + beta * *d : v1 * sc;
+    }
+  };
+  finish(n_a, s[0], s[1]);
+  finish(n_b, s[2], s[3]);
+}
+
 // ---- GEMM (T > 8) --------------------------------------------------------------------------
 
 constexpr int kBM = 128;  // weight rows per CTA
@@ -454,6 +561,29 @@ static bool i8_fused_preferred(const WeightView& W, int T) {
   return T <= umma_i8_fused_tokens() && static_cast<long long>(W.N) * W.K >= (32ll << 20) && static_cast<long long>(T) * W.K <= 32768;
 }
 
+// Small int8 matrices with up to 8 tokens: gemv_rows_i8_kernel (no K split across CTAs, no set-up).
+// RB200_I8_ROWS_MB: the largest matrix (MB) that takes it; 0 turns it off.
+static bool i8_rows_preferred(const WeightView& W, int T) {
+  static const long long max_bytes = [] {
+    const char* e = std::getenv("RB200_I8_ROWS_MB");
+    return (e ? std::atoll(e) : 20) << 20;
+  }();
+  return W.i8 != nullptr && T >= 1 && T <= 8 && W.K % (kRowsWarps * 128) == 0 && static_cast<long long>(W.N) * W.K <= max_bytes &&
+         W.ld % 32 == 0 && (reinterpret_cast<uintptr_t>(W.i8) & 31) == 0;
+}
+
+static void launch_gemv_rows_i8(const WeightView& W, const __half* x, int ldx, float* y, int T, float beta, cudaStream_t st) {
+  // rows per CTA: 16 unless that needs more CTAs than fit the SMs at once (two per SM by registers)
+  const int slots = 2 * sm_count();
+  count_launch();
+  if (div_up(W.N, 16) <= slots)
+    launch_pdl(gemv_rows_i8_kernel<8>, dim3(div_up(W.N, 16)), dim3(kRowsWarps * 32), 0, st, W.i8, W.scale, x, y, T, W.K, W.N, W.ld, ldx, beta);
+  else if (div_up(W.N, 32) <= slots)
+    launch_pdl(gemv_rows_i8_kernel<4>, dim3(div_up(W.N, 32)), dim3(kRowsWarps * 32), 0, st, W.i8, W.scale, x, y, T, W.K, W.N, W.ld, ldx, beta);
+  else
+    launch_pdl(gemv_rows_i8_kernel<2>, dim3(div_up(W.N, 64)), dim3(kRowsWarps * 32), 0, st, W.i8, W.scale, x, y, T, W.K, W.N, W.ld, ldx, beta);
+}
+
 static bool gemm_forced_legacy() {
   static const bool v = [] {
     const char* e = std::getenv("RB200_GEMM");
@@ -478,6 +608,7 @@ I8Digits linear_digits_dest(const WeightView& W, const __half* x, int ldx, int T
   // The conditions under which launch_linear reads digits from `scratch` (below), and rows whose
   // pitch is the digit planes' pitch.
   if (off || !W.i8 || gemm_forced_legacy() || T < 1 || T > 16 || ldx != W.K || !umma_i8_usable(W, x, ldx, T)) return {};
+  if (i8_rows_preferred(W, T) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) return {};  // that kernel reads x itself
   if (T <= 8 && !i8_digits_preferred(W)) return {};
   const size_t po = gemv_partials_bytes(W.N, W.K);
   const bool room = scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 && scratch_bytes >= po + i8_digits_bytes(T, W.K);
@@ -496,6 +627,10 @@ void launch_gemv(const WeightView& W, const __half* x, int ldx, float* y, int T,
   // fp16 weights stream faster through TMA (whole 128-byte row pieces) than through per-lane
   // 16-byte loads, so the few-token case uses the tcgen05 kernel with a 16-token tile.
   if (W.f16 && !gemm_forced_legacy() && umma_gemm_usable(W, x, ldx)) return launch_umma_gemm(W, x, ldx, y, T, beta, st);
+  if (!digits_ready && i8_rows_preferred(W, T) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ldx % 8 == 0) {
+    launch_gemv_rows_i8(W, x, ldx, y, T, beta, st);
+    return;
+  }
   if (W.i8 && !gemm_forced_legacy() && i8_digits_preferred(W) && umma_i8_usable(W, x, ldx, T)) {
     const bool room = scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 &&
                       scratch_bytes >= gemv_partials_bytes(W.N, W.K) + i8_digits_bytes(T, W.K);
