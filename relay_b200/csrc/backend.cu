@@ -532,8 +532,10 @@ void Backend::enqueue(const int* dm, const Plan& p, rb200_layer_cb cb, void* cb_
     const I8Digits dm = H % 4 == 0 ? linear_digits_dest(L.w_gate_up.view(), xn, Hp_, T, gs, gsb) : I8Digits{};
     launch_rmsnorm(x, nullptr, L.mlp_norm.as<float>(), xn, T, H, Hp_, eps, stream_, dm);
     launch_linear(L.w_gate_up.view(), xn, Hp_, gu, T, 0.0f, gs, gsb, stream_, dm.digits != nullptr);
-    launch_silu_mul(gu, act, T, I, Ip_, stream_);
-    launch_linear(L.w_down.view(), act, Ip_, x, T, 1.0f, gs, gsb, stream_);  // x += act w_down^T
+    // SwiGLU writes the digits the down projection reads, where it reads digits
+    const I8Digits dd = I % 4 == 0 ? linear_digits_dest(L.w_down.view(), act, Ip_, T, gs, gsb) : I8Digits{};
+    launch_silu_mul(gu, act, T, I, Ip_, stream_, dd);
+    launch_linear(L.w_down.view(), act, Ip_, x, T, 1.0f, gs, gsb, stream_, dd.digits != nullptr);  // x += act w_down^T
   }
   if (R > 0) {
     launch_rmsnorm(x, d_rows, final_norm_.as<float>(), xn, R, H, Hp_, eps, stream_);

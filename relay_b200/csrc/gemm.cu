@@ -305,7 +305,7 @@ gemv_kernel(const void* __restrict__ wv, const float* __restrict__ scale, const 
 constexpr int kRowsWarps = 8;
 
 template <int WPG>
-__global__ void __launch_bounds__(kRowsWarps * 32)
+__global__ void __launch_bounds__(kRowsWarps * 32, 2)
 gemv_rows_i8_kernel(const int8_t* __restrict__ w, const float* __restrict__ scale, const __half* __restrict__ x,
                     float* __restrict__ y, int T, int K, int N, int ldw, int ldx, float beta) {
   pdl_trigger();
@@ -337,32 +337,22 @@ gemv_rows_i8_kernel(const int8_t* __restrict__ w, const float* __restrict__ scal
     for (int u = 0; u < U; ++u) {
       const int b = b0 + u;
       if (b < nblk) {
-        uint32_t wra[8], wrb[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          wra[i] = ra[u][i];
-          wrb[i] = rbv[u][i];
-        }
-        if (b + U < nblk) {
-          ld_global_256(ra[u], wa + (b + U) * 128, true);
-          ld_global_256(rbv[u], wb + (b + U) * 128, true);
-        }
-        uint32_t xb[16];
+        // two mma per 16-byte piece of the token's activations, so only four registers of x are live
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint4 xv = make_uint4(0u, 0u, 0u, 0u);
           if (tok_live) xv = __ldg(reinterpret_cast<const uint4*>(xg + b * 128 + 8 * c));
-          xb[4 * c] = xv.x;
-          xb[4 * c + 1] = xv.y;
-          xb[4 * c + 2] = xv.z;
-          xb[4 * c + 3] = xv.w;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
           uint32_t a[4];
-          cvt_s8x4_f16x4(wra[i], a[0], a[2]);
-          cvt_s8x4_f16x4(wrb[i], a[1], a[3]);
-          mma_f16(acc, a, xb[2 * i], xb[2 * i + 1]);
+          cvt_s8x4_f16x4(ra[u][2 * c], a[0], a[2]);
+          cvt_s8x4_f16x4(rbv[u][2 * c], a[1], a[3]);
+          mma_f16(acc, a, xv.x, xv.y);
+          cvt_s8x4_f16x4(ra[u][2 * c + 1], a[0], a[2]);
+          cvt_s8x4_f16x4(rbv[u][2 * c + 1], a[1], a[3]);
+          mma_f16(acc, a, xv.z, xv.w);
+        }
+        if (b + U < nblk) {  // refill the slot: U loads stay in flight
+          ld_global_256(ra[u], wa + (b + U) * 128, true);
+          ld_global_256(rbv[u], wb + (b + U) * 128, true);
         }
       }
     }

@@ -45,7 +45,9 @@ void launch_rmsnorm(const float* x, const int* rows, const float* w, __half* out
                     cudaStream_t st, I8Digits dg = {});
 void launch_qkv_post(float* qkv, const float* bias, const float* inv_freq, const TokenMeta& m, int T, __half* kc,
                      __half* vc, int heads, int kv_heads, int D, int block_size, cudaStream_t st);
-void launch_silu_mul(const float* gu, __half* act, int T, int I, int ld_act, cudaStream_t st);
+// `dg` (from linear_digits_dest for the linear that reads `act` next; needs I and ld_act multiples
+// of 4): also write the rows as digits.
+void launch_silu_mul(const float* gu, __half* act, int T, int I, int ld_act, cudaStream_t st, I8Digits dg = {});
 void launch_f32_to_f16(const float* in, __half* out, size_t n, cudaStream_t st);
 void launch_convert_rows_f16(const float* in, __half* out, int rows, int K, int ld, cudaStream_t st);
 void launch_quantize_rows_int8(const float* in, int8_t* out, float* scale, int rows, int K, int ld, cudaStream_t st);

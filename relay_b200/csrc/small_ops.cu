@@ -198,6 +198,47 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, __half* __restrict
   }
 }
 
+// The same with one block per token, for the few-token steps whose down projection reads its input
+// as int8 digits (i8_digits.cuh): the block also finds the row's largest magnitude and writes the
+// digit planes and the token's scale, so that projection needs no digit pass of its own. The fp16
+// row is written as above (same expression, same rounding). I and ld_act are multiples of 4.
+__global__ void silu_mul_row_kernel(const float* __restrict__ gu, __half* __restrict__ act, int I, int ld_act,
+                                    int8_t* __restrict__ digits, float* __restrict__ tscale) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const float* g = gu + static_cast<long long>(t) * 2 * I;
+  const float* u = g + I;
+  __half* a = act + static_cast<long long>(t) * ld_act;
+  float mx = 0.0f;
+  for (int i = threadIdx.x * 4; i < ld_act; i += blockDim.x * 4) {
+    uint2 p = make_uint2(0u, 0u);
+    if (i < I) {
+      const float4 gv = *reinterpret_cast<const float4*>(g + i);
+      const float4 uv = *reinterpret_cast<const float4*>(u + i);
+      p.x = pack_half2(gv.x / (1.0f + expf(-gv.x)) * uv.x, gv.y / (1.0f + expf(-gv.y)) * uv.y);
+      p.y = pack_half2(gv.z / (1.0f + expf(-gv.z)) * uv.z, gv.w / (1.0f + expf(-gv.w)) * uv.w);
+    }
+    *reinterpret_cast<uint2*>(a + i) = p;
+    const __half2 m = __hmax2(__habs2(*reinterpret_cast<__half2*>(&p.x)), __habs2(*reinterpret_cast<__half2*>(&p.y)));
+    mx = fmaxf(mx, fmaxf(__low2float(m), __high2float(m)));
+  }
+  mx = block_max(mx, red);
+  float up, down;
+  i8d::digit_scales(mx, up, down);
+  if (threadIdx.x == 0) tscale[t] = down;
+  const long long plane = static_cast<long long>(gridDim.x) * ld_act;
+  int8_t* d = digits + static_cast<long long>(t) * ld_act;
+  for (int i = threadIdx.x * 4; i < ld_act; i += blockDim.x * 4) {
+    const uint2 p = *reinterpret_cast<const uint2*>(a + i);  // the four halves this thread stored above
+    uint32_t dw[i8d::kDigits];
+    i8d::digits4(p, up, dw);
+#pragma unroll
+    for (int k = 0; k < i8d::kDigits; ++k) *reinterpret_cast<uint32_t*>(d + k * plane + i) = dw[k];
+  }
+}
+
 // fp32 -> fp16 round-to-nearest-even, the bits of the host's f32_to_f16
 // (engine/src/cuda_backend.cu:110-116, engine/src/safetensors.cpp:65-88).
 __global__ void f32_to_f16_kernel(const float* __restrict__ in, __half* __restrict__ out, size_t n) {
@@ -332,10 +373,14 @@ void launch_qkv_post(float* qkv, const float* bias, const float* inv_freq, const
              block_size);
 }
 
-void launch_silu_mul(const float* gu, __half* act, int T, int I, int ld_act, cudaStream_t st) {
+void launch_silu_mul(const float* gu, __half* act, int T, int I, int ld_act, cudaStream_t st, I8Digits dg) {
   if (T == 0) return;
-  dim3 grid(div_up(ld_act, 4 * 256), T);
   count_launch();
+  if (dg.digits != nullptr && (I & 3) == 0 && (ld_act & 3) == 0) {
+    launch_pdl(silu_mul_row_kernel, dim3(T), dim3(1024), 0, st, gu, act, I, ld_act, dg.digits, dg.tscale);
+    return;
+  }
+  dim3 grid(div_up(ld_act, 4 * 256), T);
   launch_pdl(silu_mul_kernel, grid, dim3(256), 0, st, gu, act, I, ld_act);
 }
 
