@@ -170,6 +170,26 @@ __device__ __forceinline__ int swz(int row, int chunk) {
   else return row * CH + chunk;
 }
 
+// (largest value, lowest index holding it) over this thread's share of row[0..V): elements
+// t, t + n, t + 2n, ... for thread t of n. Eight loads are issued before any of them is compared,
+// so the loop runs at memory throughput rather than one round trip per element.
+__device__ __forceinline__ void strided_argmax(const float* __restrict__ row, int V, int t, int n, float& best, int& bi) {
+  best = -INFINITY;
+  bi = 0x7fffffff;
+  constexpr int U = 8;
+  for (int i0 = t; i0 < V; i0 += U * n) {
+    float v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = i0 + u * n < V ? row[i0 + u * n] : -INFINITY;
+#pragma unroll
+    for (int u = 0; u < U; ++u)  // ascending index: a later equal value never replaces an earlier one
+      if (v[u] > best) {
+        best = v[u];
+        bi = i0 + u * n;
+      }
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

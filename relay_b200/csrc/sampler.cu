@@ -57,15 +57,9 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const rb200_sampling
   if (!greedy && !((p.top_k <= 0 || p.top_k >= V) && p.top_p >= 1.0f)) return;
 
   // ---- the row's maximum and its lowest id ----
-  float best = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += kSampleThreads) {
-    const float v = row[i];
-    if (v > best || (v == best && i < bi)) {
-      best = v;
-      bi = i;
-    }
-  }
+  float best;
+  int bi;
+  strided_argmax(row, V, threadIdx.x, kSampleThreads, best, bi);
   auto merge = [&](float ov, int oi) {
     if (ov > best || (ov == best && oi < bi)) {
       best = ov;

@@ -71,7 +71,24 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
   __half* o = out + static_cast<long long>(r) * ld_out;
   float ss = 0.0f;
   const bool vec = (H & 3) == 0;
-  if (vec) {
+  // Rows of up to 8 values per thread (every width the path's models have) stay in registers
+  // between the two passes, and the norm weights are fetched before the block-wide sum: one
+  // round trip to memory instead of three.
+  const bool cached = vec && H <= static_cast<int>(blockDim.x) * 8;
+  float4 xc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+  float4 wc[2] = {xc[0], xc[0]};
+  if (cached) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = (k * blockDim.x + threadIdx.x) * 4;
+      if (i < H) {
+        xc[k] = *reinterpret_cast<const float4*>(xr + i);
+        wc[k] = *reinterpret_cast<const float4*>(w + i);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) ss += xc[k].x * xc[k].x + xc[k].y * xc[k].y + xc[k].z * xc[k].z + xc[k].w * xc[k].w;
+  } else if (vec) {
     for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
       float4 v = *reinterpret_cast<const float4*>(xr + i);
       ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
@@ -83,9 +100,15 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
   const float inv = 1.0f / sqrtf(ss / static_cast<float>(H) + eps);
   float mx = 0.0f;  // largest magnitude of the rounded row
   if (vec) {
-    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
-      float4 v = *reinterpret_cast<const float4*>(xr + i);
-      float4 g = *reinterpret_cast<const float4*>(w + i);
+    for (int i = threadIdx.x * 4, k = 0; i < H; i += blockDim.x * 4, ++k) {
+      float4 v, g;
+      if (cached) {
+        v = k == 0 ? xc[0] : xc[1];
+        g = k == 0 ? wc[0] : wc[1];
+      } else {
+        v = *reinterpret_cast<const float4*>(xr + i);
+        g = *reinterpret_cast<const float4*>(w + i);
+      }
       uint2 p;
       p.x = pack_half2(g.x * (v.x * inv), g.y * (v.y * inv));
       p.y = pack_half2(g.z * (v.z * inv), g.w * (v.w * inv));
@@ -306,15 +329,9 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int V, int*
   __shared__ float sv[32];
   __shared__ int si[32];
   const float* row = logits + static_cast<long long>(blockIdx.x) * V;
-  float best = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best || (v == best && i < bi)) {
-      best = v;
-      bi = i;
-    }
-  }
+  float best;
+  int bi;
+  strided_argmax(row, V, threadIdx.x, blockDim.x, best, bi);
   auto merge = [&](float ov, int oi) {
     if (ov > best || (ov == best && oi < bi)) {
       best = ov;

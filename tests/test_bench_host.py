@@ -48,3 +48,28 @@ def test_reference_arm_stays_idle_on_other_ranks():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1"],
                        env=env, capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and r.stdout.strip() == ""
+
+
+def test_step_bytes_count_kv_once_and_weights_once():
+    cfg = bench.llama3_8b()
+    attn, step = bench.step_bytes_of(cfg, 256, 4096, 16, int8=False)
+    # per context token 2 (K, V) x 8 KV heads x 128 x 2 bytes; per sequence q in (fp32) + out (fp16); one id per block
+    assert attn == 256 * 4096 * 4096 + 256 * 32 * 128 * 6 + 256 * 256 * 4
+    layer_params = 32 * (6144 * 4096 + 4096 * 4096 + 28672 * 4096 + 4096 * 14336)
+    head = 128256 * 4096
+    norms = (2 * 32 + 1) * 4096
+    assert step == attn * 32 + 2 * (layer_params + head + norms)
+    _, step8 = bench.step_bytes_of(cfg, 256, 4096, 16, int8=True)
+    assert step - step8 == layer_params  # only the layer matrices shrink to one byte per weight
+
+
+def test_reference_arm_sets_its_own_thread_count_under_a_launcher():
+    # a multi-process launcher exports OMP_NUM_THREADS=1 to its ranks; the CPU arm must not inherit that
+    from oracle import oracle
+    code = ("import os; os.environ['OMP_NUM_THREADS'] = '1'\n"
+            "from oracle import oracle\n"
+            "print(oracle.set_threads(), len(os.sched_getaffinity(0)))")
+    r = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True, timeout=120,
+                       env=dict(os.environ, OMP_NUM_THREADS="1"))
+    used, cores = (int(v) for v in r.stdout.split())
+    assert used == cores
