@@ -23,6 +23,7 @@
 #include <mutex>
 
 #include "kernels.h"
+#include "tcgen05.cuh"
 
 namespace rb200 {
 
@@ -102,12 +103,14 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
 decode_split_kernel(const float* __restrict__ q, TokenMeta m, const int* __restrict__ decode_tokens,
                     const __half* __restrict__ kc, const __half* __restrict__ vc, float* __restrict__ part_o,
                     float* __restrict__ part_ml, __half* __restrict__ out, int heads, int kv_heads, int bs,
-                    int bs_shift, int q_stride, int o_stride, float scale_log2e, int max_parts, int slice) {
+                    int bs_shift, int q_stride, int o_stride, float scale_log2e, int max_parts, int slice,
+                    int cluster_merge) {
   constexpr int CH = D / 8;               // 16-byte chunks per K/V row
   constexpr int TILE_HALVES = 16 * D;     // one 16-key tile of K (or V)
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ int s_table[kDecodeSlice];   // block ids covering the slice: slice / block_size <= 512 entries
   __shared__ float s_m[kDecWarps][16], s_l[kDecWarps][16];
+  __shared__ float cm_m[16], cm_l[16];    // cluster merge: this slice's (max, sum) per head
 
   pdl_trigger();
   pdl_wait();
@@ -115,8 +118,12 @@ decode_split_kernel(const float* __restrict__ q, TokenMeta m, const int* __restr
   const int tok = decode_tokens[di];
   const int ctx = m.pos[tok] + 1;
   const int k0 = part * slice;
-  if (k0 >= ctx) return;
-  const int k1 = min(ctx, k0 + slice);
+  // A slice past the context has nothing to do. Launched as a cluster over the slices (the merge
+  // then happens here, over distributed shared memory) its CTA still has to meet the others at the
+  // cluster barriers, so it runs through with no keys: max -inf, sum 0.
+  const bool empty = k0 >= ctx;
+  if (empty && !cluster_merge) return;
+  const int k1 = empty ? k0 : min(ctx, k0 + slice);
   const int ntiles = (k1 - k0 + 15) >> 4;
   const int G = heads / kv_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -126,7 +133,7 @@ decode_split_kernel(const float* __restrict__ q, TokenMeta m, const int* __restr
   const int* table = m.tables + m.table_off[m.seq[tok]];
   const int first_block = bs_shift >= 0 ? (k0 >> bs_shift) : k0 / bs;
   const int last_block = bs_shift >= 0 ? ((k1 - 1) >> bs_shift) : (k1 - 1) / bs;
-  const int nblk = last_block - first_block + 1;
+  const int nblk = empty ? 0 : last_block - first_block + 1;
   {
     const int* src = table + first_block;
     if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
@@ -320,6 +327,13 @@ decode_split_kernel(const float* __restrict__ q, TokenMeta m, const int* __restr
     const int head = kvh * G + r;
     if (max_parts == 1) {
       out[static_cast<long long>(tok) * o_stride + head * D + d] = __float2half_rn(acc / L);
+    } else if (cluster_merge) {
+      // parked behind warp 0's own partial, in a part of its ring nothing reads any more
+      reinterpret_cast<float*>(smem_raw)[16 * D + idx] = acc;
+      if (d == 0) {
+        cm_m[r] = M;
+        cm_l[r] = L;
+      }
     } else {
       const long long slot = (static_cast<long long>(di) * heads + head) * max_parts + part;
       part_o[slot * D + d] = acc;
@@ -328,6 +342,32 @@ decode_split_kernel(const float* __restrict__ q, TokenMeta m, const int* __restr
         part_ml[slot * 2 + 1] = L;
       }
     }
+  }
+  if (cluster_merge) {
+    // out = sum_p 2^(m_p - M) O_p / sum_p 2^(m_p - M) l_p over the cluster's slices
+    // (engine/src/cuda_kernels.cuh:341-362, in the log2 domain the slices already use): the CTA of
+    // slice p finishes the heads r with r % slices == p, reading every member's (m, l, O) over
+    // distributed shared memory in rank order, so the result is the same on every run and neither
+    // partial results nor a second kernel touch global memory.
+    tc::cluster_sync_all();
+    const uint32_t o_addr = smem_u32(reinterpret_cast<float*>(smem_raw) + 16 * D);
+    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+      const int r = idx / D, d = idx - r * D;
+      if (r % max_parts != part) continue;
+      float M = -INFINITY;
+      for (int p = 0; p < max_parts; ++p) M = fmaxf(M, tc::ld_dsmem_f32(smem_u32(&cm_m[r]), p));
+      float acc = 0.f, L = 0.f;
+      for (int p = 0; p < max_parts; ++p) {
+        const float mp = tc::ld_dsmem_f32(smem_u32(&cm_m[r]), p);
+        if (mp != -INFINITY) {
+          const float e = fast_exp2(mp - M);
+          acc += e * tc::ld_dsmem_f32(o_addr + static_cast<uint32_t>(idx) * 4, p);
+          L += e * tc::ld_dsmem_f32(smem_u32(&cm_l[r]), p);
+        }
+      }
+      out[static_cast<long long>(tok) * o_stride + (kvh * G + r) * D + d] = __float2half_rn(acc / L);
+    }
+    tc::cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
   }
 }
 
@@ -619,26 +659,48 @@ void raise_smem(K kernel, size_t bytes) {
 template <int D, bool CONTIG, bool WIDE>
 void launch_decode_t(const AttnShape& s, const float* q, const TokenMeta& m, const int* decode_tokens, int n_decode,
                      int parts, int slice, const __half* kc, const __half* vc, float* part_o, float* part_ml, __half* out,
-                     cudaStream_t st) {
+                     cudaStream_t st, bool cluster_merge) {
   static PerDeviceOnce once;
   auto kernel = decode_split_kernel<D, CONTIG, WIDE>;
   if (once.first()) raise_smem(kernel, decode_smem_bytes<D>());
   const float scale_log2e = kLog2e / sqrtf(static_cast<float>(D));
   dim3 grid(n_decode, s.kv_heads, parts);
   count_launch();
-  launch_pdl(kernel, grid, dim3(kDecWarps * 32), decode_smem_bytes<D>(), st, q, m, decode_tokens, kc, vc, part_o, part_ml, out,
-             s.heads, s.kv_heads, s.block_size, shift_of(s.block_size), s.q_stride, s.o_stride, scale_log2e, parts, slice);
+  if (!cluster_merge) {
+    launch_pdl(kernel, grid, dim3(kDecWarps * 32), decode_smem_bytes<D>(), st, q, m, decode_tokens, kc, vc, part_o, part_ml, out,
+               s.heads, s.kv_heads, s.block_size, shift_of(s.block_size), s.q_stride, s.o_stride, scale_log2e, parts, slice, 0);
+    return;
+  }
+  // the slices of one (token, KV head) as one thread-block cluster
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kDecWarps * 32);
+  cfg.dynamicSmemBytes = decode_smem_bytes<D>();
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = parts;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  const int heads = s.heads, kv_heads = s.kv_heads, bs = s.block_size, bs_shift = shift_of(s.block_size), q_stride = s.q_stride,
+            o_stride = s.o_stride, one = 1;
+  RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, q, m, decode_tokens, kc, vc, part_o, part_ml, out, heads, kv_heads, bs, bs_shift, q_stride,
+                             o_stride, scale_log2e, parts, slice, one));
 }
 
 template <int D>
 void launch_decode_d(const AttnShape& s, const float* q, const TokenMeta& m, const int* decode_tokens, int n_decode,
                      int parts, int slice, const __half* kc, const __half* vc, float* part_o, float* part_ml, __half* out,
-                     cudaStream_t st) {
+                     cudaStream_t st, bool cm) {
   const bool contig = s.block_size % 16 == 0, wide = s.heads / s.kv_heads > 8;
-  if (contig && !wide) launch_decode_t<D, true, false>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st);
-  else if (contig) launch_decode_t<D, true, true>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st);
-  else if (!wide) launch_decode_t<D, false, false>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st);
-  else launch_decode_t<D, false, true>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st);
+  if (contig && !wide) launch_decode_t<D, true, false>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st, cm);
+  else if (contig) launch_decode_t<D, true, true>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st, cm);
+  else if (!wide) launch_decode_t<D, false, false>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st, cm);
+  else launch_decode_t<D, false, true>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st, cm);
 }
 
 template <int D>
@@ -687,8 +749,20 @@ DecodePlan plan_decode(const AttnShape& s, int n_decode, int max_ctx) {
   DecodePlan p;
   p.slice = slice;
   p.parts = parts;
-  // one slice writes the output directly: no partial results, no merge
-  p.scratch_bytes = parts > 1 ? static_cast<size_t>(n_decode) * s.heads * parts * (s.D + 2) * sizeof(float) : 0;
+  // Up to 8 slices (the portable cluster size) can be merged inside the kernel, over distributed
+  // shared memory. That pays only while the whole grid is resident at once with an SM to each CTA: a
+  // cluster keeps all its slots until its last slice is done and must be placed inside one GPC,
+  // which costs more than the merge kernel once CTAs queue (32 sequences with contexts of
+  // 1024 - 4096: 72.6 us against 62.4; an 8-sequence step 3.57 ms against 3.38; a 1-sequence
+  // step 2.52 against 2.56). RB200_DECODE_CLUSTER=0 turns it off, =1 uses it whenever slices <= 8.
+  static const int cluster_mode = [] {
+    const char* e = std::getenv("RB200_DECODE_CLUSTER");
+    return e ? (e[0] == '0' ? 0 : 2) : 1;
+  }();
+  const bool resident = pairs_kv * parts <= static_cast<long long>(sm_count());
+  p.cluster_merge = parts > 1 && parts <= 8 && (cluster_mode == 2 || (cluster_mode == 1 && resident));
+  // one slice writes the output directly, a cluster merges on chip: no partial results, no merge kernel
+  p.scratch_bytes = (parts > 1 && !p.cluster_merge) ? static_cast<size_t>(n_decode) * s.heads * parts * (s.D + 2) * sizeof(float) : 0;
   return p;
 }
 
@@ -702,13 +776,13 @@ void launch_decode_attention(const AttnShape& s, const float* q, const TokenMeta
   float* part_o = scratch;
   float* part_ml = scratch + static_cast<size_t>(n_decode) * s.heads * parts * s.D;
   switch (s.D) {
-    case 16: launch_decode_d<16>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st); break;
-    case 32: launch_decode_d<32>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st); break;
-    case 64: launch_decode_d<64>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st); break;
-    case 128: launch_decode_d<128>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st); break;
+    case 16: launch_decode_d<16>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st, plan.cluster_merge); break;
+    case 32: launch_decode_d<32>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st, plan.cluster_merge); break;
+    case 64: launch_decode_d<64>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st, plan.cluster_merge); break;
+    case 128: launch_decode_d<128>(s, q, m, decode_tokens, n_decode, parts, slice, kc, vc, part_o, part_ml, out, st, plan.cluster_merge); break;
     default: fail(RB200_ERR_INVALID_ARGUMENT, "decode attention: head_dim must be 16, 32, 64 or 128");
   }
-  if (parts > 1) {
+  if (parts > 1 && !plan.cluster_merge) {
     const int pairs = n_decode * s.heads;
     count_launch();
     launch_pdl(decode_merge_kernel, dim3(div_up(pairs, 4)), dim3(128), 0, st, part_o, part_ml, decode_tokens, m.pos, out,

@@ -533,7 +533,7 @@ void Backend::enqueue(const int* dm, const Plan& p, rb200_layer_cb cb, void* cb_
     launch_rmsnorm(x, nullptr, L.mlp_norm.as<float>(), xn, T, H, Hp_, eps, stream_, dm);
     launch_linear(L.w_gate_up.view(), xn, Hp_, gu, T, 0.0f, gs, gsb, stream_, dm.digits != nullptr);
     // SwiGLU writes the digits the down projection reads, where it reads digits
-    const I8Digits dd = I % 4 == 0 ? linear_digits_dest(L.w_down.view(), act, Ip_, T, gs, gsb) : I8Digits{};
+    const I8Digits dd = (I % 4 == 0 && Ip_ % 32 == 0) ? linear_digits_dest(L.w_down.view(), act, Ip_, T, gs, gsb) : I8Digits{};
     launch_silu_mul(gu, act, T, I, Ip_, stream_, dd);
     launch_linear(L.w_down.view(), act, Ip_, x, T, 1.0f, gs, gsb, stream_, dd.digits != nullptr);  // x += act w_down^T
   }

@@ -45,8 +45,8 @@ void launch_rmsnorm(const float* x, const int* rows, const float* w, __half* out
                     cudaStream_t st, I8Digits dg = {});
 void launch_qkv_post(float* qkv, const float* bias, const float* inv_freq, const TokenMeta& m, int T, __half* kc,
                      __half* vc, int heads, int kv_heads, int D, int block_size, cudaStream_t st);
-// `dg` (from linear_digits_dest for the linear that reads `act` next; needs I and ld_act multiples
-// of 4): also write the rows as digits.
+// `dg` (from linear_digits_dest for the linear that reads `act` next; needs I a multiple of 4 and
+// ld_act of 32): also write the rows as digits.
 void launch_silu_mul(const float* gu, __half* act, int T, int I, int ld_act, cudaStream_t st, I8Digits dg = {});
 void launch_f32_to_f16(const float* in, __half* out, size_t n, cudaStream_t st);
 void launch_convert_rows_f16(const float* in, __half* out, int rows, int K, int ld, cudaStream_t st);
@@ -76,6 +76,7 @@ size_t decode_scratch_bytes(const AttnShape& s, int n_decode, int max_ctx);
 // bytes of partial results it parks in its scratch (0 with one slice).
 struct DecodePlan {
   int slice = 0, parts = 0;
+  bool cluster_merge = false;  // the slices of a (token, KV head) run as one cluster and merge on chip
   size_t scratch_bytes = 0;
 };
 DecodePlan plan_decode(const AttnShape& s, int n_decode, int max_ctx);

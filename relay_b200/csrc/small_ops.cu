@@ -5,6 +5,7 @@
 // bound by HBM traffic or launch latency.
 #include "i8_digits.cuh"
 #include "kernels.h"
+#include "tcgen05.cuh"
 
 namespace rb200 {
 
@@ -221,21 +222,28 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, __half* __restrict
   }
 }
 
-// The same with one block per token, for the few-token steps whose down projection reads its input
-// as int8 digits (i8_digits.cuh): the block also finds the row's largest magnitude and writes the
-// digit planes and the token's scale, so that projection needs no digit pass of its own. The fp16
-// row is written as above (same expression, same rounding). I and ld_act are multiples of 4.
+// The same for the few-token steps whose down projection reads its input as int8 digits
+// (i8_digits.cuh): a cluster of kSiluCluster CTAs per token, each taking an equal share of the row.
+// A CTA writes its share of the fp16 row as above (same expression, same rounding) and finds its
+// largest magnitude; the shares' maxima are exchanged through distributed shared memory, and every
+// CTA then writes the digit planes of its share against the row's scale (rank 0 writes the scale),
+// so that projection needs no digit pass of its own. I and ld_act are multiples of 4, ld_act of
+// 4 * kSiluCluster.
+constexpr int kSiluCluster = 8;
+
 __global__ void silu_mul_row_kernel(const float* __restrict__ gu, __half* __restrict__ act, int I, int ld_act,
                                     int8_t* __restrict__ digits, float* __restrict__ tscale) {
   pdl_trigger();
   pdl_wait();
   __shared__ float red[32];
-  const int t = blockIdx.x;
+  __shared__ float share_max;
+  const int t = blockIdx.y, rank = blockIdx.x;  // the cluster spans x
+  const int per = ld_act / kSiluCluster, lo = rank * per, hi = lo + per;
   const float* g = gu + static_cast<long long>(t) * 2 * I;
   const float* u = g + I;
   __half* a = act + static_cast<long long>(t) * ld_act;
   float mx = 0.0f;
-  for (int i = threadIdx.x * 4; i < ld_act; i += blockDim.x * 4) {
+  for (int i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
     uint2 p = make_uint2(0u, 0u);
     if (i < I) {
       const float4 gv = *reinterpret_cast<const float4*>(g + i);
@@ -248,12 +256,18 @@ __global__ void silu_mul_row_kernel(const float* __restrict__ gu, __half* __rest
     mx = fmaxf(mx, fmaxf(__low2float(m), __high2float(m)));
   }
   mx = block_max(mx, red);
+  if (threadIdx.x == 0) share_max = mx;
+  tc::cluster_sync_all();  // every share's maximum is in its CTA's shared memory
+  float row_max = 0.0f;
+#pragma unroll
+  for (int r = 0; r < kSiluCluster; ++r) row_max = fmaxf(row_max, tc::ld_dsmem_f32(smem_u32(&share_max), r));
+  tc::cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
   float up, down;
-  i8d::digit_scales(mx, up, down);
-  if (threadIdx.x == 0) tscale[t] = down;
-  const long long plane = static_cast<long long>(gridDim.x) * ld_act;
+  i8d::digit_scales(row_max, up, down);
+  if (rank == 0 && threadIdx.x == 0) tscale[t] = down;
+  const long long plane = static_cast<long long>(gridDim.y) * ld_act;
   int8_t* d = digits + static_cast<long long>(t) * ld_act;
-  for (int i = threadIdx.x * 4; i < ld_act; i += blockDim.x * 4) {
+  for (int i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
     const uint2 p = *reinterpret_cast<const uint2*>(a + i);  // the four halves this thread stored above
     uint32_t dw[i8d::kDigits];
     i8d::digits4(p, up, dw);
@@ -393,8 +407,25 @@ void launch_qkv_post(float* qkv, const float* bias, const float* inv_freq, const
 void launch_silu_mul(const float* gu, __half* act, int T, int I, int ld_act, cudaStream_t st, I8Digits dg) {
   if (T == 0) return;
   count_launch();
-  if (dg.digits != nullptr && (I & 3) == 0 && (ld_act & 3) == 0) {
-    launch_pdl(silu_mul_row_kernel, dim3(T), dim3(1024), 0, st, gu, act, I, ld_act, dg.digits, dg.tscale);
+  RB_REQUIRE(dg.digits == nullptr || ((I & 3) == 0 && ld_act % (4 * kSiluCluster) == 0 && dg.tscale != nullptr),
+             "silu_mul: digits need I a multiple of 4 and rows of whole 32-element groups");
+  if (dg.digits != nullptr) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(kSiluCluster, T);
+    cfg.blockDim = dim3(512);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kSiluCluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    int8_t* digits = dg.digits;
+    float* tscale = dg.tscale;
+    RB_CUDA(cudaLaunchKernelEx(&cfg, silu_mul_row_kernel, gu, act, I, ld_act, digits, tscale));
     return;
   }
   dim3 grid(div_up(ld_act, 4 * 256), T);

@@ -205,6 +205,8 @@ DECODE_CASES = [
     (64, 12, 4, 1, [1, 9, 530]),      # block size 1: every key in its own block
     (64, 6, 2, 8, [5, 29, 1100]),     # block size below the 16-key tile
     (16, 4, 2, 48, [100, 777]),       # block size not a power of two
+    (128, 8, 2, 16, [5000, 4097, 700, 3]),  # more than eight slices: partials in global memory and the merge kernel
+    (64, 8, 8, 16, [6100, 1]),
 ]
 
 

@@ -46,7 +46,7 @@ def _run_both(ops, seed, ctxs, heads, kv_heads, D, bs):
     ops.decode_attention(shape, q, meta, toks, max(ctxs), kp, vp, want)           # caller-owned scratch
     ops.decode_attention_static(shape, q, meta, toks, max(ctxs), kp, vp, got)     # the library's own array
     torch.cuda.synchronize()
-    assert ops.decode_plan(shape, T, max(ctxs))[2] > 0  # several slices: the scratch is really used
+    assert ops.decode_plan(shape, T, max(ctxs))[2] > 0  # more than eight slices: the scratch is really used
     cpu = oracle.attention(c["q"], c["q"].shape[1], c["pos"], c["seq"], c["table_off"], c["tables"], c["k_pool"], c["v_pool"],
                            heads, kv_heads, D, bs)
     return got.cpu().numpy().astype(np.float32), want.cpu().numpy().astype(np.float32), cpu
@@ -56,9 +56,10 @@ def test_static_scratch_entry_point_matches_the_caller_scratch_one_twice_in_a_ro
     if not torch.cuda.is_available():
         pytest.fail("the gpu tests need a CUDA device")
     from relay_b200 import ops
-    # both batches are split into several 512-key slices, so the scratch is really used
-    got1, want1, cpu1 = _run_both(ops, 41, [1300, 700, 2048, 513, 90], 32, 8, 128, 16)
-    got2, want2, cpu2 = _run_both(ops, 42, [600, 1025, 33], 8, 2, 64, 16)  # smaller: runs over the first call's leftovers
+    # both batches are split into more than eight 512-key slices (up to eight are merged on chip and park
+    # nothing), so the scratch is really used
+    got1, want1, cpu1 = _run_both(ops, 41, [5000, 700, 2048, 4097, 90], 32, 8, 128, 16)
+    got2, want2, cpu2 = _run_both(ops, 42, [600, 4700, 33], 8, 2, 64, 16)  # smaller: runs over the first call's leftovers
     for got, want, cpu in ((got1, want1, cpu1), (got2, want2, cpu2)):
         assert np.isfinite(got).all()
         assert _row_err(got, want) < ATTN_TOL
@@ -71,9 +72,9 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
         pytest.fail("the gpu tests need a CUDA device")
     from relay_b200 import _lib, ops
     shape = ops.attn_shape(32, 8, 128, 16)
-    # 140 tokens leave room for two slices per context, and 65536 keys are more than the largest
-    # slice (512 table entries = 8192 keys) holds: 8 slices x 140 x 32 heads x 130 floats = 18.6 MB
-    n, ctx = 140, 65536
+    # 140 tokens leave room for two slices per context, and 131072 keys are sixteen of the largest
+    # slice (512 table entries = 8192 keys): 16 slices x 140 x 32 heads x 130 floats = 37 MB
+    n, ctx = 140, 131072
     _, parts, need = ops.decode_plan(shape, n, ctx)
     assert parts > 1 and need > _lib.STATIC_DECODE_SCRATCH_BYTES
     z = torch.zeros(16, device="cuda")
