@@ -134,8 +134,10 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
     layer_bytes = 2 * be.kv_block_bytes() * per
     hop_bytes = layer_bytes * cfg.layers
 
-    # one link per decode GPU: a ring of 4 slots, each as large as one layer of a whole prompt
-    slot = (layer_bytes + 255) // 256 * 256
+    # one link per decode GPU: a ring of 4 slots, each as large as a quarter of a whole prompt's
+    # layers (a streamed layer takes one slot; a finished prompt travels as four messages)
+    group = max(1, cfg.layers // 4)
+    slot = (group * layer_bytes + 255) // 256 * 256
     links = {}
     if rank == 0:
         mine = [be.kv_link_create(4, slot) for _ in range(n_dec)]
@@ -245,6 +247,23 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
                 receive_all(transport)
             be.kv_hop_sync(60000)
 
+        def pair_ranges():  # the same prompt as a finished request: whole layer ranges per message
+            if rank == 0:
+                t0 = time.perf_counter()
+                be.kv_link_send_layers(links[1], 0, cfg.layers, tables[0])
+                enqueue_ms["ranges"] = (time.perf_counter() - t0) * 1e3
+            elif rank == 1:
+                be.kv_link_recv_layers(links[0], 0, cfg.layers, tables[0])
+            be.kv_hop_sync(30000)
+
+        def fan_ranges():
+            if rank == 0:
+                for d in range(1, world):
+                    be.kv_link_send_layers(links[d], 0, cfg.layers, tables[d - 1])
+            else:
+                be.kv_link_recv_layers(links[0], 0, cfg.layers, tables[rank - 1])
+            be.kv_hop_sync(30000)
+
         t_pair, t_fan, t_str = best_of(pair), best_of(fan), best_of(streamed)
         # byte compare of what arrived: three layers of the last prompt each decode GPU received
         digests = []
@@ -263,13 +282,37 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
                           "fan_out_ms": t_fan * 1e3, "fan_out_gbs_from_gpu0": hop_bytes * n_dec / t_fan / 1e9,
                           "streamed_prefill_ms_per_prompt": t_str / n_prompts * 1e3,
                           "received_pages_identical": bool(identical)}
+        if transport == "link":
+            # after the digests above; the receivers first wipe the pages that are compared below, so
+            # that the compare covers what the range messages landed
+            if rank > 0:
+                for layer in (0, cfg.layers // 2, cfg.layers - 1):
+                    be.write_kv_layer(layer, tables[rank - 1], np.zeros_like(be.read_kv_layer(layer, tables[rank - 1])))
+            t_pr, t_fr = best_of(pair_ranges, 5), best_of(fan_ranges, 5)
+            res["link"].update({"layer_ranges_per_message": group, "pair_ranges_ms": t_pr * 1e3,
+                                "pair_ranges_gbs": hop_bytes / t_pr / 1e9,
+                                "pair_ranges_host_enqueue_ms": enqueue_ms.get("ranges"),
+                                "fan_out_ranges_ms": t_fr * 1e3,
+                                "fan_out_ranges_gbs_from_gpu0": hop_bytes * n_dec / t_fr / 1e9})
+            digests = []
+            for d in range(1, world):
+                if rank == 0 or rank == d:
+                    h = hashlib.sha256()
+                    for layer in (0, cfg.layers // 2, cfg.layers - 1):
+                        h.update(be.read_kv_layer(layer, tables[d - 1]).tobytes())
+                    digests.append((d, h.hexdigest()))
+            allg = [None] * world
+            dist.all_gather_object(allg, digests)
+            want = dict(allg[0])
+            res["link"]["ranges_received_pages_identical"] = bool(all(want[d] == x for r in range(1, world) for d, x in allg[r]))
     # the prefill alone once more, after the streamed runs: the SM clock under the power cap drifts
     # over a run of this length, and the exposed time is a difference of two such numbers
     plain = min(plain, best_of(run_plain))
     res["prefill_ms_per_prompt"] = plain / n_prompts * 1e3
     for transport in ("nccl", "link"):
         res[transport]["exposed_ms_per_prompt"] = res[transport]["streamed_prefill_ms_per_prompt"] - res["prefill_ms_per_prompt"]
-    res["gbs_per_pair"] = res["link"]["pair_gbs"]
+    # a finished prompt handed over as layer ranges (the hop alone); layer by layer: link.pair_gbs
+    res["gbs_per_pair"] = res["link"]["pair_ranges_gbs"]
     res["transport_note"] = ("nccl: page gather -> ncclSend / ncclRecv -> scatter on one copy stream; link: gather -> copy-engine "
                              "peer copy into the receiver's ring -> scatter, ordered by two counters (no SM held during the copy)")
     for l in links.values():

@@ -276,6 +276,17 @@ int rb200_kv_link_connect(rb200_backend* b, int link, const void* peer_handle);
 int rb200_kv_link_connect_local(rb200_backend* a, int link_a, rb200_backend* b, int link_b);
 int rb200_kv_link_send_layer(rb200_backend* b, int link, int layer, const int32_t* blocks, int n);
 int rb200_kv_link_recv_layer(rb200_backend* b, int link, int layer, const int32_t* blocks, int n);
+/* The same for n_layers consecutive layers of one request whose K/V is complete (a prompt handed
+ * over after its prefill rather than streamed during it: engine/src/kv_transfer.cpp:107-128 sends
+ * the Layer frames of a finished request back to back): as many whole layers as a slot holds
+ * travel as ONE message (one gather, one copy-engine copy, one counter store), so a ring of slots
+ * of several layers moves a prompt at the copy engines' rate instead of the host's enqueue rate.
+ * The receiver makes the matching call with the same first_layer, n_layers and n (the ends cut
+ * messages by the same rule); rb200_kv_link_skip_layers is the dropping counterpart. With
+ * n_layers == 1 these are the calls above. */
+int rb200_kv_link_send_layers(rb200_backend* b, int link, int first_layer, int n_layers, const int32_t* blocks, int n);
+int rb200_kv_link_recv_layers(rb200_backend* b, int link, int first_layer, int n_layers, const int32_t* blocks, int n);
+int rb200_kv_link_skip_layers(rb200_backend* b, int link, int n_layers, int n);
 /* Sender: waits until every layer sent so far has been read out of the cache (its gather has
  * run; the copy may still be under way), after which the sender's blocks may be rewritten. The
  * reference frees a request's blocks once its last frame is written

@@ -326,6 +326,25 @@ class Backend:
         b = i32(blocks)
         _lib.check(self._L.rb200_kv_link_recv_layer(self._h, link, layer, ptr(b), b.size))
 
+    def kv_link_send_layers(self, link: int, first_layer: int, n_layers: int, blocks: Sequence[int]) -> None:
+        """Consecutive layers of a finished request, as many per message as a slot holds."""
+        b = i32(blocks)
+        _lib.check(self._L.rb200_kv_link_send_layers(self._h, link, first_layer, n_layers, ptr(b), b.size))
+
+    def kv_link_recv_layers(self, link: int, first_layer: int, n_layers: int, blocks: Sequence[int]) -> None:
+        b = i32(blocks)
+        _lib.check(self._L.rb200_kv_link_recv_layers(self._h, link, first_layer, n_layers, ptr(b), b.size))
+
+    def kv_link_skip_layers(self, link: int, n_layers: int, n_blocks: int) -> None:
+        _lib.check(self._L.rb200_kv_link_skip_layers(self._h, link, n_layers, n_blocks))
+
+    def kv_link_connect_local(self, link: int, other: "Backend", other_link: int) -> None:
+        """Joins two backends of this process (same or different devices) by address."""
+        _lib.check(self._L.rb200_kv_link_connect_local(self._h, link, other._h, other_link))
+
+    def kv_link_wait(self, link: int, timeout_ms: int = 0) -> None:
+        _lib.check(self._L.rb200_kv_link_wait(self._h, link, timeout_ms))
+
     def kv_link_close(self, link: int) -> None:
         _lib.check(self._L.rb200_kv_link_close(self._h, link))
 

@@ -53,12 +53,14 @@ DeviceBuf::DeviceBuf(size_t n, bool zero) : bytes(n) {
   RB_CUDA(cudaMalloc(&p, n));
   if (zero) RB_CUDA(cudaMemset(p, 0, n));
 }
+std::atomic<bool> g_device_wedged{false};
+
 DeviceBuf::~DeviceBuf() {
-  if (p) cudaFree(p);
+  if (p && !g_device_wedged.load()) cudaFree(p);  // cudaFree waits for the whole device
 }
 DeviceBuf& DeviceBuf::operator=(DeviceBuf&& o) noexcept {
   if (this != &o) {
-    if (p) cudaFree(p);
+    if (p && !g_device_wedged.load()) cudaFree(p);
     p = o.p;
     bytes = o.bytes;
     o.p = nullptr;
@@ -72,7 +74,7 @@ void DeviceBuf::ensure(size_t n) {
 }
 
 PinnedBuf::~PinnedBuf() {
-  if (p) cudaFreeHost(p);
+  if (p && !g_device_wedged.load()) cudaFreeHost(p);
 }
 void PinnedBuf::ensure(size_t n) {
   if (n <= bytes) return;
@@ -130,7 +132,13 @@ void rope_inv_freq(const rb200_model_config& c, std::vector<float>& inv) {
 }
 }  // namespace
 
-void Backend::set_device() const { RB_CUDA(cudaSetDevice(device_)); }
+void Backend::set_device() const {
+  // Every entry point passes here: once a stream has been abandoned behind a wait nobody will
+  // satisfy, further work in this process could block for ever in a device-wide synchronisation.
+  if (g_device_wedged.load())
+    fail(RB200_ERR_RUNTIME, "a K/V link stream of this process is stuck behind an unreleased wait; the process must be restarted");
+  RB_CUDA(cudaSetDevice(device_));
+}
 
 Matrix Backend::make_matrix(int N, int K, bool int8) {
   Matrix m;
@@ -290,9 +298,7 @@ Backend::Backend(const rb200_model_config& cfg, const rb200_weights* w, int num_
 Backend::~Backend() {
   cudaSetDevice(device_);
   nccl_finalize_noexcept();
-  cudaDeviceSynchronize();
-  session_.reset();
-  try {  // a link wait the peer never satisfied must not block the destructor
+  try {  // a link wait the peer never satisfied must not block the destructor: before any device-wide sync
     bool idle = links_idle();
     for (int i = 0; i < 50 && !idle; ++i) {  // work in flight gets half a second to drain
       std::this_thread::sleep_for(std::chrono::milliseconds(10));
@@ -301,6 +307,8 @@ Backend::~Backend() {
     if (!idle) links_release();
   } catch (...) {
   }
+  if (!g_device_wedged.load()) cudaDeviceSynchronize();
+  session_.reset();
   links_.clear();
   if (pass_done_) cudaEventDestroy(pass_done_);
   for (auto e : layer_done_) cudaEventDestroy(e);
@@ -1100,6 +1108,30 @@ int rb200_kv_link_recv_layer(rb200_backend* b, int link, int layer, const int32_
   return guarded([&] {
     RB_REQUIRE(b != nullptr, "kv_link_recv_layer: null backend");
     b->impl->kv_link_recv_layer(link, layer, blocks, n);
+    return 0;
+  });
+}
+
+int rb200_kv_link_send_layers(rb200_backend* b, int link, int first_layer, int n_layers, const int32_t* blocks, int n) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "kv_link_send_layers: null backend");
+    b->impl->kv_link_send_layers(link, first_layer, n_layers, blocks, n);
+    return 0;
+  });
+}
+
+int rb200_kv_link_recv_layers(rb200_backend* b, int link, int first_layer, int n_layers, const int32_t* blocks, int n) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "kv_link_recv_layers: null backend");
+    b->impl->kv_link_recv_layers(link, first_layer, n_layers, blocks, n);
+    return 0;
+  });
+}
+
+int rb200_kv_link_skip_layers(rb200_backend* b, int link, int n_layers, int n) {
+  return guarded([&] {
+    RB_REQUIRE(b != nullptr, "kv_link_skip_layers: null backend");
+    b->impl->kv_link_skip_layers(link, n_layers, n);
     return 0;
   });
 }

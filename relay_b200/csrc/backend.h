@@ -5,6 +5,7 @@
 // time and run on their own stream under copy_mu_.
 #pragma once
 
+#include <atomic>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -16,6 +17,11 @@
 namespace rb200 {
 
 // Device memory with RAII; zero-filled on allocation when asked.
+// Set when a stream of this process is left behind a wait nobody will satisfy (a K/V link whose
+// release did not get through): from then on nothing that synchronises the whole device may be
+// called, so buffers are abandoned instead of freed and destructors skip their device-wide sync.
+extern std::atomic<bool> g_device_wedged;
+
 struct DeviceBuf {
   void* p = nullptr;
   size_t bytes = 0;
@@ -69,8 +75,11 @@ struct KvLink {
   bool peer_is_ipc = false;  // mapped with cudaIpcOpenMemHandle (another process) rather than taken by address
   cudaStream_t streams[2] = {nullptr, nullptr};  // consecutive messages alternate between them
   cudaEvent_t gathered[2] = {nullptr, nullptr};  // behind the latest gather on each stream
+  cudaStream_t release_stream = nullptr;          // carries nothing but the host's release of this end's counters
+  PinnedBuf release_words;                        // what that release writes (filled when the link is created)
   uint32_t sent = 0, received = 0;  // messages enqueued so far in each direction
   bool broken = false;
+  bool wedged = false;  // still busy after a release: its region is abandoned, not freed
   ~KvLink();
 };
 
@@ -154,10 +163,13 @@ class Backend {
   // kv_link.cu
   int kv_link_create(int n_slots, size_t slot_bytes, void* handle_out);
   void kv_link_connect(int link, const void* peer_handle);
-  void kv_link_send_layer(int link, int layer, const int32_t* blocks, int n);
-  void kv_link_recv_layer(int link, int layer, const int32_t* blocks, int n);
+  void kv_link_send_layers(int link, int layer0, int n_layers, const int32_t* blocks, int n);
+  void kv_link_recv_layers(int link, int layer0, int n_layers, const int32_t* blocks, int n);
+  void kv_link_send_layer(int link, int layer, const int32_t* blocks, int n) { kv_link_send_layers(link, layer, 1, blocks, n); }
+  void kv_link_recv_layer(int link, int layer, const int32_t* blocks, int n) { kv_link_recv_layers(link, layer, 1, blocks, n); }
   void kv_link_connect_local(int link, Backend& other, int other_link);
-  void kv_link_skip_layer(int link, int n);
+  void kv_link_skip_layers(int link, int n_layers, int n);
+  void kv_link_skip_layer(int link, int n) { kv_link_skip_layers(link, 1, n); }
   void kv_link_wait(int link, int timeout_ms);
   void kv_link_wait_gathered(int link, int timeout_ms);
   void kv_link_close(int link);

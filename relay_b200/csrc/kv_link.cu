@@ -33,6 +33,7 @@
 #include <cstring>
 #include <string>
 #include <thread>
+#include <vector>
 
 #include "backend.h"
 
@@ -59,23 +60,25 @@ struct IdList {
   int ids[kMaxIds];
 };
 
-// Pages of one layer into / out of a contiguous [K of each block][V of each block] slot; the
-// block ids ride in the kernel's parameters, so no upload precedes the launch.
+// Pages of one or more consecutive layers into / out of a contiguous slot, per layer
+// [K of each block][V of each block]; the block ids ride in the kernel's parameters, so no upload
+// precedes the launch. k and v point at the first layer of the message; grid = (blocks, 2,
+// layers x parts), `parts` CTAs sharing one block.
 __global__ void link_gather_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, const __grid_constant__ IdList ids,
-                                   long long block_vec, uint4* __restrict__ out) {
-  const int i = blockIdx.x, which = blockIdx.y;
-  const uint4* src = (which ? v : k) + static_cast<long long>(ids.ids[i]) * block_vec;
-  uint4* dst = out + (static_cast<long long>(which) * ids.n + i) * block_vec;
-  for (long long e = blockIdx.z * blockDim.x + threadIdx.x; e < block_vec; e += static_cast<long long>(gridDim.z) * blockDim.x)
+                                   long long block_vec, long long layer_vec, int parts, uint4* __restrict__ out) {
+  const int i = blockIdx.x, which = blockIdx.y, lz = blockIdx.z / parts, part = blockIdx.z % parts;
+  const uint4* src = (which ? v : k) + lz * layer_vec + static_cast<long long>(ids.ids[i]) * block_vec;
+  uint4* dst = out + ((static_cast<long long>(lz) * 2 + which) * ids.n + i) * block_vec;
+  for (long long e = part * blockDim.x + threadIdx.x; e < block_vec; e += static_cast<long long>(parts) * blockDim.x)
     dst[e] = src[e];
 }
 
 __global__ void link_scatter_kernel(uint4* __restrict__ k, uint4* __restrict__ v, const __grid_constant__ IdList ids,
-                                    long long block_vec, const uint4* __restrict__ in) {
-  const int i = blockIdx.x, which = blockIdx.y;
-  uint4* dst = (which ? v : k) + static_cast<long long>(ids.ids[i]) * block_vec;
-  const uint4* src = in + (static_cast<long long>(which) * ids.n + i) * block_vec;
-  for (long long e = blockIdx.z * blockDim.x + threadIdx.x; e < block_vec; e += static_cast<long long>(gridDim.z) * blockDim.x)
+                                    long long block_vec, long long layer_vec, int parts, const uint4* __restrict__ in) {
+  const int i = blockIdx.x, which = blockIdx.y, lz = blockIdx.z / parts, part = blockIdx.z % parts;
+  uint4* dst = (which ? v : k) + lz * layer_vec + static_cast<long long>(ids.ids[i]) * block_vec;
+  const uint4* src = in + ((static_cast<long long>(lz) * 2 + which) * ids.n + i) * block_vec;
+  for (long long e = part * blockDim.x + threadIdx.x; e < block_vec; e += static_cast<long long>(parts) * blockDim.x)
     dst[e] = src[e];
 }
 
@@ -120,6 +123,27 @@ char* slot_of(void* region, const KvLink& l, uint32_t k) {
   return static_cast<char*>(region) + kControlBytes + static_cast<size_t>(k % static_cast<uint32_t>(l.n_slots)) * l.slot_bytes;
 }
 
+// How `n_layers` layers of `n` blocks each travel: whole layers per message while a layer fits a
+// slot (as many as the slot holds), else one layer as several messages of blocks. Both ends cut
+// the same way, because they were created with the same ring.
+struct LinkMsg {
+  int layer, layers, b0, m;
+};
+
+std::vector<LinkMsg> link_messages(const KvLink& l, size_t block_bytes, int layer0, int n_layers, int n) {
+  std::vector<LinkMsg> out;
+  const size_t layer_bytes = 2 * static_cast<size_t>(n) * block_bytes;
+  if (n <= kMaxIds && layer_bytes <= l.slot_bytes) {
+    const int per = static_cast<int>(std::min<size_t>(l.slot_bytes / layer_bytes, 4096));
+    for (int a = 0; a < n_layers; a += per) out.push_back({layer0 + a, std::min(per, n_layers - a), 0, n});
+    return out;
+  }
+  const int per_msg = static_cast<int>(std::min<size_t>(kMaxIds, l.slot_bytes / (2 * block_bytes)));
+  for (int a = 0; a < n_layers; ++a)
+    for (int b0 = 0; b0 < n; b0 += per_msg) out.push_back({layer0 + a, 1, b0, std::min(per_msg, n - b0)});
+  return out;
+}
+
 bool sm_copy() {  // RB200_KV_LINK=sm: the gather kernel stores straight into the peer's slot (no copy engine)
   static const bool on = [] {
     const char* e = std::getenv("RB200_KV_LINK");
@@ -131,7 +155,13 @@ bool sm_copy() {  // RB200_KV_LINK=sm: the gather kernel stores straight into th
 }  // namespace
 
 KvLink::~KvLink() {
+  if (wedged) {  // a stream of this link never came back: nothing here may wait for the device
+    region.p = nullptr;
+    region.bytes = 0;
+    return;
+  }
   if (peer && peer_is_ipc) cudaIpcCloseMemHandle(peer);
+  if (release_stream) cudaStreamDestroy(release_stream);
   for (cudaStream_t s : streams)
     if (s) cudaStreamDestroy(s);
   for (cudaEvent_t e : gathered)
@@ -154,6 +184,9 @@ int Backend::kv_link_create(int n_slots, size_t slot_bytes, void* handle_out) {
   l->region = DeviceBuf(kControlBytes + static_cast<size_t>(n_slots) * slot_bytes);
   RB_CUDA(cudaMemset(l->region.p, 0, kControlBytes));
   for (cudaStream_t& s : l->streams) RB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  RB_CUDA(cudaStreamCreateWithFlags(&l->release_stream, cudaStreamNonBlocking));
+  l->release_words.ensure(kControlBytes);
+  for (size_t i = 0; i < kControlBytes / 4; ++i) l->release_words.as<uint32_t>()[i] = 0x7fffffffu;  // satisfies every >= wait on this end
   for (cudaEvent_t& e : l->gathered) RB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   LinkHandle h{};
   h.magic = kLinkMagic;
@@ -221,46 +254,50 @@ void Backend::kv_link_close(int link) {
   links_[link].reset();
 }
 
-void Backend::kv_link_send_layer(int link, int layer, const int32_t* blocks, int n) {
+void Backend::kv_link_send_layers(int link, int layer0, int n_layers, const int32_t* blocks, int n) {
   set_device();
-  check_layer(layer);
+  RB_REQUIRE(n_layers >= 1, "kv_link_send_layers: no layers");
+  check_layer(layer0);
+  check_layer(layer0 + n_layers - 1);
   check_blocks(blocks, n);
   if (n == 0) return;
   std::lock_guard<std::mutex> lock(copy_mu_);
   KvLink& l = link_of(link);
-  RB_REQUIRE(l.peer != nullptr, "kv_link_send_layer: the link is not connected");
+  RB_REQUIRE(l.peer != nullptr, "kv_link_send_layers: the link is not connected");
   if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
   const size_t bb = kv_block_bytes();
-  const int per_msg = static_cast<int>(std::min<size_t>(kMaxIds, l.slot_bytes / (2 * bb)));
   const long long vec = static_cast<long long>(bb / 16);
-  const size_t off = static_cast<size_t>(layer) * layer_elems();
-  // The gather must see this layer's appends of the latest forward pass: the streams this call
-  // uses wait for the layer's event, unless it has completed already.
-  const bool layer_pending = cudaEventQuery(layer_done_[layer]) != cudaSuccess;
-  cudaGetLastError();
-  bool waited[2] = {false, false};
-  for (int b0 = 0; b0 < n; b0 += per_msg) {
-    const int m = std::min(per_msg, n - b0);
+  const int parts = static_cast<int>(std::max<long long>(1, std::min<long long>(8, vec / 256)));
+  // The gather must see these layers' appends of the latest forward pass: a stream this call
+  // uses waits for the event of the last layer of its message, unless that has completed already
+  // (the layers of a pass complete in order).
+  int waited_for[2] = {-1, -1};
+  for (const LinkMsg& msg : link_messages(l, bb, layer0, n_layers, n)) {
     const uint32_t k = l.sent++;
     cudaStream_t st = l.streams[k & 1];
-    if (layer_pending && !waited[k & 1]) {
-      RB_CUDA(cudaStreamWaitEvent(st, layer_done_[layer], 0));
-      waited[k & 1] = true;
+    const int last = msg.layer + msg.layers - 1;
+    if (waited_for[k & 1] < last) {
+      const bool pending = cudaEventQuery(layer_done_[last]) != cudaSuccess;
+      cudaGetLastError();
+      if (pending) RB_CUDA(cudaStreamWaitEvent(st, layer_done_[last], 0));
+      waited_for[k & 1] = last;
     }
     if (k >= static_cast<uint32_t>(l.n_slots)) stream_wait_geq(st, ack_of(l.region.p, l, k), k - l.n_slots + 1);
     IdList ids;
-    ids.n = m;
-    std::memcpy(ids.ids, blocks + b0, static_cast<size_t>(m) * 4);
-    const size_t bytes = 2 * static_cast<size_t>(m) * bb;
+    ids.n = msg.m;
+    std::memcpy(ids.ids, blocks + msg.b0, static_cast<size_t>(msg.m) * 4);
+    const size_t bytes = 2 * static_cast<size_t>(msg.m) * bb * msg.layers;
+    const size_t off = static_cast<size_t>(msg.layer) * layer_elems();
     char* mine = slot_of(l.region.p, l, k);
     char* theirs = slot_of(l.peer, l, k);
-    dim3 grid(m, 2, static_cast<unsigned>(std::max<long long>(1, std::min<long long>(8, vec / 256))));
+    dim3 grid(msg.m, 2, static_cast<unsigned>(parts * msg.layers));
     // RB200_KV_LINK=sm: the gather stores straight into the peer's slot (measured about 10 % faster
     // back to back, but its CTAs then hold SMs for the whole NVLink transfer); default: copy engine.
     // Folding the signal into that kernel (last CTA done stores the counter) measured slower: every
     // thread then pays a system-wide fence behind its peer stores.
     count_launch(2);
     link_gather_kernel<<<grid, 256, 0, st>>>(kc_.as<uint4>() + off / 8, vc_.as<uint4>() + off / 8, ids, vec,
+                                             static_cast<long long>(layer_elems() / 8), parts,
                                              reinterpret_cast<uint4*>(sm_copy() ? theirs : mine));
     RB_CUDA(cudaEventRecord(l.gathered[k & 1], st));  // from here on the message no longer reads the pages
     if (!sm_copy()) RB_CUDA(cudaMemcpyAsync(theirs, mine, bytes, cudaMemcpyDefault, st));  // peer copy, by address
@@ -269,49 +306,51 @@ void Backend::kv_link_send_layer(int link, int layer, const int32_t* blocks, int
   }
 }
 
-void Backend::kv_link_recv_layer(int link, int layer, const int32_t* blocks, int n) {
+void Backend::kv_link_recv_layers(int link, int layer0, int n_layers, const int32_t* blocks, int n) {
   set_device();
-  check_layer(layer);
+  RB_REQUIRE(n_layers >= 1, "kv_link_recv_layers: no layers");
+  check_layer(layer0);
+  check_layer(layer0 + n_layers - 1);
   check_blocks(blocks, n);
   if (n == 0) return;
   std::lock_guard<std::mutex> lock(copy_mu_);
   KvLink& l = link_of(link);
-  RB_REQUIRE(l.peer != nullptr, "kv_link_recv_layer: the link is not connected");
+  RB_REQUIRE(l.peer != nullptr, "kv_link_recv_layers: the link is not connected");
   if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
   const size_t bb = kv_block_bytes();
-  const int per_msg = static_cast<int>(std::min<size_t>(kMaxIds, l.slot_bytes / (2 * bb)));
   const long long vec = static_cast<long long>(bb / 16);
-  const size_t off = static_cast<size_t>(layer) * layer_elems();
-  for (int b0 = 0; b0 < n; b0 += per_msg) {
-    const int m = std::min(per_msg, n - b0);
+  const int parts = static_cast<int>(std::max<long long>(1, std::min<long long>(8, vec / 256)));
+  for (const LinkMsg& msg : link_messages(l, bb, layer0, n_layers, n)) {
     const uint32_t k = l.received++;
     cudaStream_t st = l.streams[k & 1];
     stream_wait_geq(st, arrived_of(l.region.p, l, k), k + 1);
     IdList ids;
-    ids.n = m;
-    std::memcpy(ids.ids, blocks + b0, static_cast<size_t>(m) * 4);
-    dim3 grid(m, 2, static_cast<unsigned>(std::max<long long>(1, std::min<long long>(8, vec / 256))));
+    ids.n = msg.m;
+    std::memcpy(ids.ids, blocks + msg.b0, static_cast<size_t>(msg.m) * 4);
+    const size_t off = static_cast<size_t>(msg.layer) * layer_elems();
+    dim3 grid(msg.m, 2, static_cast<unsigned>(parts * msg.layers));
     count_launch(2);
     link_scatter_kernel<<<grid, 256, 0, st>>>(kc_.as<uint4>() + off / 8, vc_.as<uint4>() + off / 8, ids, vec,
+                                              static_cast<long long>(layer_elems() / 8), parts,
                                               reinterpret_cast<const uint4*>(slot_of(l.region.p, l, k)));
     link_signal_kernel<<<1, 1, 0, st>>>(ack_of(l.peer, l, k), k + 1);
     RB_CUDA(cudaGetLastError());
   }
 }
 
-// Consumes the messages of a layer of n blocks the peer has sent (or will send) without landing
-// them anywhere: the receiver had no room for the request and drops the frame
+// Consumes the messages of n_layers layers of n blocks the peer has sent (or will send) without
+// landing them anywhere: the receiver had no room for the request and drops the frame
 // (engine/src/kv_transfer.cpp:284-288), but the ring must move on.
-void Backend::kv_link_skip_layer(int link, int n) {
+void Backend::kv_link_skip_layers(int link, int n_layers, int n) {
   set_device();
-  RB_REQUIRE(n >= 0, "kv_link_skip_layer: negative block count");
+  RB_REQUIRE(n >= 0 && n_layers >= 1, "kv_link_skip_layers: bad counts");
   if (n == 0) return;
   std::lock_guard<std::mutex> lock(copy_mu_);
   KvLink& l = link_of(link);
-  RB_REQUIRE(l.peer != nullptr, "kv_link_skip_layer: the link is not connected");
+  RB_REQUIRE(l.peer != nullptr, "kv_link_skip_layers: the link is not connected");
   if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
-  const int per_msg = static_cast<int>(std::min<size_t>(kMaxIds, l.slot_bytes / (2 * kv_block_bytes())));
-  for (int b0 = 0; b0 < n; b0 += per_msg) {
+  const size_t n_msgs = link_messages(l, kv_block_bytes(), 0, n_layers, n).size();
+  for (size_t i = 0; i < n_msgs; ++i) {
     const uint32_t k = l.received++;
     cudaStream_t st = l.streams[k & 1];
     stream_wait_geq(st, arrived_of(l.region.p, l, k), k + 1);
@@ -391,14 +430,26 @@ bool Backend::links_idle() {
 }
 
 void Backend::links_release() {
+  // Every wait here is bounded: the counters are written on a stream that carries nothing else,
+  // and the link's streams are polled, not synchronised. A link still busy two seconds later
+  // (its streams sit behind work this end cannot release) is abandoned: marked wedged, its
+  // region never freed, and the process stops making device-wide synchronising calls.
   for (auto& l : links_) {
-    if (!l) continue;
+    if (!l || l->wedged) continue;
     if (cudaStreamQuery(l->streams[0]) != cudaErrorNotReady && cudaStreamQuery(l->streams[1]) != cudaErrorNotReady) continue;
     l->broken = true;
-    uint32_t big[128];
-    for (uint32_t& w : big) w = 0x7fffffffu;  // satisfies every pending >= wait on this end (arrived and ack)
-    cudaMemcpy(l->region.p, big, sizeof(big), cudaMemcpyHostToDevice);
-    for (cudaStream_t s : l->streams) cudaStreamSynchronize(s);
+    cudaMemcpyAsync(l->region.p, l->release_words.p, kControlBytes, cudaMemcpyHostToDevice, l->release_stream);
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(2);
+    bool busy = true;
+    while (busy && std::chrono::steady_clock::now() < deadline) {
+      busy = cudaStreamQuery(l->streams[0]) == cudaErrorNotReady || cudaStreamQuery(l->streams[1]) == cudaErrorNotReady ||
+             cudaStreamQuery(l->release_stream) == cudaErrorNotReady;
+      if (busy) std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+    if (busy) {
+      l->wedged = true;
+      g_device_wedged.store(true);
+    }
   }
   cudaGetLastError();
 }

@@ -26,7 +26,10 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <mutex>
 #include <string>
+#include <unordered_map>
+#include <utility>
 
 #include "i8_digits.cuh"
 #include "kernels.h"
@@ -170,7 +173,7 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   unsigned char* gen_base = smem_dyn + (base - smem_u32(smem_dyn));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // `rows` (a multiple of 8, at most 128) weight rows per CTA: the host shrinks the tile so that
+  // `rows` (at most 128) weight rows per CTA: the host shrinks the tile so that
   // the grid fills the SMs evenly; the MMA still spans 128 lanes and the rest is ignored.
   const int m0 = blockIdx.x * rows, tok0 = blockIdx.y * BN;
   const uint32_t stage_tx = static_cast<uint32_t>(rows) * kBlockKB + (FUSED ? 0 : S::kBBytes);
@@ -446,19 +449,48 @@ void launch_i8_t(const WeightView& W, const int8_t* digits, const float* tscale,
       capacity[sp] = n;
     }
   }
+  // The search is per (N, K, token tiles) and remembered: it runs once per matrix shape.
+  static std::mutex plan_mu;
+  static std::unordered_map<uint64_t, std::pair<int, int>> plans;
+  const uint64_t key = (static_cast<uint64_t>(W.N) << 36) ^ (static_cast<uint64_t>(W.K) << 12) ^ static_cast<uint64_t>(ttiles);
   int rows = kTileM, splits = 1;
-  double best = 1e30;
-  for (int r = kTileM; r >= 64; r -= 8) {
-    for (int sp = 1; sp <= 8; ++sp) {
-      if (sp > 1 && (nk / sp < 4 || static_cast<size_t>(BN) * kTileM * 4 > static_cast<size_t>(S::kStages) * S::kStageBytes)) break;
-      const long long clusters = static_cast<long long>(div_up(W.N, r)) * ttiles;
-      const double cost = static_cast<double>(div_up(clusters, static_cast<long long>(capacity[sp]))) *
-                          (static_cast<double>(r) * W.K / sp + 48.0 * 1024 + (sp > 1 ? 8.0 * 1024 : 0.0));
-      if (cost < best - 1e-9) {
-        best = cost;
-        rows = r;
-        splits = sp;
+  {
+    std::lock_guard<std::mutex> lock(plan_mu);
+    auto it = plans.find(key);
+    if (it == plans.end()) {
+      // Any row count works (the TMA box is `rows` high, the MMA spans 128 lanes and the epilogue
+      // ignores the rest), but a stage of the ring holds `rows` x 128 bytes, and with much fewer
+      // than 128 rows a CTA no longer has enough bytes in flight: 56-row tiles in 74 clusters of
+      // two measured 20.7 us on the 14336 -> 4096 matrix against 13.3 us for 128-row tiles in 32
+      // clusters of four, 42-row tiles 9.4 against 8.4 us on 4096 -> 6144; 97-row tiles (148 CTAs
+      // instead of 138 of 104 rows) gain 3 % on 4096 -> 14336. Hence: any count from 96 up,
+      // multiples of 8 below. RB200_I8_ROW_STEP=8: multiples of 8 only.
+      static const int step = [] {
+        const char* e = std::getenv("RB200_I8_ROW_STEP");
+        return e && std::atoi(e) == 8 ? 8 : 1;
+      }();
+      double best = 1e30;
+      for (int r = kTileM; r >= 64; --r) {
+        if (r % 8 != 0 && (step == 8 || r < 96)) continue;
+        for (int sp = 1; sp <= 8; ++sp) {
+          if (sp > 1 && (nk / sp < 4 || static_cast<size_t>(BN) * kTileM * 4 > static_cast<size_t>(S::kStages) * S::kStageBytes)) break;
+          const long long clusters = static_cast<long long>(div_up(W.N, r)) * ttiles;
+          // below about 1.25 x BN rows a CTA is bound by its MMAs (3 x BN columns per k block
+          // whatever the row count), not by its weight bytes
+          const double eff_rows = std::max<double>(r, 1.25 * BN);
+          const double cost = static_cast<double>(div_up(clusters, static_cast<long long>(capacity[sp]))) *
+                              (eff_rows * W.K / sp + 48.0 * 1024 + (sp > 1 ? 8.0 * 1024 : 0.0));
+          if (cost < best - 1e-9) {
+            best = cost;
+            rows = r;
+            splits = sp;
+          }
+        }
       }
+      plans.emplace(key, std::make_pair(rows, splits));
+    } else {
+      rows = it->second.first;
+      splits = it->second.second;
     }
   }
   static const int forced = [] {

@@ -12,6 +12,17 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 
 
+def pytest_collection_modifyitems(config, items):
+    # No test may occupy a GPU box for ever: with pytest-timeout present, a test that is still
+    # running after 15 minutes (the slowest ones take two or three) ends the run with the stacks
+    # of all threads (method "thread": a call stuck inside a C library never returns to Python).
+    if not config.pluginmanager.hasplugin("timeout"):
+        return
+    for item in items:
+        if item.get_closest_marker("timeout") is None:
+            item.add_marker(pytest.mark.timeout(900, method="thread"))
+
+
 @pytest.fixture(scope="session")
 def golden_dir():
     return os.path.join(ROOT, "tests", "golden")

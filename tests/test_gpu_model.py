@@ -170,6 +170,60 @@ def test_kv_blocks_moved_to_another_backend_decode_identically(mk):
         tok = argmax_lowest(ra)
 
 
+@pytest.mark.parametrize("layers_per_slot", [1, 2, 5])
+def test_kv_link_moves_layer_ranges_between_two_backends(mk, layers_per_slot):
+    # The prefill -> decode hop of a finished request over a K/V link joining two backends of this
+    # process: whole layers per message, as many as a slot holds (a 5-layer model: 5, 3 and 1
+    # messages); the received pages equal the sender's bit for bit, a dropped request moves the
+    # ring on, and both backends decode the same tokens afterwards. Both ends share one GPU and one
+    # host thread here, so the sender's work is always enqueued first and never has to wait for a
+    # slot (8 slots, a host wait after every request): streams of one device may share a hardware
+    # queue, and a wait enqueued ahead of the work that satisfies it could then block that work.
+    # Slot reuse behind acknowledgements runs between processes in test_multi_gpu.py.
+    cfg = ModelConfig(hidden=128, intermediate=200, layers=5, heads=4, kv_heads=2, head_dim=32, vocab=260)
+    w = synthetic(cfg, 31)
+    a, b = mk(w, 48, 16), mk(w, 48, 16)
+    rng = np.random.Generator(np.random.PCG64(4))
+    prompt = rng.integers(0, cfg.vocab, 150).tolist()
+    ta, tb = list(range(2, 12)), list(range(30, 40))[::-1]
+    la = a.forward(ForwardBatch([SeqChunk(prompt, 0, ta)]))
+    slot = layers_per_slot * 2 * len(ta) * a.kv_block_bytes()
+    (link_a, _), (link_b, _) = a.kv_link_create(8, slot), b.kv_link_create(8, slot)
+    a.kv_link_connect_local(link_a, b, link_b)
+
+    def settle():
+        a.kv_link_wait(link_a, 20000)
+        b.kv_link_wait(link_b, 20000)
+
+    # a request the receiver drops, then the one it lands
+    a.kv_link_send_layers(link_a, 0, cfg.layers, ta)
+    settle()
+    b.kv_link_skip_layers(link_b, cfg.layers, len(ta))
+    settle()
+    a.kv_link_send_layers(link_a, 0, cfg.layers, ta)
+    settle()
+    b.kv_link_recv_layers(link_b, 0, cfg.layers, tb)
+    settle()
+    for layer in range(cfg.layers):
+        assert np.array_equal(b.read_kv_layer(layer, tb), a.read_kv_layer(layer, ta))
+    # a range in the middle, into other blocks
+    tc = list(range(12, 22))
+    a.kv_link_send_layers(link_a, 1, 3, ta)
+    settle()
+    b.kv_link_recv_layers(link_b, 1, 3, tc)
+    settle()
+    for layer in (1, 2, 3):
+        assert np.array_equal(b.read_kv_layer(layer, tc), a.read_kv_layer(layer, ta))
+    tok = argmax_lowest(la[0])
+    for s in range(4):
+        ra = a.forward(ForwardBatch([SeqChunk([tok], 150 + s, ta)]))[0]
+        rb = b.forward(ForwardBatch([SeqChunk([tok], 150 + s, tb)]))[0]
+        assert np.array_equal(ra, rb)
+        tok = argmax_lowest(ra)
+    a.kv_link_close(link_a)
+    b.kv_link_close(link_b)
+
+
 def test_kv_pages_match_cpu_pages_rounded_to_fp16(mk):
     cfg = WIDE_CONFIGS["d128_g4"]
     w = synthetic(cfg, 2)

@@ -186,7 +186,7 @@ def _link_worker(rank, world, port, q):
         torch.cuda.set_device(rank)
         cfg = WIDE_CONFIGS["d128_g4"]
         w = synthetic(cfg, 12)
-        be = make_cuda_backend(w, 64, 16, device=rank, max_batch_tokens=512)
+        be = make_cuda_backend(w, 128, 16, device=rank, max_batch_tokens=512)
         # a ring of 3 slots of 4 blocks each: the 19-block layers travel as 5 messages, and the
         # 2 layers x 5 messages wrap the ring, so slot reuse behind the receiver's acknowledgements runs
         slot = 4 * 2 * be.kv_block_bytes()
@@ -220,6 +220,23 @@ def _link_worker(rank, world, port, q):
             tok = int(np.argmax(row))
             toks.append(tok)
         pages = [be.read_kv_layer(l, table[:19]) for l in range(cfg.layers)]
+        # the same request once more as a finished one: both layers in one message over a second
+        # link whose slots hold two layers, into blocks nothing has written
+        link2, handle2 = be.kv_link_create(2, 2 * 19 * 2 * be.kv_block_bytes())
+        handles2 = [None, None]
+        dist.all_gather_object(handles2, handle2)
+        be.kv_link_connect(link2, handles2[1 - rank])
+        if rank == 0:
+            be.kv_link_send_layers(link2, 0, cfg.layers, src_blocks)
+            be.kv_hop_sync(20000)
+            pages2 = pages
+        else:
+            far = list(range(100, 119))
+            be.kv_link_recv_layers(link2, 0, cfg.layers, far)
+            be.kv_hop_sync(20000)
+            pages2 = [be.read_kv_layer(l, far) for l in range(cfg.layers)]
+        dist.barrier()
+        be.kv_link_close(link2)
         # A receive nothing sends: the wait must run out on the host, the link is then refused,
         # and the backend goes on working (no GPU wait is left spinning).
         timed_out = refused = False
@@ -235,7 +252,8 @@ def _link_worker(rank, world, port, q):
                 refused = "broken" in str(e)
         after = be.forward(ForwardBatch([SeqChunk([toks[-1]], 306, table)]))[0]
         dist.barrier()
-        q.put((rank, toks, np.stack(rows), [p.tobytes() for p in pages], timed_out, refused, bool(np.isfinite(after).all())))
+        q.put((rank, toks, np.stack(rows), [p.tobytes() for p in pages], timed_out, refused, bool(np.isfinite(after).all()),
+               [p.tobytes() for p in pages2]))
     finally:
         dist.destroy_process_group()
 
@@ -264,3 +282,4 @@ def test_kv_link_hop_equals_colocated_decode_and_its_waits_are_bounded():
     assert got[0][2] == got[1][2]                    # the pages that crossed NVLink are byte-identical
     assert got[1][3] and got[1][4]                   # the unmatched receive timed out; the link is then refused
     assert got[0][5] and got[1][5]                   # both backends still compute
+    assert got[0][6] == got[1][6]                    # the layer-range message landed the same bytes
