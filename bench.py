@@ -108,6 +108,9 @@ def prefill_pass(be, fb, cfg, bs, out) -> dict:
             "timing": "host clock around the forward calls, best of 2 after a warm-up"}
 
 
+RANGE_PROMPTS = 8  # finished prompts sent back to back in the layer-range reading of the K/V hop
+
+
 def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
     """The disaggregated variant: GPU 0 prefills 2048-token prompts and streams every layer's K/V
     pages over NVLink to the decode GPUs (ranks 1 .. N-1, prompts dealt round robin), which land
@@ -135,7 +138,9 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
     hop_bytes = layer_bytes * cfg.layers
 
     # one link per decode GPU: a ring of 4 slots, each as large as a quarter of a whole prompt's
-    # layers (a streamed layer takes one slot; a finished prompt travels as four messages)
+    # layers (a streamed layer takes one slot; a finished prompt travels as four messages: with 4
+    # layers per message one prompt measured 560 GB/s and eight back to back 599, with 16 layers
+    # 537 and 673)
     group = max(1, cfg.layers // 4)
     slot = (group * layer_bytes + 255) // 256 * 256
     links = {}
@@ -215,7 +220,28 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
         for p in range(n_prompts):
             prefill(p, None)
     run_plain = lambda: [prefill(p, None) for p in range(n_prompts)] if rank == 0 else None
-    plain = best_of(run_plain)
+
+    def once(fn):
+        sync_all()
+        t0 = time.perf_counter()
+        fn()
+        return mx(time.perf_counter() - t0)
+
+    def streamed_against_plain(fn, rounds=3):
+        """What streaming adds to the prefill: every streamed run is timed between two plain runs
+        (the SM clock under the power cap drifts over a run of this length, and the difference of
+        two numbers taken minutes apart would measure that drift); the median of the rounds."""
+        once(fn)
+        s_all, p_all, d_all = [], [], []
+        for _ in range(rounds):
+            p0, s, p1 = once(run_plain), once(fn), once(run_plain)
+            s_all.append(s)
+            p_all += [p0, p1]
+            d_all.append(s - 0.5 * (p0 + p1))
+        return float(np.median(s_all)), p_all, float(np.median(d_all))
+
+    best_of(run_plain)
+    plains = []
     enqueue_ms = {}
     for transport in ("nccl", "link"):
         def pair():  # one prompt, all layers back to back, GPU 0 -> GPU 1
@@ -264,7 +290,18 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
                 be.kv_link_recv_layers(links[0], 0, cfg.layers, tables[rank - 1])
             be.kv_hop_sync(30000)
 
-        t_pair, t_fan, t_str = best_of(pair), best_of(fan), best_of(streamed)
+        def pair_ranges_stream():  # RANGE_PROMPTS finished prompts back to back over one link (the ring's acknowledgements pace the sender)
+            if rank == 0:
+                for _ in range(RANGE_PROMPTS):
+                    be.kv_link_send_layers(links[1], 0, cfg.layers, tables[0])
+            elif rank == 1:
+                for _ in range(RANGE_PROMPTS):
+                    be.kv_link_recv_layers(links[0], 0, cfg.layers, tables[0])
+            be.kv_hop_sync(30000)
+
+        t_pair, t_fan = best_of(pair), best_of(fan)
+        t_str, p_all, t_exposed = streamed_against_plain(streamed)
+        plains += p_all
         # byte compare of what arrived: three layers of the last prompt each decode GPU received
         digests = []
         for p in range(n_prompts - n_dec, n_prompts):
@@ -281,6 +318,7 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
                           "pair_host_enqueue_ms": enqueue_ms.get(transport),
                           "fan_out_ms": t_fan * 1e3, "fan_out_gbs_from_gpu0": hop_bytes * n_dec / t_fan / 1e9,
                           "streamed_prefill_ms_per_prompt": t_str / n_prompts * 1e3,
+                          "exposed_ms_per_prompt": t_exposed / n_prompts * 1e3,
                           "received_pages_identical": bool(identical)}
         if transport == "link":
             # after the digests above; the receivers first wipe the pages that are compared below, so
@@ -288,9 +326,12 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
             if rank > 0:
                 for layer in (0, cfg.layers // 2, cfg.layers - 1):
                     be.write_kv_layer(layer, tables[rank - 1], np.zeros_like(be.read_kv_layer(layer, tables[rank - 1])))
-            t_pr, t_fr = best_of(pair_ranges, 5), best_of(fan_ranges, 5)
+            t_pr, t_fr, t_ps = best_of(pair_ranges, 5), best_of(fan_ranges, 5), best_of(pair_ranges_stream, 3)
             res["link"].update({"layer_ranges_per_message": group, "pair_ranges_ms": t_pr * 1e3,
                                 "pair_ranges_gbs": hop_bytes / t_pr / 1e9,
+                                "pair_ranges_prompts_back_to_back": RANGE_PROMPTS,
+                                "pair_ranges_back_to_back_ms_per_prompt": t_ps / RANGE_PROMPTS * 1e3,
+                                "pair_ranges_back_to_back_gbs": hop_bytes * RANGE_PROMPTS / t_ps / 1e9,
                                 "pair_ranges_host_enqueue_ms": enqueue_ms.get("ranges"),
                                 "fan_out_ranges_ms": t_fr * 1e3,
                                 "fan_out_ranges_gbs_from_gpu0": hop_bytes * n_dec / t_fr / 1e9})
@@ -305,16 +346,16 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
             dist.all_gather_object(allg, digests)
             want = dict(allg[0])
             res["link"]["ranges_received_pages_identical"] = bool(all(want[d] == x for r in range(1, world) for d, x in allg[r]))
-    # the prefill alone once more, after the streamed runs: the SM clock under the power cap drifts
-    # over a run of this length, and the exposed time is a difference of two such numbers
-    plain = min(plain, best_of(run_plain))
-    res["prefill_ms_per_prompt"] = plain / n_prompts * 1e3
-    for transport in ("nccl", "link"):
-        res[transport]["exposed_ms_per_prompt"] = res[transport]["streamed_prefill_ms_per_prompt"] - res["prefill_ms_per_prompt"]
-    # a finished prompt handed over as layer ranges (the hop alone); layer by layer: link.pair_gbs
-    res["gbs_per_pair"] = res["link"]["pair_ranges_gbs"]
-    res["transport_note"] = ("nccl: page gather -> ncclSend / ncclRecv -> scatter on one copy stream; link: gather -> copy-engine "
-                             "peer copy into the receiver's ring -> scatter, ordered by two counters (no SM held during the copy)")
+    res["prefill_ms_per_prompt"] = float(np.median(plains)) / n_prompts * 1e3
+    res["exposed_note"] = ("exposed_ms_per_prompt: median over 3 rounds of (streamed run - mean of the plain prefill runs "
+                           "directly before and after it)")
+    # finished prompts handed over as layer ranges, back to back over one link (the hop alone, host
+    # clock from the first enqueue to the last page landed); one prompt: link.pair_ranges_gbs; layer
+    # by layer: link.pair_gbs
+    res["gbs_per_pair"] = res["link"]["pair_ranges_back_to_back_gbs"]
+    res["transport_note"] = ("nccl: page gather -> ncclSend / ncclRecv -> scatter on one copy stream; link: one kernel gathers the pages "
+                             "straight into the receiver's ring with plain peer stores (RB200_KV_LINK=ce: gather + copy-engine peer "
+                             "copy) -> scatter, ordered by two counters")
     for l in links.values():
         be.kv_link_close(l)
     be.nccl_finalize()

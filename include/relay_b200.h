@@ -272,7 +272,13 @@ int rb200_kv_link_create(rb200_backend* b, int n_slots, size_t slot_bytes, void*
 /* Maps the other end's region; both ends must have been created with the same ring. */
 int rb200_kv_link_connect(rb200_backend* b, int link, const void* peer_handle);
 /* The same for two backends of one process (a process cannot open its own IPC handle): each end
- * takes the other's region by address; backends on different devices get peer access first. */
+ * takes the other's region by address; backends on different devices get peer access first.
+ * A link orders its streams by counters the CUDA scheduler does not see, so its two ends belong
+ * on two devices: on ONE device (tests) streams may share a hardware queue, and a wait enqueued
+ * ahead of the work that satisfies it then holds that work back until the host deadline of
+ * rb200_kv_link_wait / rb200_kv_hop_sync breaks the link. There, enqueue a message's send before
+ * its receive and keep fewer messages in flight than the ring has slots, or give every stream its
+ * own queue (CUDA_DEVICE_MAX_CONNECTIONS=32). */
 int rb200_kv_link_connect_local(rb200_backend* a, int link_a, rb200_backend* b, int link_b);
 int rb200_kv_link_send_layer(rb200_backend* b, int link, int layer, const int32_t* blocks, int n);
 int rb200_kv_link_recv_layer(rb200_backend* b, int link, int layer, const int32_t* blocks, int n);

@@ -73,8 +73,11 @@ struct KvLink {
   DeviceBuf region;
   void* peer = nullptr;
   bool peer_is_ipc = false;  // mapped with cudaIpcOpenMemHandle (another process) rather than taken by address
-  cudaStream_t streams[2] = {nullptr, nullptr};  // consecutive messages alternate between them
-  cudaEvent_t gathered[2] = {nullptr, nullptr};  // behind the latest gather on each stream
+  static constexpr int kStreams = 2;       // consecutive messages alternate between them (four measured no faster)
+  cudaStream_t streams[kStreams] = {};
+  cudaEvent_t gathered[kStreams] = {};     // behind the latest gather on each stream
+  // cudaErrorNotReady while any stream (or, gathers_only, any gather) still has work; errors pass through
+  cudaError_t busy(bool gathers_only = false) const;
   cudaStream_t release_stream = nullptr;          // carries nothing but the host's release of this end's counters
   PinnedBuf release_words;                        // what that release writes (filled when the link is created)
   uint32_t sent = 0, received = 0;  // messages enqueued so far in each direction

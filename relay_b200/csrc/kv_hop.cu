@@ -209,7 +209,8 @@ void Backend::recv_kv_layer(int peer, int layer, const int32_t* blocks, int n) {
 void Backend::kv_hop_sync(int timeout_ms) {
   set_device();
   if (timeout_ms <= 0) timeout_ms = kDefaultSyncTimeoutMs;  // never wait without a limit
-  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  const auto started = std::chrono::steady_clock::now();
+  const auto deadline = started + std::chrono::milliseconds(timeout_ms);
   for (;;) {
     const cudaError_t q = cudaStreamQuery(copy_stream_);
     if (q == cudaSuccess) {
@@ -239,7 +240,8 @@ void Backend::kv_hop_sync(int timeout_ms) {
       cudaGetLastError();
       fail(RB200_ERR_RUNTIME, "kv_hop_sync: timed out; communicator aborted");
     }
-    std::this_thread::sleep_for(std::chrono::microseconds(50));
+    // a hop of a prompt or two ends within a millisecond or two: poll without sleeping that long
+    if (std::chrono::steady_clock::now() - started > std::chrono::milliseconds(2)) std::this_thread::sleep_for(std::chrono::microseconds(50));
   }
 }
 

@@ -2,8 +2,8 @@
 // the way. It carries the same payload as the NCCL hop of kv_hop.cu and the Layer frames of
 // relay's transfer engine (engine/include/relay/kv_transfer.h:14-18: all K blocks of a layer,
 // then all V blocks, request-relative order; sender engine/src/kv_transfer.cpp:107-128,
-// receiver :269-301), but moves it with the copy engines and orders it with two counters, so
-// that no SM is held while the bytes cross NVLink and no per-operation library latency is paid.
+// receiver :269-301), but moves it with one kernel of plain peer stores (or, optionally, the
+// copy engines) and orders it with two counters, so that no per-operation library latency is paid.
 //
 // Each end of a link owns one device region: a ring of `n_slots` landing slots and, per slot,
 // two 32-bit counters. The ends exchange CUDA IPC handles of their regions out of band (the host
@@ -11,20 +11,26 @@
 //
 //   sender, message k (slot s = k % n_slots):
 //                        wait until its own ack[s] says the message that last used s was scattered;
-//                        gather the layer's pages into its own slot (one kernel, HBM speed);
-//                        copy the slot into the peer's slot (copy engine over NVLink);
+//                        gather the pages straight into the PEER's slot (one kernel whose 16-byte
+//                        stores cross NVLink: the pages are read once and nothing is staged);
 //                        store k + 1 into the peer's arrived[s] (one-thread kernel);
 //   receiver, message k: stream-wait until its own arrived[s] reaches k + 1;
 //                        scatter its slot into the pages of its own block ids;
 //                        store k + 1 into the peer's ack[s].
-// Consecutive messages alternate between two streams on each end, so the gather of message
-// k + 1 runs while the copy engine moves message k; the per-slot counters keep that safe.
+// Consecutive messages alternate between two streams on each end; the per-slot counters keep
+// that safe whatever stream a message is on. RB200_KV_LINK=ce gathers into the sender's own slot
+// and lets a copy engine move the slot instead (no SM busy during the transfer): a copy-engine
+// peer copy has a fixed cost of about 20 us on this hardware (back-to-back copies of 8 / 32 /
+// 256 MB run at 270 / 515 / 734 GB/s) that neither more streams (four measured no faster than
+// two) nor the gather of the next message hide, so that path measured 360 GB/s layer by layer
+// and 500 GB/s with 134 MB messages against 408 and 673 GB/s for the peer stores, at the same
+// cost to a prefill running beside it (0.4 ms per 2048-token prompt either way).
 //
 // The waits are stream memory operations (cuStreamWaitValue32) on the waiting GPU's own memory:
 // no kernel spins, and a wait the peer never satisfies is released from the host when
 // rb200_kv_hop_sync's deadline runs out (the link is then marked broken). Only plain stores from
-// this library's own one-thread kernels and copy-engine copies touch the peer's memory; no TMA
-// and no library kernel ever sees a peer pointer. Messages pair up by order on the link, which
+// this library's own kernels and copy-engine copies touch the peer's memory; no TMA and no
+// library kernel ever sees a peer pointer. Messages pair up by order on the link, which
 // the host connection's ordered frames already guarantee.
 #include <cuda.h>
 
@@ -64,13 +70,26 @@ struct IdList {
 // [K of each block][V of each block]; the block ids ride in the kernel's parameters, so no upload
 // precedes the launch. k and v point at the first layer of the message; grid = (blocks, 2,
 // layers x parts), `parts` CTAs sharing one block.
+// A CTA's share of one block: four 16-byte loads in flight per thread before the first store.
+__device__ __forceinline__ void copy_share(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n, int part, int parts) {
+  const long long stride = static_cast<long long>(parts) * blockDim.x;
+  long long e = static_cast<long long>(part) * blockDim.x + threadIdx.x;
+  for (; e + 3 * stride < n; e += 4 * stride) {
+    const uint4 a = src[e], b = src[e + stride], c = src[e + 2 * stride], d = src[e + 3 * stride];
+    dst[e] = a;
+    dst[e + stride] = b;
+    dst[e + 2 * stride] = c;
+    dst[e + 3 * stride] = d;
+  }
+  for (; e < n; e += stride) dst[e] = src[e];
+}
+
 __global__ void link_gather_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, const __grid_constant__ IdList ids,
                                    long long block_vec, long long layer_vec, int parts, uint4* __restrict__ out) {
   const int i = blockIdx.x, which = blockIdx.y, lz = blockIdx.z / parts, part = blockIdx.z % parts;
   const uint4* src = (which ? v : k) + lz * layer_vec + static_cast<long long>(ids.ids[i]) * block_vec;
   uint4* dst = out + ((static_cast<long long>(lz) * 2 + which) * ids.n + i) * block_vec;
-  for (long long e = part * blockDim.x + threadIdx.x; e < block_vec; e += static_cast<long long>(parts) * blockDim.x)
-    dst[e] = src[e];
+  copy_share(src, dst, block_vec, part, parts);
 }
 
 __global__ void link_scatter_kernel(uint4* __restrict__ k, uint4* __restrict__ v, const __grid_constant__ IdList ids,
@@ -78,8 +97,7 @@ __global__ void link_scatter_kernel(uint4* __restrict__ k, uint4* __restrict__ v
   const int i = blockIdx.x, which = blockIdx.y, lz = blockIdx.z / parts, part = blockIdx.z % parts;
   uint4* dst = (which ? v : k) + lz * layer_vec + static_cast<long long>(ids.ids[i]) * block_vec;
   const uint4* src = in + ((static_cast<long long>(lz) * 2 + which) * ids.n + i) * block_vec;
-  for (long long e = part * blockDim.x + threadIdx.x; e < block_vec; e += static_cast<long long>(parts) * blockDim.x)
-    dst[e] = src[e];
+  copy_share(src, dst, block_vec, part, parts);
 }
 
 // One store of `value` to a counter in the peer's region, behind everything this stream has
@@ -144,15 +162,36 @@ std::vector<LinkMsg> link_messages(const KvLink& l, size_t block_bytes, int laye
   return out;
 }
 
-bool sm_copy() {  // RB200_KV_LINK=sm: the gather kernel stores straight into the peer's slot (no copy engine)
+// CTAs sharing one block: each thread moves four 16-byte pieces where the message is large
+// enough to fill the SMs that way, fewer where it is not.
+int link_parts(long long block_vec, int n_blocks) {
+  int parts = static_cast<int>(std::max<long long>(1, std::min<long long>(8, block_vec / 1024)));
+  while (parts < 8 && static_cast<long long>(parts) * 2 * 256 <= block_vec && 2LL * n_blocks * parts < 2 * sm_count()) parts *= 2;
+  return parts;
+}
+
+bool sm_copy() {  // false with RB200_KV_LINK=ce: gather into this end's slot, then a copy-engine peer copy
   static const bool on = [] {
     const char* e = std::getenv("RB200_KV_LINK");
-    return e && std::string(e) == "sm";
+    return !(e && std::string(e) == "ce");
   }();
   return on;
 }
 
 }  // namespace
+
+cudaError_t KvLink::busy(bool gathers_only) const {
+  cudaError_t worst = cudaSuccess;
+  for (int i = 0; i < kStreams; ++i) {
+    const cudaError_t q = gathers_only ? cudaEventQuery(gathered[i]) : cudaStreamQuery(streams[i]);
+    if (q == cudaErrorNotReady) {
+      if (worst == cudaSuccess) worst = q;
+    } else if (q != cudaSuccess) {
+      worst = q;
+    }
+  }
+  return worst;
+}
 
 KvLink::~KvLink() {
   if (wedged) {  // a stream of this link never came back: nothing here may wait for the device
@@ -249,7 +288,7 @@ void Backend::kv_link_close(int link) {
   KvLink& l = link_of(link);
   // The caller has synchronised the hop (rb200_kv_hop_sync) before closing; a link that is
   // still busy here is waiting for a peer that will not come.
-  if (cudaStreamQuery(l.streams[0]) == cudaErrorNotReady || cudaStreamQuery(l.streams[1]) == cudaErrorNotReady) links_release();
+  if (l.busy() == cudaErrorNotReady) links_release();
   cudaGetLastError();
   links_[link].reset();
 }
@@ -267,20 +306,21 @@ void Backend::kv_link_send_layers(int link, int layer0, int n_layers, const int3
   if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
   const size_t bb = kv_block_bytes();
   const long long vec = static_cast<long long>(bb / 16);
-  const int parts = static_cast<int>(std::max<long long>(1, std::min<long long>(8, vec / 256)));
+  const int parts = link_parts(vec, n);
   // The gather must see these layers' appends of the latest forward pass: a stream this call
   // uses waits for the event of the last layer of its message, unless that has completed already
   // (the layers of a pass complete in order).
-  int waited_for[2] = {-1, -1};
+  int waited_for[KvLink::kStreams];
+  for (int& w : waited_for) w = -1;
   for (const LinkMsg& msg : link_messages(l, bb, layer0, n_layers, n)) {
     const uint32_t k = l.sent++;
-    cudaStream_t st = l.streams[k & 1];
+    cudaStream_t st = l.streams[k % KvLink::kStreams];
     const int last = msg.layer + msg.layers - 1;
-    if (waited_for[k & 1] < last) {
+    if (waited_for[k % KvLink::kStreams] < last) {
       const bool pending = cudaEventQuery(layer_done_[last]) != cudaSuccess;
       cudaGetLastError();
       if (pending) RB_CUDA(cudaStreamWaitEvent(st, layer_done_[last], 0));
-      waited_for[k & 1] = last;
+      waited_for[k % KvLink::kStreams] = last;
     }
     if (k >= static_cast<uint32_t>(l.n_slots)) stream_wait_geq(st, ack_of(l.region.p, l, k), k - l.n_slots + 1);
     IdList ids;
@@ -291,15 +331,13 @@ void Backend::kv_link_send_layers(int link, int layer0, int n_layers, const int3
     char* mine = slot_of(l.region.p, l, k);
     char* theirs = slot_of(l.peer, l, k);
     dim3 grid(msg.m, 2, static_cast<unsigned>(parts * msg.layers));
-    // RB200_KV_LINK=sm: the gather stores straight into the peer's slot (measured about 10 % faster
-    // back to back, but its CTAs then hold SMs for the whole NVLink transfer); default: copy engine.
-    // Folding the signal into that kernel (last CTA done stores the counter) measured slower: every
-    // thread then pays a system-wide fence behind its peer stores.
+    // Folding the signal into the gather kernel (last CTA done stores the counter) measured slower:
+    // every thread then pays a system-wide fence behind its peer stores.
     count_launch(2);
     link_gather_kernel<<<grid, 256, 0, st>>>(kc_.as<uint4>() + off / 8, vc_.as<uint4>() + off / 8, ids, vec,
                                              static_cast<long long>(layer_elems() / 8), parts,
                                              reinterpret_cast<uint4*>(sm_copy() ? theirs : mine));
-    RB_CUDA(cudaEventRecord(l.gathered[k & 1], st));  // from here on the message no longer reads the pages
+    RB_CUDA(cudaEventRecord(l.gathered[k % KvLink::kStreams], st));  // from here on the message no longer reads the pages
     if (!sm_copy()) RB_CUDA(cudaMemcpyAsync(theirs, mine, bytes, cudaMemcpyDefault, st));  // peer copy, by address
     link_signal_kernel<<<1, 1, 0, st>>>(arrived_of(l.peer, l, k), k + 1);
     RB_CUDA(cudaGetLastError());
@@ -319,10 +357,10 @@ void Backend::kv_link_recv_layers(int link, int layer0, int n_layers, const int3
   if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
   const size_t bb = kv_block_bytes();
   const long long vec = static_cast<long long>(bb / 16);
-  const int parts = static_cast<int>(std::max<long long>(1, std::min<long long>(8, vec / 256)));
+  const int parts = link_parts(vec, n);
   for (const LinkMsg& msg : link_messages(l, bb, layer0, n_layers, n)) {
     const uint32_t k = l.received++;
-    cudaStream_t st = l.streams[k & 1];
+    cudaStream_t st = l.streams[k % KvLink::kStreams];
     stream_wait_geq(st, arrived_of(l.region.p, l, k), k + 1);
     IdList ids;
     ids.n = msg.m;
@@ -352,7 +390,7 @@ void Backend::kv_link_skip_layers(int link, int n_layers, int n) {
   const size_t n_msgs = link_messages(l, kv_block_bytes(), 0, n_layers, n).size();
   for (size_t i = 0; i < n_msgs; ++i) {
     const uint32_t k = l.received++;
-    cudaStream_t st = l.streams[k & 1];
+    cudaStream_t st = l.streams[k % KvLink::kStreams];
     stream_wait_geq(st, arrived_of(l.region.p, l, k), k + 1);
     count_launch();
     link_signal_kernel<<<1, 1, 0, st>>>(ack_of(l.peer, l, k), k + 1);
@@ -370,10 +408,9 @@ void Backend::kv_link_wait(int link, int timeout_ms) {
     {
       std::lock_guard<std::mutex> lock(copy_mu_);
       KvLink& l = link_of(link);
-      const cudaError_t a = cudaStreamQuery(l.streams[0]), b = cudaStreamQuery(l.streams[1]);
+      const cudaError_t a = l.busy();
       if (a != cudaErrorNotReady && a != cudaSuccess) RB_CUDA(a);
-      if (b != cudaErrorNotReady && b != cudaSuccess) RB_CUDA(b);
-      if (a == cudaSuccess && b == cudaSuccess) {
+      if (a == cudaSuccess) {
         if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
         return;
       }
@@ -398,10 +435,9 @@ void Backend::kv_link_wait_gathered(int link, int timeout_ms) {
     {
       std::lock_guard<std::mutex> lock(copy_mu_);
       KvLink& l = link_of(link);
-      const cudaError_t a = cudaEventQuery(l.gathered[0]), b = cudaEventQuery(l.gathered[1]);
+      const cudaError_t a = l.busy(true);
       if (a != cudaErrorNotReady && a != cudaSuccess) RB_CUDA(a);
-      if (b != cudaErrorNotReady && b != cudaSuccess) RB_CUDA(b);
-      if (a == cudaSuccess && b == cudaSuccess) {
+      if (a == cudaSuccess) {
         if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
         return;
       }
@@ -436,14 +472,13 @@ void Backend::links_release() {
   // region never freed, and the process stops making device-wide synchronising calls.
   for (auto& l : links_) {
     if (!l || l->wedged) continue;
-    if (cudaStreamQuery(l->streams[0]) != cudaErrorNotReady && cudaStreamQuery(l->streams[1]) != cudaErrorNotReady) continue;
+    if (l->busy() != cudaErrorNotReady) continue;
     l->broken = true;
     cudaMemcpyAsync(l->region.p, l->release_words.p, kControlBytes, cudaMemcpyHostToDevice, l->release_stream);
     const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(2);
     bool busy = true;
     while (busy && std::chrono::steady_clock::now() < deadline) {
-      busy = cudaStreamQuery(l->streams[0]) == cudaErrorNotReady || cudaStreamQuery(l->streams[1]) == cudaErrorNotReady ||
-             cudaStreamQuery(l->release_stream) == cudaErrorNotReady;
+      busy = l->busy() == cudaErrorNotReady || cudaStreamQuery(l->release_stream) == cudaErrorNotReady;
       if (busy) std::this_thread::sleep_for(std::chrono::microseconds(200));
     }
     if (busy) {

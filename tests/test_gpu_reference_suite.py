@@ -52,8 +52,12 @@ def test_relays_transfer_engine_over_a_kv_link(devices):
         import torch
         if torch.cuda.device_count() < 2:
             pytest.skip("needs two GPUs")
-    env = dict(os.environ, RB200_LINK_DEVICES=devices)
-    r = subprocess.run([exe], cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    # A link orders its streams by counters the CUDA scheduler cannot see. With both ends on one
+    # device, two of their streams may share a hardware queue, and a wait enqueued ahead of the work
+    # that satisfies it would then hold that work back until the link's host deadline: give every
+    # stream a queue of its own (two devices, the real use, have separate queues anyway).
+    env = dict(os.environ, RB200_LINK_DEVICES=devices, CUDA_DEVICE_MAX_CONNECTIONS="32")
+    r = subprocess.run([exe], cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     tail = (r.stdout + r.stderr)[-3000:]
     assert r.returncode == 0, tail
     assert "\n0 failed" in tail, tail
