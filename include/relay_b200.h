@@ -283,8 +283,9 @@ int rb200_kv_link_connect_local(rb200_backend* a, int link_a, rb200_backend* b, 
 int rb200_kv_link_send_layer(rb200_backend* b, int link, int layer, const int32_t* blocks, int n);
 int rb200_kv_link_recv_layer(rb200_backend* b, int link, int layer, const int32_t* blocks, int n);
 /* The same for n_layers consecutive layers of one request whose K/V is complete (a prompt handed
- * over after its prefill rather than streamed during it: engine/src/kv_transfer.cpp:107-128 sends
- * the Layer frames of a finished request back to back): as many whole layers as a slot holds
+ * over after its prefill rather than streamed during it; relay's sender thread takes the queued
+ * Layer jobs of such a request one frame at a time, engine/src/kv_transfer.cpp:130-150, each
+ * through send_layer, :107-128): as many whole layers as a slot holds
  * travel as ONE message (one gather, one copy-engine copy, one counter store), so a ring of slots
  * of several layers moves a prompt at the copy engines' rate instead of the host's enqueue rate.
  * The receiver makes the matching call with the same first_layer, n_layers and n (the ends cut
