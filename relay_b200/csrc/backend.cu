@@ -31,21 +31,21 @@ std::atomic<uint64_t>& launch_counter() {
 }
 
 int sm_count() {
-  static int cached[64] = {0};
+  static std::atomic<int> cached[64];  // zero-initialised; racing first calls store the same value
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     cudaGetLastError();
     return 148;  // B200; only used for planning when no device is present
   }
-  if (cached[dev] == 0) {
+  if (cached[dev].load(std::memory_order_relaxed) == 0) {
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = 148;
     }
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return cached[dev].load(std::memory_order_relaxed);
 }
 
 DeviceBuf::DeviceBuf(size_t n, bool zero) : bytes(n) {

@@ -5,6 +5,9 @@
 
 #include <cuda.h>
 
+#include <algorithm>
+#include <array>
+
 #include "common.cuh"
 
 namespace rb200 {
@@ -183,6 +186,37 @@ __host__ __device__ constexpr uint32_t umma_idesc(int M, int N) {
   return (1u << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+
+// How many clusters of 1..8 CTAs (along z) of `kernel` are resident at once on the current device
+// ([0] unused). A cluster needs its CTAs on SMs of one GPC at the same time, so fewer clusters
+// than SMs / size fit; the occupancy query knows how many. Callers keep the answer in a
+// function-local static (initialised once, thread-safe): the GPUs of one box are the same model.
+template <class Kernel>
+std::array<int, 9> cluster_capacity(Kernel kernel, int threads, size_t dynamic_smem) {
+  std::array<int, 9> cap{};
+  cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dynamic_smem));
+  for (int sp = 1; sp <= 8; ++sp) {
+    cudaLaunchConfig_t q{};
+    q.gridDim = dim3(1, 1, sp);
+    q.blockDim = dim3(threads);
+    q.dynamicSmemBytes = dynamic_smem;
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = 1;
+    qa[0].val.clusterDim.y = 1;
+    qa[0].val.clusterDim.z = sp;
+    q.attrs = qa;
+    q.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = std::max(1, sm_count() / sp / 2);  // a cautious guess
+    }
+    cap[sp] = n;
+  }
+  cudaGetLastError();
+  return cap;
+}
 
 }  // namespace tc
 }  // namespace rb200

@@ -520,30 +520,8 @@ void launch_umma_t(const WeightView& W, const __half* x, int ldx, float* y, int 
   // epilogue) counts like 48 KB of weights. A cluster needs its CTAs on SMs of one GPC at the same
   // time, so fewer clusters than SMs / size are resident together: the occupancy query says how many.
   const int ttiles = div_up(T, BN), nk = div_up(W.K, S::kKB);
-  static int capacity[9] = {0};  // clusters of size s resident at once on this device
-  if (capacity[1] == 0) {
-    auto kernel = umma_gemm_kernel<BN, INT8, 1>;
-    RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kTotal)));
-    for (int sp = 1; sp <= 8; ++sp) {
-      cudaLaunchConfig_t q{};
-      q.gridDim = dim3(1, 1, sp);
-      q.blockDim = dim3(INT8 ? kUmmaThreadsInt8 : kUmmaThreads);
-      q.dynamicSmemBytes = S::kTotal;
-      cudaLaunchAttribute qa[1];
-      qa[0].id = cudaLaunchAttributeClusterDimension;
-      qa[0].val.clusterDim.x = 1;
-      qa[0].val.clusterDim.y = 1;
-      qa[0].val.clusterDim.z = sp;
-      q.attrs = qa;
-      q.numAttrs = 1;
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) != cudaSuccess || n <= 0) {
-        cudaGetLastError();
-        n = std::max(1, sm_count() / sp / 2);  // a cautious guess
-      }
-      capacity[sp] = n;
-    }
-  }
+  static const std::array<int, 9> capacity =
+      cluster_capacity(umma_gemm_kernel<BN, INT8, 1>, INT8 ? kUmmaThreadsInt8 : kUmmaThreads, S::kTotal);
   const bool can_split = static_cast<size_t>(BN) * kTileM * 4 <= static_cast<size_t>(S::kStages) * S::kStageBytes;
   using S2 = UmmaSmem<BN, INT8, INT8 ? 1 : 2>;
   const bool can_split2 = static_cast<size_t>(BN) * kTileM * 4 <= static_cast<size_t>(S2::kStages) * S2::kStageBytes;

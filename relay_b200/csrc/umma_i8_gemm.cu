@@ -427,28 +427,7 @@ void launch_i8_t(const WeightView& W, const int8_t* digits, const float* tscale,
   // needs its CTAs on SMs of one GPC at the same time, so fewer clusters than SMs / size are
   // resident together: the occupancy query says how many.
   const int ttiles = div_up(T, BN), nk = div_up(W.K, kBlockKB);
-  static int capacity[9] = {0};  // clusters of size s resident at once on this device
-  if (capacity[1] == 0) {
-    for (int sp = 1; sp <= 8; ++sp) {
-      cudaLaunchConfig_t q{};
-      q.gridDim = dim3(1, 1, sp);
-      q.blockDim = dim3(kI8Threads);
-      q.dynamicSmemBytes = S::kTotal;
-      cudaLaunchAttribute qa[1];
-      qa[0].id = cudaLaunchAttributeClusterDimension;
-      qa[0].val.clusterDim.x = 1;
-      qa[0].val.clusterDim.y = 1;
-      qa[0].val.clusterDim.z = sp;
-      q.attrs = qa;
-      q.numAttrs = 1;
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) != cudaSuccess || n <= 0) {
-        cudaGetLastError();
-        n = std::max(1, sm_count() / sp / 2);  // a cautious guess
-      }
-      capacity[sp] = n;
-    }
-  }
+  static const std::array<int, 9> capacity = cluster_capacity(kernel, kI8Threads, S::kTotal);
   // The search is per (N, K, token tiles) and remembered: it runs once per matrix shape.
   static std::mutex plan_mu;
   static std::unordered_map<uint64_t, std::pair<int, int>> plans;
