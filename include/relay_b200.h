@@ -294,6 +294,12 @@ int rb200_kv_link_recv_layer(rb200_backend* b, int link, int layer, const int32_
 int rb200_kv_link_send_layers(rb200_backend* b, int link, int first_layer, int n_layers, const int32_t* blocks, int n);
 int rb200_kv_link_recv_layers(rb200_backend* b, int link, int first_layer, int n_layers, const int32_t* blocks, int n);
 int rb200_kv_link_skip_layers(rb200_backend* b, int link, int n_layers, int n);
+/* How the calls above cut n_layers layers of n blocks of block_bytes (each block once for K and
+ * once for V) into messages for a ring of slots of slot_bytes: the number of messages (returned;
+ * -1 for arguments no link accepts) and the largest number of whole layers one message carries
+ * (0 when a single layer already needs several messages). Pure host arithmetic, the same on
+ * both ends; a sender may keep as many messages in flight as the ring has slots. */
+int rb200_kv_link_plan(size_t slot_bytes, size_t block_bytes, int n_layers, int n, int32_t* layers_per_message_out);
 /* Sender: waits until every layer sent so far has been read out of the cache (its gather has
  * run; the copy may still be under way), after which the sender's blocks may be rewritten. The
  * reference frees a request's blocks once its last frame is written

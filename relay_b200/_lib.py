@@ -86,6 +86,7 @@ SIGNATURES = {
     "rb200_kv_link_send_layers": (I, [P, I, I, I, P, I]),
     "rb200_kv_link_recv_layers": (I, [P, I, I, I, P, I]),
     "rb200_kv_link_skip_layers": (I, [P, I, I, I]),
+    "rb200_kv_link_plan": (I, [SZ, SZ, I, I, P]),
     "rb200_kv_link_connect_local": (I, [P, I, P, I]),
     "rb200_kv_link_skip_layer": (I, [P, I, I]),
     "rb200_kv_link_wait": (I, [P, I, I]),

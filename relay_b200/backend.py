@@ -338,6 +338,15 @@ class Backend:
     def kv_link_skip_layers(self, link: int, n_layers: int, n_blocks: int) -> None:
         _lib.check(self._L.rb200_kv_link_skip_layers(self._h, link, n_layers, n_blocks))
 
+    @staticmethod
+    def kv_link_plan(slot_bytes: int, block_bytes: int, n_layers: int, n_blocks: int) -> Tuple[int, int]:
+        """(messages, most whole layers in one message) for such a request over a ring of such slots."""
+        per = C.c_int32(0)
+        n = _lib.lib().rb200_kv_link_plan(slot_bytes, block_bytes, n_layers, n_blocks, C.byref(per))
+        if n < 0:
+            raise ValueError("kv_link_plan: arguments no link accepts")
+        return n, per.value
+
     def kv_link_connect_local(self, link: int, other: "Backend", other_link: int) -> None:
         """Joins two backends of this process (same or different devices) by address."""
         _lib.check(self._L.rb200_kv_link_connect_local(self._h, link, other._h, other_link))

@@ -148,15 +148,15 @@ struct LinkMsg {
   int layer, layers, b0, m;
 };
 
-std::vector<LinkMsg> link_messages(const KvLink& l, size_t block_bytes, int layer0, int n_layers, int n) {
+std::vector<LinkMsg> link_messages(size_t slot_bytes, size_t block_bytes, int layer0, int n_layers, int n) {
   std::vector<LinkMsg> out;
   const size_t layer_bytes = 2 * static_cast<size_t>(n) * block_bytes;
-  if (n <= kMaxIds && layer_bytes <= l.slot_bytes) {
-    const int per = static_cast<int>(std::min<size_t>(l.slot_bytes / layer_bytes, 4096));
+  if (n <= kMaxIds && layer_bytes <= slot_bytes) {
+    const int per = static_cast<int>(std::min<size_t>(slot_bytes / layer_bytes, 4096));
     for (int a = 0; a < n_layers; a += per) out.push_back({layer0 + a, std::min(per, n_layers - a), 0, n});
     return out;
   }
-  const int per_msg = static_cast<int>(std::min<size_t>(kMaxIds, l.slot_bytes / (2 * block_bytes)));
+  const int per_msg = static_cast<int>(std::min<size_t>(kMaxIds, slot_bytes / (2 * block_bytes)));
   for (int a = 0; a < n_layers; ++a)
     for (int b0 = 0; b0 < n; b0 += per_msg) out.push_back({layer0 + a, 1, b0, std::min(per_msg, n - b0)});
   return out;
@@ -312,7 +312,7 @@ void Backend::kv_link_send_layers(int link, int layer0, int n_layers, const int3
   // (the layers of a pass complete in order).
   int waited_for[KvLink::kStreams];
   for (int& w : waited_for) w = -1;
-  for (const LinkMsg& msg : link_messages(l, bb, layer0, n_layers, n)) {
+  for (const LinkMsg& msg : link_messages(l.slot_bytes, bb, layer0, n_layers, n)) {
     const uint32_t k = l.sent++;
     cudaStream_t st = l.streams[k % KvLink::kStreams];
     const int last = msg.layer + msg.layers - 1;
@@ -358,7 +358,7 @@ void Backend::kv_link_recv_layers(int link, int layer0, int n_layers, const int3
   const size_t bb = kv_block_bytes();
   const long long vec = static_cast<long long>(bb / 16);
   const int parts = link_parts(vec, n);
-  for (const LinkMsg& msg : link_messages(l, bb, layer0, n_layers, n)) {
+  for (const LinkMsg& msg : link_messages(l.slot_bytes, bb, layer0, n_layers, n)) {
     const uint32_t k = l.received++;
     cudaStream_t st = l.streams[k % KvLink::kStreams];
     stream_wait_geq(st, arrived_of(l.region.p, l, k), k + 1);
@@ -387,7 +387,7 @@ void Backend::kv_link_skip_layers(int link, int n_layers, int n) {
   KvLink& l = link_of(link);
   RB_REQUIRE(l.peer != nullptr, "kv_link_skip_layers: the link is not connected");
   if (l.broken) fail(RB200_ERR_RUNTIME, "kv link: broken by an earlier timeout");
-  const size_t n_msgs = link_messages(l, kv_block_bytes(), 0, n_layers, n).size();
+  const size_t n_msgs = link_messages(l.slot_bytes, kv_block_bytes(), 0, n_layers, n).size();
   for (size_t i = 0; i < n_msgs; ++i) {
     const uint32_t k = l.received++;
     cudaStream_t st = l.streams[k % KvLink::kStreams];
@@ -490,3 +490,17 @@ void Backend::links_release() {
 }
 
 }  // namespace rb200
+
+extern "C" int rb200_kv_link_plan(size_t slot_bytes, size_t block_bytes, int n_layers, int n, int32_t* layers_per_message_out) {
+  if (block_bytes == 0 || slot_bytes < 2 * block_bytes || slot_bytes % 256 != 0 || n_layers < 1 || n < 0) return -1;
+  if (n == 0) {
+    if (layers_per_message_out) *layers_per_message_out = 0;
+    return 0;
+  }
+  const std::vector<rb200::LinkMsg> msgs = rb200::link_messages(slot_bytes, block_bytes, 0, n_layers, n);
+  int most = 0;
+  for (const rb200::LinkMsg& m : msgs)
+    if (m.m == n) most = std::max(most, m.layers);
+  if (layers_per_message_out) *layers_per_message_out = most;
+  return static_cast<int>(msgs.size());
+}

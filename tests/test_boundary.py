@@ -86,6 +86,26 @@ def test_scratch_sizes_are_host_computable():
     assert L.rb200_kernel_launches() == 0
 
 
+def test_kv_link_message_plan_is_host_computable():
+    from relay_b200.backend import Backend
+    bb = 8 * 16 * 128 * 2                       # a Llama-3-8B block: 8 KV heads x 16 keys x 128 x fp16
+    layer = 2 * 128 * bb                        # a 2048-token prompt: 128 blocks, K and V
+    assert Backend.kv_link_plan(layer, bb, 1, 128) == (1, 1)          # a streamed layer: one message
+    assert Backend.kv_link_plan(layer, bb, 32, 128) == (32, 1)        # a finished prompt over such a ring
+    assert Backend.kv_link_plan(8 * layer, bb, 32, 128) == (4, 8)     # slots of 8 layers: four messages
+    assert Backend.kv_link_plan(5 * layer, bb, 32, 128) == (7, 5)     # 6 x 5 layers + 2
+    assert Backend.kv_link_plan(8 * layer, bb, 3, 128) == (1, 3)      # a short range does not fill the slot
+    # a layer larger than a slot travels as messages of blocks, layer by layer
+    assert Backend.kv_link_plan(4 * 2 * bb, bb, 2, 19) == (10, 0)
+    # more blocks than ride in one kernel's parameters (480): also cut by blocks, whatever the slot
+    assert Backend.kv_link_plan(4096 * 2 * bb, bb, 1, 1000) == (3, 0)
+    assert Backend.kv_link_plan(layer, bb, 32, 0) == (0, 0)
+    for bad in ((bb, bb, 1, 1), (layer + 1, bb, 1, 1), (layer, 0, 1, 1), (layer, bb, 0, 1), (layer, bb, 1, -1)):
+        with pytest.raises(ValueError):
+            Backend.kv_link_plan(*bad)
+    assert _lib.lib().rb200_kernel_launches() == 0
+
+
 @pytest.mark.skipif(_lib.lib().rb200_device_count() > 0, reason="a CUDA device is present")
 def test_no_cpu_fallback_without_a_device():
     from relay_b200.backend import make_cuda_backend
