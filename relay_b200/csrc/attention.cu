@@ -113,7 +113,9 @@ decode_split_kernel(const float* __restrict__ q, TokenMeta m, const int* __restr
   __shared__ float cm_m[16], cm_l[16];    // cluster merge: this slice's (max, sum) per head
 
   pdl_trigger();
-  pdl_wait();
+  // The token's context length and the block ids of the slice are batch metadata, complete before
+  // the pass started: they are fetched (a chain of four dependent loads) while the kernel ahead,
+  // which writes q and this step's K/V, still runs.
   const int di = blockIdx.x, kvh = blockIdx.y, part = blockIdx.z;
   const int tok = decode_tokens[di];
   const int ctx = m.pos[tok] + 1;
@@ -148,6 +150,7 @@ decode_split_kernel(const float* __restrict__ q, TokenMeta m, const int* __restr
       for (int i = threadIdx.x; i < nblk; i += blockDim.x) s_table[i] = src[i];
     }
   }
+  pdl_wait();
 
   // The G query heads of this KV head as A fragments (rows = heads, columns = d), fp16.
   uint32_t qf[D / 16][4];
@@ -663,6 +666,7 @@ void launch_decode_t(const AttnShape& s, const float* q, const TokenMeta& m, con
   static PerDeviceOnce once;
   auto kernel = decode_split_kernel<D, CONTIG, WIDE>;
   if (once.first()) raise_smem(kernel, decode_smem_bytes<D>());
+  RB_REQUIRE(!cluster_merge || parts <= 8, "decode attention: a cluster holds at most 8 slices");
   const float scale_log2e = kLog2e / sqrtf(static_cast<float>(D));
   dim3 grid(n_decode, s.kv_heads, parts);
   count_launch();
@@ -761,6 +765,8 @@ DecodePlan plan_decode(const AttnShape& s, int n_decode, int max_ctx) {
   }();
   const bool resident = pairs_kv * parts <= static_cast<long long>(sm_count());
   p.cluster_merge = parts > 1 && parts <= 8 && (cluster_mode == 2 || (cluster_mode == 1 && resident));
+  // (Slices of 256 keys in clusters of up to 16, which put twice the CTAs on a single sequence's
+  // keys, were measured too: 2.49 against 2.45 ms per 1-sequence step, no gain, and left out.)
   // one slice writes the output directly, a cluster merges on chip: no partial results, no merge kernel
   p.scratch_bytes = (parts > 1 && !p.cluster_merge) ? static_cast<size_t>(n_decode) * s.heads * parts * (s.D + 2) * sizeof(float) : 0;
   return p;

@@ -95,6 +95,13 @@ struct PerDeviceOnce {
 // kernel ahead of it has completed and its writes are visible), and is launched through
 // launch_pdl(): its launch latency and block scheduling then overlap the tail of its
 // predecessor. Both instructions do nothing in a kernel launched the ordinary way.
+//
+// What a kernel may read BEFORE pdl_wait(): the weights, and the batch metadata (positions,
+// sequence ids, block tables, row lists). The metadata reaches the device by a copy that precedes
+// the first kernel of a pass, or is updated by session_advance_kernel / session_finish_kernel, and
+// session_advance_kernel does not call pdl_trigger(): the kernel behind it, and with it every
+// later kernel of the step, starts only once the update is complete. Activations and K/V pages
+// are written by kernels of the same pass and are read after the wait only.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

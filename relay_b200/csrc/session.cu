@@ -27,7 +27,9 @@ namespace {
 // the previous step picked), the block ids appended to the tables.
 __global__ void session_advance_kernel(int* __restrict__ meta, const int* __restrict__ picked, int S, int cap, int T4,
                                        int tables_off, int delta_off, int tokens_off, int blocks_off) {
-  pdl_trigger();
+  // No pdl_trigger(): the kernels of the step read this metadata before their own dependency
+  // wait, so none of them may start before this kernel (and session_finish_kernel of the step
+  // before it, which it waits for) has completed.
   pdl_wait();
   const int* hdr = meta + delta_off;
   const int n_new = hdr[0], feed_own = hdr[1];

@@ -65,7 +65,6 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
                                __half* __restrict__ out, int H, int ld_out, float eps, int8_t* __restrict__ digits,
                                float* __restrict__ tscale) {
   pdl_trigger();
-  pdl_wait();
   __shared__ float red[32];
   const int r = blockIdx.x;
   const float* xr = x + static_cast<long long>(rows ? rows[r] : r) * H;
@@ -73,8 +72,9 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
   float ss = 0.0f;
   const bool vec = (H & 3) == 0;
   // Rows of up to 8 values per thread (every width the path's models have) stay in registers
-  // between the two passes, and the norm weights are fetched before the block-wide sum: one
-  // round trip to memory instead of three.
+  // between the two passes, and the norm weights are fetched before the dependency wait (they and
+  // the row list do not come from the kernel ahead): one round trip to memory behind the wait
+  // instead of three.
   const bool cached = vec && H <= static_cast<int>(blockDim.x) * 8;
   float4 xc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
   float4 wc[2] = {xc[0], xc[0]};
@@ -82,10 +82,15 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
       const int i = (k * blockDim.x + threadIdx.x) * 4;
-      if (i < H) {
-        xc[k] = *reinterpret_cast<const float4*>(xr + i);
-        wc[k] = *reinterpret_cast<const float4*>(w + i);
-      }
+      if (i < H) wc[k] = *reinterpret_cast<const float4*>(w + i);
+    }
+  }
+  pdl_wait();
+  if (cached) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = (k * blockDim.x + threadIdx.x) * 4;
+      if (i < H) xc[k] = *reinterpret_cast<const float4*>(xr + i);
     }
 #pragma unroll
     for (int k = 0; k < 2; ++k) ss += xc[k].x * xc[k].x + xc[k].y * xc[k].y + xc[k].z * xc[k].z + xc[k].w * xc[k].w;
@@ -147,13 +152,14 @@ __global__ void qkv_post_kernel(float* __restrict__ qkv, const float* __restrict
                                 const float* __restrict__ inv_freq, TokenMeta m, __half* __restrict__ kc,
                                 __half* __restrict__ vc, int heads, int kv_heads, int D, int block_size) {
   pdl_trigger();
-  pdl_wait();
   extern __shared__ float cs[];  // [D/2] cos, [D/2] sin
   // gridDim.y blocks share a token (heads and kv_heads are multiples of it): each takes its share
   // of the q heads and of the k/v heads.
   const int t = blockIdx.x, part = blockIdx.y, parts = gridDim.y;
   const int Q = heads * D, KV = kv_heads * D, QKV = Q + 2 * KV, half = D / 2;
   float* row = qkv + static_cast<long long>(t) * QKV;
+  // The rotation angles and the token's page depend on the batch metadata only: both are ready
+  // by the time the projection ahead of this kernel has finished.
   const int p = m.pos[t];
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     float s, c;
@@ -163,6 +169,7 @@ __global__ void qkv_post_kernel(float* __restrict__ qkv, const float* __restrict
   }
   const int block = m.tables[m.table_off[m.seq[t]] + p / block_size], slot = p % block_size;
   __syncthreads();
+  pdl_wait();
   // rotation: this part's q heads, then this part's k heads (stored below by the same block)
   const int qh = heads / parts, kh = kv_heads / parts;
   const int items = (qh + kh) * half;

@@ -207,6 +207,13 @@ DECODE_CASES = [
     (16, 4, 2, 48, [100, 777]),       # block size not a power of two
     (128, 8, 2, 16, [5000, 4097, 700, 3]),  # more than eight slices: partials in global memory and the merge kernel
     (64, 8, 8, 16, [6100, 1]),
+    # one or two sequences: the grid fits the SMs, so the slices of a (token, KV head) run as one
+    # cluster and merge on chip
+    (128, 32, 8, 16, [4096]),         # 8 slices
+    (128, 32, 8, 16, [3000]),         # 6 slices, the last one ragged
+    (128, 32, 8, 16, [2048, 1500]),   # 4 slices; the shorter context leaves one of its own empty
+    (128, 8, 2, 16, [4000]),
+    (64, 16, 4, 16, [4096]),
 ]
 
 
