@@ -383,13 +383,14 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
                                     __half* __restrict__ out, int heads, int D, int o_stride, int max_parts,
                                     int n_pairs, int slice) {
   pdl_trigger();
-  pdl_wait();
   const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (pair >= n_pairs) return;
   const int lane = threadIdx.x & 31;
-  const int di = pair / heads, h = pair - di * heads;
-  const int tok = decode_tokens[di];
-  const int parts = (pos[tok] + slice) / slice;  // ceil((pos + 1) / slice)
+  const int pair_c = min(pair, n_pairs - 1);
+  const int di = pair_c / heads, h = pair_c - di * heads;
+  const int tok = decode_tokens[di];                 // batch metadata: read while the split kernel still runs
+  const int parts = (pos[tok] + slice) / slice;      // ceil((pos + 1) / slice)
+  pdl_wait();
+  if (pair >= n_pairs) return;
   const long long base = static_cast<long long>(pair) * max_parts;
   float M = -INFINITY;
   for (int p0 = 0; p0 < parts; p0 += 32)

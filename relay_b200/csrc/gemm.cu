@@ -327,7 +327,18 @@ gemv_rows_i8_kernel(const int8_t* __restrict__ w, const float* __restrict__ scal
       ld_global_256(rbv[u], wb + u * 128, true);
     }
   }
+  // the row scales are weights too; what y holds (read with beta) is fetched right behind the wait,
+  // so that neither is a round trip to memory after the last multiply
+  const float sc_a = scale[min(n_a, N - 1)], sc_b = scale[min(n_b, N - 1)];
   pdl_wait();  // x and y belong to the kernels ahead until they complete
+  const int tok = 2 * t4;
+  float old[4] = {0.f, 0.f, 0.f, 0.f};  // y at (tok, n_a), (tok + 1, n_a), (tok, n_b), (tok + 1, n_b)
+  if (part == 0 && beta != 0.f) {
+    if (n_a < N && tok < T) old[0] = y[static_cast<long long>(tok) * N + n_a];
+    if (n_a < N && tok + 1 < T) old[1] = y[static_cast<long long>(tok + 1) * N + n_a];
+    if (n_b < N && tok < T) old[2] = y[static_cast<long long>(tok) * N + n_b];
+    if (n_b < N && tok + 1 < T) old[3] = y[static_cast<long long>(tok + 1) * N + n_b];
+  }
   // token g's 32 activations of a block, at the same k as this lane's 32 weight bytes
   const __half* xg = x + static_cast<long long>(min(g, T - 1)) * ldx + k0 + 32 * t4;
   const bool tok_live = g < T;
@@ -367,21 +378,13 @@ gemv_rows_i8_kernel(const int8_t* __restrict__ w, const float* __restrict__ scal
 #pragma unroll
     for (int i = 0; i < 4; ++i) s[i] += red[group * WPG + wv][lane][i];
   // s[0], s[1]: row n_a, tokens 2 t4 and 2 t4 + 1; s[2], s[3]: row n_b
-  const int tok = 2 * t4;
-  auto finish = [&](int n, float v0, float v1) {
+  auto finish = [&](int n, float sc, float v0, float v1, float o0, float o1) {
     if (n >= N) return;
-    const float sc = scale[n];
-    if (tok < T) {
-      float* d = y + static_cast<long long>(tok) * N + n;
-      *d = beta != 0.f ? v0 * sc + beta * *d : v0 * sc;
-    }
-    if (tok + 1 < T) {
-      float* d = y + static_cast<long long>(tok + 1) * N + n;
-      *d = beta != 0.f ? v1 * sc + beta * *d : v1 * sc;
-    }
+    if (tok < T) y[static_cast<long long>(tok) * N + n] = beta != 0.f ? v0 * sc + beta * o0 : v0 * sc;
+    if (tok + 1 < T) y[static_cast<long long>(tok + 1) * N + n] = beta != 0.f ? v1 * sc + beta * o1 : v1 * sc;
   };
-  finish(n_a, s[0], s[1]);
-  finish(n_b, s[2], s[3]);
+  finish(n_a, sc_a, s[0], s[1], old[0], old[1]);
+  finish(n_b, sc_b, s[2], s[3], old[2], old[3]);
 }
 
 // ---- GEMM (T > 8) --------------------------------------------------------------------------

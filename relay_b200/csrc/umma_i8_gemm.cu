@@ -337,14 +337,24 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else {
       pdl_wait();  // token scales (and, with beta, y) come from kernels before this one
     }
-    const bool done = mbar_wait(accum_bar, 0);
-    if (!done) atomicExch(status, 24);
-    tc_fence_after();
+    // What the epilogue needs besides the accumulator is in memory already (the row scales are
+    // weights; the token scales and y come from kernels that have completed): the first 16 token
+    // columns' worth is fetched while the MMAs still run, not behind them.
     const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
     const int row = quarter * 32 + lane;
     const int n = m0 + row;
     const bool live = row < rows && n < N;
     const float sc = live ? scale[n] : 0.f;
+    const int nt0 = min(16, T - tok0);
+    float old0[16], ts0[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      old0[j] = (splits == 1 && live && beta != 0.f && j < nt0) ? y[static_cast<long long>(tok0 + j) * N + n] : 0.f;
+      ts0[j] = FUSED ? ts[j & (kFusedTokens - 1)] : (j < nt0 ? tscale[tok0 + j] : 0.f);
+    }
+    const bool done = mbar_wait(accum_bar, 0);
+    if (!done) atomicExch(status, 24);
+    tc_fence_after();
     const uint32_t trow = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     float* red = reinterpret_cast<float*>(gen_base);  // split K: this CTA's partial tile, red[token][row]
 #pragma unroll 1
@@ -365,29 +375,50 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       } else if (done && live) {
         const int nt = min(16, T - tok0 - c0);  // valid token columns of this chunk
         float* dst = y + static_cast<long long>(tok0 + c0) * N + n;
-        float old[16];
+        float old[16], tsv[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) old[j] = (beta != 0.f && j < nt) ? dst[static_cast<long long>(j) * N] : 0.f;
+        for (int j = 0; j < 16; ++j) {
+          old[j] = c0 == 0 ? old0[j] : ((beta != 0.f && j < nt) ? dst[static_cast<long long>(j) * N] : 0.f);
+          tsv[j] = c0 == 0 ? ts0[j] : (FUSED ? ts[j & (kFusedTokens - 1)] : (j < nt ? tscale[tok0 + c0 + j] : 0.f));
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j)
-          if (j < nt) dst[static_cast<long long>(j) * N] = v[j] * (sc * (FUSED ? ts[j & (kFusedTokens - 1)] : tscale[tok0 + c0 + j])) + beta * old[j];
+          if (j < nt) dst[static_cast<long long>(j) * N] = v[j] * (sc * tsv[j]) + beta * old[j];
       }
     }
   }
   if (splits > 1) {
+    // What this CTA's share of the columns needs from memory (row scale, token scales, y) is
+    // fetched before the cluster barrier, not behind it.
+    const int per = (BN + splits - 1) / splits;  // token columns this CTA finishes
+    const int c_begin = split * per, c_end = min(min(BN, c_begin + per), T - tok0);
+    constexpr int kPre = 8;
+    float old_pre[kPre], ts_pre[kPre];
+    float sc_pre = 0.f;
+    if (warp >= 2) {
+      const int row = (warp & 3) * 32 + lane;
+      const int n = m0 + row;
+      const bool live = row < rows && n < N;
+      sc_pre = live ? scale[n] : 0.f;
+#pragma unroll
+      for (int i = 0; i < kPre; ++i) {
+        const int c = c_begin + i;
+        const bool in = c < c_end;
+        old_pre[i] = (in && live && beta != 0.f) ? y[static_cast<long long>(tok0 + c) * N + n] : 0.f;
+        ts_pre[i] = !in ? 0.f : !FUSED ? tscale[tok0 + c] : c == 0 ? ts[0] : c == 1 ? ts[1] : c == 2 ? ts[2] : ts[3];
+      }
+    }
     cluster_sync_all();  // every member's partial tile is in its shared memory
     if (warp >= 2) {
       const int row = (warp & 3) * 32 + lane;
       const int n = m0 + row;
       const bool live = row < rows && n < N;
-      const float sc = live ? scale[n] : 0.f;
-      const int per = (BN + splits - 1) / splits;  // token columns this CTA finishes
-      const int c_begin = split * per, c_end = min(min(BN, c_begin + per), T - tok0);
+      const float sc = sc_pre;
       uint32_t peer[8];
 #pragma unroll
       for (int r = 0; r < 8; ++r)
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[r]) : "r"(base + static_cast<uint32_t>(row) * 4), "r"(r < splits ? r : 0));
-      for (int c = c_begin; c < c_end; ++c) {
+      auto finish_column = [&](int c, float old, float tsc) {
         float acc = 0.f;
 #pragma unroll
         for (int r = 0; r < 8; ++r) {  // members in rank order: the sum is the same on every run
@@ -396,12 +427,15 @@ umma_i8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part) : "r"(peer[r] + static_cast<uint32_t>(c * kTileM) * 4) : "memory");
           acc += part;
         }
-        if (live) {
-          float* dst = y + static_cast<long long>(tok0 + c) * N + n;
-          const float old = beta != 0.f ? *dst : 0.f;
-          const float tsc = !FUSED ? tscale[tok0 + c] : c == 0 ? ts[0] : c == 1 ? ts[1] : c == 2 ? ts[2] : ts[3];
-          *dst = acc * (sc * tsc) + beta * old;
-        }
+        if (live) y[static_cast<long long>(tok0 + c) * N + n] = acc * (sc * tsc) + beta * old;
+      };
+#pragma unroll
+      for (int i = 0; i < kPre; ++i)
+        if (c_begin + i < c_end) finish_column(c_begin + i, old_pre[i], ts_pre[i]);
+      for (int c = c_begin + kPre; c < c_end; ++c) {  // wider token tiles with few members: fetched here
+        const float old = (live && beta != 0.f) ? y[static_cast<long long>(tok0 + c) * N + n] : 0.f;
+        const float tsc = !FUSED ? tscale[tok0 + c] : c == 0 ? ts[0] : c == 1 ? ts[1] : c == 2 ? ts[2] : ts[3];
+        finish_column(c, old, tsc);
       }
     }
     cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
