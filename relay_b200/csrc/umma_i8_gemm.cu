@@ -491,7 +491,13 @@ void launch_i8_t(const WeightView& W, const int8_t* digits, const float* tscale,
           // below about 1.25 x BN rows a CTA is bound by its MMAs (3 x BN columns per k block
           // whatever the row count), not by its weight bytes
           const double eff_rows = std::max<double>(r, 1.25 * BN);
-          const double cost = static_cast<double>(div_up(clusters, static_cast<long long>(capacity[sp]))) *
+          // A grid of exactly as many clusters as fit at once only starts together on an empty
+          // GPU; under the tail of the kernel ahead its last cluster waits for a whole GPC's worth
+          // of slots. Filling the last slot measured no faster (33 clusters of four against 32 on
+          // 14336 -> 4096, 74 of two against 70 on 4096 -> 6144: within the run-to-run spread), so
+          // one cluster of room is kept.
+          const long long room = sp > 1 ? std::max(1, capacity[sp] - 1) : capacity[sp];
+          const double cost = static_cast<double>(div_up(clusters, room)) *
                               (eff_rows * W.K / sp + 48.0 * 1024 + (sp > 1 ? 8.0 * 1024 : 0.0));
           if (cost < best - 1e-9) {
             best = cost;
