@@ -750,12 +750,37 @@ DecodePlan plan_decode(const AttnShape& s, int n_decode, int max_ctx) {
   int slice = round_up(std::max(1, div_up(std::max(max_ctx, 1), want_parts)), kDecodeSlice);
   slice = static_cast<int>(std::min<long long>(slice, static_cast<long long>(kDecodeSlice) * s.block_size));
   slice = std::max(kDecodeSlice, slice / kDecodeSlice * kDecodeSlice);
-  const int parts = div_up(std::max(max_ctx, 1), slice);
+  int parts = div_up(std::max(max_ctx, 1), slice);
+  // A batch of a few sequences whose 512-key slices need more than one CTA per SM, but whose
+  // (token, KV head) pairs are few: at most four longer slices per pair, so that the whole grid
+  // is one wave (two CTAs per SM by shared memory; an eighth of the slots is left free, because a
+  // grid that needs every slot queues behind the tail of the kernel ahead) and still at least 128
+  // CTAs. Every CTA is then on an SM from the start, none is longer than the others (a slice
+  // bounds its keys), and the slices of a pair merge on chip below. Measured, int8 steps through
+  // rb200_decode_step, against 512-key slices and the merge kernel: 5 sequences 2.74 against
+  // 2.92 ms, 8 sequences 3.01 against 3.14, 12 sequences (192 CTAs of 2048 keys) 3.42 against
+  // 3.64, 16 sequences 3.74 against 4.03; 4 sequences the same (2.67 / 2.65). Left alone:
+  // 3 sequences (96 CTAs would be too few: 2.62 against 2.53) and plans that fill the slots
+  // (12 sequences as 288 CTAs of 1536 keys: 4.02). RB200_DECODE_ONE_WAVE=0 turns it off.
+  static const bool one_wave = [] {
+    const char* e = std::getenv("RB200_DECODE_ONE_WAVE");
+    return !(e && e[0] == '0');
+  }();
+  const long long slots = 2LL * sm_count() * 7 / 8;
+  if (one_wave && pairs_kv * parts > sm_count() && slots / pairs_kv >= 2) {
+    const int fit = static_cast<int>(std::min<long long>(4, slots / pairs_kv));
+    const int slice2 = round_up(div_up(std::max(max_ctx, 1), fit), kDecodeSlice);
+    const int parts2 = div_up(std::max(max_ctx, 1), slice2);
+    if (parts2 < parts && parts2 >= 2 && pairs_kv * parts2 >= 128 && slice2 <= kDecodeSlice * s.block_size) {
+      slice = slice2;
+      parts = parts2;
+    }
+  }
   DecodePlan p;
   p.slice = slice;
   p.parts = parts;
   // Up to 8 slices (the portable cluster size) can be merged inside the kernel, over distributed
-  // shared memory. That pays only while the whole grid is resident at once with an SM to each CTA: a
+  // shared memory. That pays only while the whole grid is resident at once: a
   // cluster keeps all its slots until its last slice is done and must be placed inside one GPC,
   // which costs more than the merge kernel once CTAs queue (32 sequences with contexts of
   // 1024 - 4096: 72.6 us against 62.4; an 8-sequence step 3.57 ms against 3.38; a 1-sequence
@@ -764,7 +789,8 @@ DecodePlan plan_decode(const AttnShape& s, int n_decode, int max_ctx) {
     const char* e = std::getenv("RB200_DECODE_CLUSTER");
     return e ? (e[0] == '0' ? 0 : 2) : 1;
   }();
-  const bool resident = pairs_kv * parts <= static_cast<long long>(sm_count());
+  // resident at once: one CTA per SM, or up to two with clusters of at most four
+  const bool resident = pairs_kv * parts <= sm_count() || (one_wave && parts <= 4 && pairs_kv * parts <= slots);
   p.cluster_merge = parts > 1 && parts <= 8 && (cluster_mode == 2 || (cluster_mode == 1 && resident));
   // (Slices of 256 keys in clusters of up to 16, which put twice the CTAs on a single sequence's
   // keys, were measured too: 2.49 against 2.45 ms per 1-sequence step, no gain, and left out.)
