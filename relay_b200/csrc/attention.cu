@@ -736,21 +736,28 @@ size_t decode_scratch_bytes(const AttnShape& s, int n_decode, int max_ctx) {
   return static_cast<size_t>(n_decode) * s.heads * parts * (s.D + 2) * sizeof(float);
 }
 
-// Slices are 512 keys when the batch alone would not fill the GPU; with many (token, KV
-// head) pairs they grow (in steps of 512, up to 512 block-table entries) until a few waves
-// of CTAs remain, which spares the partial results and, at one slice, the merge.
+// A batch with enough (token, KV head) pairs to put a CTA on most SMs (more than half the
+// resident slots: 17 sequences of the benchmark model) gets ONE slice per pair, as long as a
+// slice's block ids fit the kernel's table (512 entries: 8192 keys at block size 16): no partial
+// results, no merge. Splitting such contexts further to even out the waves of CTAs costs more
+// than it gains (int8 steps at 20 / 24 / 32 sequences: 4.15 / 4.45 / 5.24 ms against 4.49 / 4.73 /
+// 5.42 with slices cut for eight waves; 32 sequences with contexts of 1024 - 4096: 58.3 against
+// 62.3 us per launch). Fewer pairs are cut into 512-key slices and then treated as below.
+// RB200_DECODE_WAVES=n: slices cut for n waves of CTAs, whatever the batch.
 DecodePlan plan_decode(const AttnShape& s, int n_decode, int max_ctx) {
   const long long pairs_kv = std::max<long long>(1, static_cast<long long>(n_decode) * s.kv_heads);
-  static const int waves = [] {
+  static const int forced_waves = [] {
     const char* e = std::getenv("RB200_DECODE_WAVES");
-    return e && std::atoi(e) > 0 ? std::atoi(e) : 8;
+    return e && std::atoi(e) > 0 ? std::atoi(e) : 0;
   }();
-  const long long want_ctas = static_cast<long long>(waves) * sm_count();
-  const int want_parts = static_cast<int>(std::max<long long>(1, div_up(want_ctas, pairs_kv)));
+  const bool many = pairs_kv > 2LL * sm_count() * 7 / 16;  // more than half the slots the one-wave rule below counts
+  const long long want_ctas = static_cast<long long>(forced_waves ? forced_waves : 8) * sm_count();
+  const int want_parts = (many && !forced_waves) ? 1 : static_cast<int>(std::max<long long>(1, div_up(want_ctas, pairs_kv)));
   int slice = round_up(std::max(1, div_up(std::max(max_ctx, 1), want_parts)), kDecodeSlice);
   slice = static_cast<int>(std::min<long long>(slice, static_cast<long long>(kDecodeSlice) * s.block_size));
   slice = std::max(kDecodeSlice, slice / kDecodeSlice * kDecodeSlice);
   int parts = div_up(std::max(max_ctx, 1), slice);
+  slice = round_up(div_up(std::max(max_ctx, 1), parts), kDecodeSlice);  // the same number of slices, of even length
   // A batch of a few sequences whose 512-key slices need more than one CTA per SM, but whose
   // (token, KV head) pairs are few: at most four longer slices per pair, so that the whole grid
   // is one wave (two CTAs per SM by shared memory; an eighth of the slots is left free, because a

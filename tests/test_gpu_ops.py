@@ -233,15 +233,16 @@ def test_decode_attention_full_size_c2_shape(ops):
     assert row_err(got, want) < ATTN_TOL
 
 
-@pytest.mark.parametrize("n_seqs,why", [
-    (256, "2048 (token, KV head) pairs: one 4096-key slice per pair, written straight to the output, no merge"),
-    (64, "512 pairs: the planner cuts each context into a few slices of more than 512 keys and merges them"),
+@pytest.mark.parametrize("n_seqs,ctx,why", [
+    (256, 4096, "2048 (token, KV head) pairs: one 4096-key slice per pair, written straight to the output, no merge"),
+    (64, 4096, "512 pairs: one slice per pair as well, in fewer than two waves of CTAs"),
+    (32, 9024, "256 pairs whose contexts exceed the 8192 keys a slice's table holds: two slices each, partials and the merge kernel"),
 ])
-def test_decode_attention_at_the_decode_step_benchmark_size(ops, n_seqs, why):
-    # The launch the headline decode step makes per layer: every sequence at context 4096, 32 q /
-    # 8 kv heads of 128, block 16. With this many (token, KV head) pairs the slice rule grows the
-    # 512-key slices (launch_decode_attention), a path the small cases above never take.
-    heads, kv_heads, D, bs, ctx = 32, 8, 128, 16, 4096
+def test_decode_attention_at_the_decode_step_benchmark_size(ops, n_seqs, ctx, why):
+    # The launch the headline decode step makes per layer: every sequence at one context, 32 q /
+    # 8 kv heads of 128, block 16. With this many (token, KV head) pairs a slice is the whole
+    # context (launch_decode_attention), a path the small cases above never take.
+    heads, kv_heads, D, bs = 32, 8, 128, 16
     case = WideDecodeCase(5, n_seqs, ctx, heads, kv_heads, D, bs)
     k16, v16 = case.pools16()
     shape = ops.attn_shape(heads, kv_heads, D, bs)
