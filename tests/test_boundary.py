@@ -86,6 +86,35 @@ def test_scratch_sizes_are_host_computable():
     assert L.rb200_kernel_launches() == 0
 
 
+def test_decode_slice_plan_is_host_computable():
+    # (keys per slice, slices per context, bytes of partials) for the benchmark model's head layout
+    # on a 148-SM device (the count the planner assumes when no device is present)
+    L = _lib.lib()
+    if L.rb200_device_count() > 0:
+        pytest.skip("the plan follows the SM count of the device that is present")
+    shape = _lib.CAttnShape(32, 8, 128, 16, 6144, 4096)
+
+    def plan(n, ctx):
+        sl, parts = C.c_int32(0), C.c_int32(0)
+        nbytes = L.rb200_decode_plan(C.byref(shape), n, ctx, C.byref(sl), C.byref(parts))
+        return sl.value, parts.value, nbytes
+
+    # one or two sequences: 512-key slices, merged on chip as clusters of up to eight
+    assert plan(1, 4096) == (512, 8, 0) and plan(2, 4096) == (512, 8, 0) and plan(1, 3000) == (512, 6, 0)
+    # three: 192 CTAs of 512 keys, more than the SMs and too few for longer slices: partials and the merge kernel
+    assert plan(3, 4096) == (512, 8, 3 * 32 * 8 * 130 * 4)
+    # 4 - 16: at most four longer slices per pair, one wave, merged on chip
+    assert plan(4, 4096) == (1024, 4, 0) and plan(8, 4096) == (1024, 4, 0)
+    assert plan(12, 4096) == (2048, 2, 0) and plan(16, 4096) == (2048, 2, 0)
+    # from 17 sequences (136 pairs): one slice per pair
+    for n in (17, 32, 64, 256):
+        assert plan(n, 4096) == (4096, 1, 0)
+    # a slice's table holds 512 block ids: longer contexts are cut evenly and merged from partials
+    assert plan(32, 9024) == (4608, 2, 32 * 32 * 2 * 130 * 4)
+    assert plan(140, 131072)[:2] == (8192, 16)
+    assert L.rb200_kernel_launches() == 0
+
+
 def test_kv_link_message_plan_is_host_computable():
     from relay_b200.backend import Backend
     bb = 8 * 16 * 128 * 2                       # a Llama-3-8B block: 8 KV heads x 16 keys x 128 x fp16
