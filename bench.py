@@ -115,7 +115,7 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
     """The disaggregated variant: GPU 0 prefills 2048-token prompts and streams every layer's K/V
     pages over NVLink to the decode GPUs (ranks 1 .. N-1, prompts dealt round robin), which land
     them in their own block ids. Two transports carry the same payload: NCCL send/recv
-    (rb200_send_kv_layer / rb200_recv_kv_layer) and the K/V links (copy engines + counters,
+    (rb200_send_kv_layer / rb200_recv_kv_layer) and the K/V links (plain peer stores + counters,
     rb200_kv_link_*). For each: the hop alone, all layers of a prompt back to back (one pair, and
     one prompt to every decode GPU at once), and the hop issued from the layer observer while the
     prompts are prefilled (what it adds to the prefill time). The received pages of three layers

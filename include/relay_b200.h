@@ -252,16 +252,17 @@ int rb200_recv_kv_layer(rb200_backend* b, int peer, int layer, const int32_t* bl
  * wait the same way with a 10 s limit, so an unmatched send or receive cannot block them. */
 int rb200_kv_hop_sync(rb200_backend* b, int timeout_ms);
 
-/* ---- the same hop over a K/V link: copy engines and two counters, no library kernel -------
+/* ---- the same hop over a K/V link: plain peer stores and two counters, no library kernel ---
  * A link joins one backend in each of two processes on one box. Each end creates its side (a
  * ring of n_slots landing slots of slot_bytes each in its own device memory) and gets a
  * handle; the ends swap handles out of band (the host connection that carries the transfer
  * engine's Hello frame, engine/src/kv_transfer.cpp:185-200) and connect. The k-th
  * rb200_kv_link_send_layer on one end pairs with the k-th rb200_kv_link_recv_layer on the
  * other: same payload and order as the Layer frames (engine/include/relay/kv_transfer.h:14-18;
- * sender engine/src/kv_transfer.cpp:107-128, receiver :269-301). The sender gathers the pages
- * into its slot, a copy engine moves the slot across NVLink, the receiver scatters it into its
- * own block ids; slots are reused once the receiver has acknowledged them. Both calls only
+ * sender engine/src/kv_transfer.cpp:107-128, receiver :269-301). The sender's gather kernel
+ * stores the pages straight into the receiver's slot across NVLink (RB200_KV_LINK=ce: into its
+ * own slot, which a copy engine then moves), the receiver scatters the slot into its own block
+ * ids; slots are reused once the receiver has acknowledged them. Both calls only
  * enqueue (the send is ordered behind the layer's K/V append on the device);
  * rb200_kv_hop_sync waits for the links too, and on its deadline releases every wait the peer
  * has not satisfied and marks those links broken. A layer with more blocks than a slot holds
@@ -286,8 +287,8 @@ int rb200_kv_link_recv_layer(rb200_backend* b, int link, int layer, const int32_
  * over after its prefill rather than streamed during it; relay's sender thread takes the queued
  * Layer jobs of such a request one frame at a time, engine/src/kv_transfer.cpp:130-150, each
  * through send_layer, :107-128): as many whole layers as a slot holds
- * travel as ONE message (one gather, one copy-engine copy, one counter store), so a ring of slots
- * of several layers moves a prompt at the copy engines' rate instead of the host's enqueue rate.
+ * travel as ONE message (one gather, one counter store), so a ring of slots of several layers
+ * moves a prompt at NVLink's rate instead of the host's enqueue rate.
  * The receiver makes the matching call with the same first_layer, n_layers and n (the ends cut
  * messages by the same rule); rb200_kv_link_skip_layers is the dropping counterpart. With
  * n_layers == 1 these are the calls above. */

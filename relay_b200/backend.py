@@ -308,7 +308,7 @@ class Backend:
         b = i32(blocks)
         _lib.check(self._L.rb200_recv_kv_layer(self._h, peer, layer, ptr(b), b.size))
 
-    # -- K/V links (copy engines + counters; include/relay_b200.h) -----------------------------
+    # -- K/V links (plain peer stores + counters; include/relay_b200.h) ------------------------
     def kv_link_create(self, n_slots: int, slot_bytes: int) -> Tuple[int, bytes]:
         """(link id, handle to give to the other end)."""
         buf = C.create_string_buffer(_lib.KV_LINK_HANDLE_BYTES)
