@@ -118,7 +118,9 @@ def kv_hop_pass(be, fb, cfg, bs, out, rank, world, dist, torch) -> dict:
     (rb200_send_kv_layer / rb200_recv_kv_layer) and the K/V links (plain peer stores + counters,
     rb200_kv_link_*). For each: the hop alone, all layers of a prompt back to back (one pair, and
     one prompt to every decode GPU at once), and the hop issued from the layer observer while the
-    prompts are prefilled (what it adds to the prefill time). The received pages of three layers
+    prompts are prefilled (what it adds to the prefill time). The links also carry a finished
+    prompt as layer ranges (rb200_kv_link_send_layers: several layers per message), one prompt and
+    RANGE_PROMPTS of them back to back; `gbs_per_pair` is the latter. The received pages of three layers
     are compared byte for byte with the sender's inside the run. Times are the host clock up to
     rb200_kv_hop_sync, max over ranks."""
     import hashlib
